@@ -1,0 +1,162 @@
+/* ks_b200.h -- C ABI of the B200 trace -> interference-table library (libks_b200.so).
+ *
+ * Calling convention, copied from the reference's own ctypes exports (scheduler/agent.cpp:39,71,75,643,788,805 and
+ * the binding table scheduler/sched_hooks.py:36-59): plain C scalars and pointers, no exceptions, no exit(); an
+ * integer comes back, negative = error (sched_prefetch returns -1 on a null tag, agent.cpp:788-790), zero or
+ * positive = rows / items produced.  The text of the last error of a handle is ks_last_error().
+ *
+ * Threading: one handle = one CUDA stream = not re-entrant.  A call may arrive on a thread with no current CUDA
+ * context (ctypes releases the GIL and the reference guards against exactly that, agent.cpp:653-656), so every
+ * entry point selects the handle's device itself.
+ *
+ * Memory: the caller owns inputs and outputs; the handle owns its scratch.  Unless a flag says otherwise pointers
+ * are HOST pointers; KS_ON_DEVICE marks them as device pointers on the handle's device (all pointer arguments of
+ * that call).  There is no CPU fallback anywhere: without a CUDA device every call fails with KS_ERR_CUDA.
+ */
+#ifndef KS_B200_H
+#define KS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KS_VERSION 1
+
+/* ---- status codes (returned negated: -KS_ERR_x) */
+#define KS_OK 0
+#define KS_ERR_ARG 1          /* null pointer, bad flag, size out of range */
+#define KS_ERR_CUDA 2         /* a CUDA call failed; see ks_last_error */
+#define KS_ERR_RECORD 3       /* a record has end_ns < start_ns or a duration >= 2^31 ns */
+#define KS_ERR_NOT_ORDERED 4  /* KS_ASSUME_TIME_ORDERED was given but start_ns decreases somewhere */
+#define KS_ERR_TOO_MANY_KEYS 5 /* more than 65,535 distinct kernel keys */
+#define KS_ERR_TABLE_FULL 6   /* the pair dictionary is full: create the handle with a larger max_pair_rows */
+#define KS_ERR_CAPACITY 7     /* an output buffer is too small */
+#define KS_ERR_WAIT 8         /* a bounded device-side wait ran out (the result is not valid) */
+#define KS_ERR_DUPLICATE 9    /* ks_count_batches: a start_ns occurs twice in one file (the reference asserts) */
+#define KS_ERR_TOO_LARGE 10   /* more items than one call supports (2^30 per sort, 2^32 overlapping pairs) */
+
+/* ---- flags */
+#define KS_ON_DEVICE 1u            /* pointer arguments are device pointers */
+#define KS_ASSUME_TIME_ORDERED 2u  /* records are ordered by start_ns: verified, not sorted */
+#define KS_KEY_TYPE 4u             /* key = tenant + name + block (a TYPE row); default is the SHAPE key */
+
+/* 48-byte launch record.  Replaces one row of the agent's timing log: scheduler/agent.cpp:500-508 (TimingResult)
+ * as written at :692-705, with the kernel name (kernel_key.hpp:13-55 short form) replaced by a dictionary id. */
+typedef struct ks_record {
+  uint32_t name_id;
+  uint32_t grid[3];
+  uint32_t block[3];
+  uint32_t smem_word; /* bits 0..22 dynamic smem bytes, bit 23 solo run, bits 24..31 tenant */
+  uint64_t start_ns;
+  uint64_t end_ns;
+} ks_record;
+
+/* One row of the pair table, sorted by (key_a, key_b); side a is the lower tenant.  Carries what the daemon's
+ * pair_eff.tsv row needs (scheduler/scheduler_daemon.cpp:193-202: efficiency, gangs = count) plus the slowdown
+ * statistics of both sides.  A side whose key has no solo baseline has NaN statistics and its flag bit clear. */
+typedef struct ks_pair_row {
+  uint64_t key_a, key_b;
+  uint64_t count;
+  uint64_t flags; /* bit 0: side a has a baseline; bit 1: side b has one */
+  double sum_a, mean_a, min_a, max_a, median_a;
+  double sum_b, mean_b, min_b, max_b, median_b;
+  double efficiency;    /* median over occurrences of (solo_a + solo_b) / (max(end) - min(start)) */
+  uint64_t span_sum_ns; /* sum over occurrences of max(end) - min(start) */
+} ks_pair_row;
+
+/* One row of the per-key table, sorted by key: what kernel_us.tsv needs (scheduler_daemon.cpp:195, :250-264). */
+typedef struct ks_key_row {
+  uint64_t key;
+  uint32_t name_id;
+  uint32_t grid[3];
+  uint32_t block[3];
+  uint32_t smem;
+  uint32_t tenant;
+  uint32_t reserved;
+  uint64_t launches;
+  uint64_t solo_launches;
+  double solo_ns; /* exact median duration of the solo launches; NaN if there are none */
+} ks_key_row;
+
+typedef struct ks_config {
+  uint64_t max_records;   /* scratch is sized for this many records up front (it grows on demand) */
+  uint64_t max_pairs;     /* ... and this many overlapping launch pairs */
+  uint32_t max_pair_rows; /* capacity of the pair dictionary in rows (rounded up to a power of two, x2 slots) */
+  uint32_t reserved;
+} ks_config;
+
+typedef struct ks_table_info {
+  uint64_t n_records, n_keys, n_solo, n_pairs, n_rows;
+  uint64_t max_duration_ns;
+  uint64_t min_start_ns, max_start_ns;
+  uint32_t was_time_ordered; /* 1 if the input needed no sort */
+  uint32_t reserved;
+  /* device time of the stages of the last call, CUDA events on the handle's stream */
+  float ms_stage_in, ms_decode, ms_order, ms_dict, ms_join, ms_sort, ms_reduce, ms_finalize, ms_total;
+  float reserved_f;
+} ks_table_info;
+
+typedef struct ks_handle ks_handle;
+
+int ks_version(void);
+const char* ks_status_string(int status);
+
+/* stream: a cudaStream_t to launch on, or NULL for a stream of the handle's own.  cfg may be NULL. */
+ks_handle* ks_create(int device, void* stream, const ks_config* cfg);
+void ks_destroy(ks_handle* h);
+const char* ks_last_error(ks_handle* h);
+/* the stream the handle launches on (for timing with events) */
+void* ks_stream(ks_handle* h);
+
+/* ---- the whole path.  Stands where the reference runs its offline post-processing over the agents' logs
+ * (scheduler/postprocess.py:8-41 and the absent make_pair_eff.py named at scheduler_daemon.cpp:5,193,848).
+ * Returns the number of pair rows; the tables stay in the handle until the next call. info may be NULL. */
+int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info);
+int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows, uint32_t flags);
+int64_t ks_copy_key_rows(ks_handle* h, ks_key_row* dst, uint64_t capacity_rows, uint32_t flags);
+
+/* ---- stage entry points (each is what one kernel family computes; used by the parity tests) */
+
+/* K1: 64-bit kernel key of every record.  Key composition: scheduler_daemon.cpp:196-197, :210-213 (shape
+ * signature model|kernel|block|grid) and :213 / pairprof_daemon.cpp:122-123 (type: no grid). */
+int64_t ks_hash_keys(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t* keys_out);
+
+/* K2: stable LSD radix sort of (key, value) pairs on key bits [begin_bit, end_bit), in place.  The grouping
+ * primitive behind pandas' sort-based groupby in postprocess/profile_postprocess.py:10-25. */
+int64_t ks_sort_pairs_u64(ks_handle* h, uint64_t* keys, uint64_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags);
+int64_t ks_sort_pairs_u32(ks_handle* h, uint32_t* keys, uint32_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags);
+
+/* K1+K2: the launches grouped by key: (key, start_ns) of every record in (key, start_ns) order. */
+int64_t ks_sort_launches(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t* keys_out, uint64_t* start_out);
+
+/* K3: the interval join.  Writes the overlapping launch pairs as positions in the start_ns-ordered trace
+ * (idx_a: the launch of the lower tenant).  Replaces the quadratic scans of postprocess.py:19-39 with the interval
+ * rule a.start < b.end && b.start < a.end.  The order of the pairs is unspecified.  Returns the pair count; if it
+ * exceeds capacity only the count is valid (-KS_ERR_CAPACITY is NOT returned, so a first call with capacity 0
+ * sizes the buffers). */
+int64_t ks_join_overlaps(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint32_t* idx_a, uint32_t* idx_b, uint64_t capacity);
+
+/* K4: per segment of `values` (segment s = [offsets[s], offsets[s+1])): sum, min, max and the two middle order
+ * statistics x[(n-1)/2], x[n/2] -- exact, by selection.  out: 6 uint64 per segment {count, sum, min, max, lo, hi}. */
+int64_t ks_segment_stats(ks_handle* h, const uint32_t* values, const uint64_t* offsets, uint64_t n_segments, uint32_t flags, uint64_t* out);
+
+/* The reference's batch counter verbatim: scheduler/postprocess.py:17-41 prints [n_alone, n_pairs] where a pair is
+ * two launches, one per file, with the same start_ns.  The caller applies the [-200000:] slice of :12. */
+int64_t ks_count_batches(ks_handle* h, const uint64_t* start1, uint64_t n1, const uint64_t* start2, uint64_t n2, uint32_t flags, uint64_t out[2]);
+
+/* postprocess/profile_postprocess.py:5-27 combine_duplicates: launches-weighted mean per group, NaN cells skipped
+ * in numerator and weight (min_count=1 semantics, :14,:21), plus the group's total launches (:25).
+ * group: dense group id per row (the host maps (Kernel, Block) to ids); values: rows x cols, row major. */
+int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double* launches, const double* values, uint64_t rows, uint32_t cols,
+                              uint32_t n_groups, uint32_t flags, double* out_total, double* out_means);
+
+/* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
+ * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */
+int64_t ks_function_base(const char* symbol, char* out, uint64_t capacity);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

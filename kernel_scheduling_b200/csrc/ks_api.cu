@@ -1,0 +1,865 @@
+// ks_api.cu -- the handle, the host-side orchestration of the stages and the extern "C" layer (include/ks_b200.h).
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "ks_common.cuh"
+#include "ks_decode.cuh"
+#include "ks_dict.cuh"
+#include "ks_join.cuh"
+#include "ks_misc.cuh"
+#include "ks_reduce.cuh"
+#include "ks_sort.cuh"
+
+using namespace ks;
+
+namespace {
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+};
+
+}  // namespace
+
+struct ks_handle {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  std::string last_error;
+  ks_config cfg{};
+
+  Control* d_ctl = nullptr;
+  Control* h_ctl = nullptr;  // pinned
+
+  // dictionary (fixed size)
+  unsigned long long* dict_keys = nullptr;
+  uint4* dict_words = nullptr;
+  uint32_t *dict_launches = nullptr, *dict_solo = nullptr;
+  unsigned long long* dkeys = nullptr;
+  uint32_t *dslot = nullptr, *drank = nullptr, *kid_of_slot = nullptr, *slot_of_kid = nullptr, *row_of_kid = nullptr;
+  unsigned long long* keys_sorted = nullptr;
+  double* solo_ns = nullptr;
+  ks_key_row* key_rows = nullptr;
+
+  // growable
+  DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
+  DevBuf skey[2], lane[2][kLanes];
+  DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
+  DevBuf tmp[6];
+
+  // results of the last ks_build_table
+  uint64_t n_pair_rows = 0, n_key_rows = 0;
+  cudaEvent_t ev[12]{};
+};
+
+namespace {
+
+thread_local std::string g_null_error;
+
+int fail(ks_handle* h, int code, const std::string& msg) {
+  if (h) h->last_error = msg;
+  return -code;
+}
+
+#define KS_CUDA(h, call)                                                                                            \
+  do {                                                                                                              \
+    cudaError_t e__ = (call);                                                                                       \
+    if (e__ != cudaSuccess) return fail((h), KS_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__));     \
+  } while (0)
+
+int ensure(ks_handle* h, DevBuf& b, size_t bytes) {
+  if (bytes <= b.cap) return 0;
+  if (b.p) {
+    cudaError_t e = cudaFree(b.p);
+    b.p = nullptr;
+    b.cap = 0;
+    if (e != cudaSuccess) return fail(h, KS_ERR_CUDA, std::string("cudaFree: ") + cudaGetErrorString(e));
+  }
+  const size_t want = (bytes + 255) & ~(size_t)255;
+  cudaError_t e = cudaMalloc(&b.p, want);
+  if (e != cudaSuccess) return fail(h, KS_ERR_CUDA, "cudaMalloc of " + std::to_string(want) + " bytes: " + cudaGetErrorString(e));
+  b.cap = want;
+  return 0;
+}
+#define KS_ENSURE(h, buf, bytes)              \
+  do {                                        \
+    int r__ = ensure((h), (buf), (bytes));    \
+    if (r__) return r__;                      \
+  } while (0)
+
+template <typename T>
+T* as(const DevBuf& b) { return reinterpret_cast<T*>(b.p); }
+
+int bit_length(uint64_t v) {
+  int b = 0;
+  while (v) { ++b; v >>= 1; }
+  return b;
+}
+
+int status_of_err(uint32_t err, bool assume_ordered) {
+  if (err & kErrWait) return KS_ERR_WAIT;
+  if (err & kErrRecord) return KS_ERR_RECORD;
+  if (err & kErrTooManyKeys) return KS_ERR_TOO_MANY_KEYS;
+  if ((err & kErrUnordered) && assume_ordered) return KS_ERR_NOT_ORDERED;
+  if (err & kErrPairTableFull) return KS_ERR_TABLE_FULL;
+  if (err & kErrTooLarge) return KS_ERR_TOO_LARGE;
+  if (err & kErrDuplicate) return KS_ERR_DUPLICATE;
+  return KS_OK;
+}
+
+int read_ctl(ks_handle* h) {
+  KS_CUDA(h, cudaMemcpyAsync(h->h_ctl, h->d_ctl, sizeof(Control), cudaMemcpyDeviceToHost, h->stream));
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return 0;
+}
+
+// ---- K2 driver: sorts (keys, NV payload arrays) on key bits [begin_bit, end_bit); ping-pongs between the given
+// buffer sets; returns the index (0/1) of the set that holds the result, or a negative status.
+template <typename KeyT, typename ValT, int NV, int ITEMS>
+int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint64_t n, const uint32_t* n_dev, int begin_bit, int end_bit) {
+  if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
+  const int passes = (end_bit - begin_bit + 7) / 8;
+  if (passes <= 0 || n == 0) return 0;
+  constexpr int TILE = kSortThreads * ITEMS;
+  const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
+  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);  // + ticket
+  KS_ENSURE(h, h->lookback, lb_bytes);
+  KS_ENSURE(h, h->hist, 2 * 8 * 256 * sizeof(uint32_t));
+  uint32_t* hist = as<uint32_t>(h->hist);
+  uint32_t* gbase = hist + 8 * 256;
+  KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
+  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 8);
+  k_radix_hist<KeyT><<<hist_grid, 256, 0, h->stream>>>(keys[0], n_dev, (uint32_t)n, begin_bit, end_bit, hist);
+  k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
+  auto kern = k_onesweep_pass<KeyT, ValT, NV, ITEMS>;
+  constexpr size_t smem = sort_smem_bytes<KeyT, ValT, ITEMS>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    KS_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  int cur = 0;
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
+  for (int p = 0; p < passes; ++p) {
+    KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+    SortPassArgs<KeyT, ValT, NV> a{};
+    a.kin = keys[cur];
+    a.kout = keys[cur ^ 1];
+    for (int v = 0; v < NV; ++v) { a.vin[v] = vals[cur][v]; a.vout[v] = vals[cur ^ 1][v]; }
+    a.n_dev = n_dev;
+    a.n = (uint32_t)n;
+    a.shift = begin_bit + 8 * p;
+    a.bits = std::min(8, end_bit - a.shift);
+    a.gbase = gbase + p * 256;
+    a.lookback = as<uint32_t>(h->lookback);
+    a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+    a.err = &h->d_ctl->err;
+    kern<<<grid, kSortThreads, smem, h->stream>>>(a);
+    cur ^= 1;
+  }
+  KS_CUDA(h, cudaGetLastError());
+  return cur;
+}
+
+// stage a host or device input into a device pointer
+template <typename T>
+int stage_in(ks_handle* h, DevBuf& buf, const T* src, uint64_t count, bool on_device, const T** out) {
+  if (on_device) { *out = src; return 0; }
+  KS_ENSURE(h, buf, std::max<size_t>(count * sizeof(T), 16));
+  KS_CUDA(h, cudaMemcpyAsync(buf.p, src, count * sizeof(T), cudaMemcpyHostToDevice, h->stream));
+  *out = as<const T>(buf);
+  return 0;
+}
+
+int copy_out(ks_handle* h, void* dst, const void* src_dev, size_t bytes, bool on_device) {
+  if (bytes == 0) return 0;
+  KS_CUDA(h, cudaMemcpyAsync(dst, src_dev, bytes, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
+  return 0;
+}
+
+int reset_run(ks_handle* h) {
+  Control init{};
+  init.min_start = ~0ull;
+  *h->h_ctl = init;
+  KS_CUDA(h, cudaMemcpyAsync(h->d_ctl, h->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->dict_keys, 0, (size_t)kDictSlots * 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->dict_launches, 0, (size_t)kDictSlots * 4, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->dict_solo, 0, (size_t)kDictSlots * 4, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->drank, 0, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  return 0;
+}
+
+// K1 over device records -> timeline set 0, solo stream, dictionary.  keys_out optional (device).
+int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, unsigned long long* keys_out) {
+  KS_ENSURE(h, h->tl_start[0], std::max<size_t>(n * 8, 16));
+  KS_ENSURE(h, h->tl_dm[0], std::max<size_t>(n * 8, 16));
+  KS_ENSURE(h, h->solo_stream, std::max<size_t>(n * 8, 16));
+  if (n == 0) return 0;
+  DecodeArgs a{};
+  a.records = reinterpret_cast<const unsigned char*>(d_records);
+  a.n = n;
+  a.type_mode = (flags & KS_KEY_TYPE) ? 1 : 0;
+  a.dict_keys = h->dict_keys;
+  a.dict_words = h->dict_words;
+  a.dict_launches = h->dict_launches;
+  a.dict_solo = h->dict_solo;
+  a.tl_start = as<unsigned long long>(h->tl_start[0]);
+  a.tl_dm = as<unsigned long long>(h->tl_dm[0]);
+  a.solo_stream = as<unsigned long long>(h->solo_stream);
+  a.keys_out = keys_out;
+  a.ctl = h->d_ctl;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KS_CUDA(h, cudaFuncSetAttribute(k_decode_hash, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes()));
+    attr_set = true;
+  }
+  const uint64_t ntiles = (n + kDecodeThreads - 1) / kDecodeThreads;
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 3);
+  k_decode_hash<<<grid, kDecodeThreads, decode_smem_bytes(), h->stream>>>(a);
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
+// sorts timeline set 0 by start_ns if the decode found it unordered; returns the set that holds the ordered timeline
+int order_timeline(ks_handle* h, uint64_t n, bool* was_ordered) {
+  *was_ordered = !(h->h_ctl->err & kErrUnordered);
+  if (*was_ordered || n < 2) return 0;
+  KS_ENSURE(h, h->tl_start[1], n * 8);
+  KS_ENSURE(h, h->tl_dm[1], n * 8);
+  unsigned long long* keys[2] = {as<unsigned long long>(h->tl_start[0]), as<unsigned long long>(h->tl_start[1])};
+  unsigned long long* vals[2][1] = {{as<unsigned long long>(h->tl_dm[0])}, {as<unsigned long long>(h->tl_dm[1])}};
+  const int end_bit = bit_length(h->h_ctl->min_start ^ h->h_ctl->max_start);
+  return radix_sort<unsigned long long, unsigned long long, 1, 8>(h, keys, vals, n, nullptr, 0, end_bit);
+}
+
+int run_dict(ks_handle* h) {
+  DictArgs d{};
+  d.dict_keys = h->dict_keys;
+  d.dkeys = h->dkeys;
+  d.dslot = h->dslot;
+  d.drank = h->drank;
+  d.kid_of_slot = h->kid_of_slot;
+  d.slot_of_kid = h->slot_of_kid;
+  d.keys_sorted = h->keys_sorted;
+  d.ctl = h->d_ctl;
+  k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
+  k_dict_rank<<<dim3((kMaxKeys + 255) / 256, kRankSplit), 256, 0, h->stream>>>(d);
+  k_dict_place<<<(kMaxKeys + 255) / 256, 256, 0, h->stream>>>(d);
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
+int ensure_samples(ks_handle* h, uint64_t cap) {
+  for (int s = 0; s < 2; ++s) {
+    KS_ENSURE(h, h->skey[s], cap * 4);
+    for (int l = 0; l < kLanes; ++l) KS_ENSURE(h, h->lane[s][l], cap * 4);
+  }
+  return 0;
+}
+
+uint64_t sample_capacity(ks_handle* h) {
+  uint64_t cap = h->skey[0].cap / 4;
+  for (int s = 0; s < 2; ++s) {
+    cap = std::min<uint64_t>(cap, h->skey[s].cap / 4);
+    for (int l = 0; l < kLanes; ++l) cap = std::min<uint64_t>(cap, h->lane[s][l].cap / 4);
+  }
+  return cap;
+}
+
+int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b) {
+  if (n == 0) return 0;
+  JoinArgs j{};
+  j.tl_start = as<unsigned long long>(h->tl_start[tl]);
+  j.tl_dm = as<unsigned long long>(h->tl_dm[tl]);
+  j.kid_of_slot = h->kid_of_slot;
+  j.n = n;
+  j.skey = as<uint32_t>(h->skey[0]);
+  j.lane0 = as<uint32_t>(h->lane[0][0]);
+  j.lane1 = as<uint32_t>(h->lane[0][1]);
+  j.lane2 = as<uint32_t>(h->lane[0][2]);
+  j.idx_a = idx_a;
+  j.idx_b = idx_b;
+  j.capacity = capacity;
+  j.ctl = h->d_ctl;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KS_CUDA(h, cudaFuncSetAttribute(k_join<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem_bytes()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_join<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem_bytes()));
+    attr_set = true;
+  }
+  const unsigned grid = (unsigned)((n + kJoinTile - 1) / kJoinTile);
+  if (idx_a) k_join<true><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
+  else k_join<false><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
+// rows + segment statistics over sorted samples (set `s`), n samples
+int run_rows_and_stats(ks_handle* h, const uint32_t* skey, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n, uint32_t max_rows) {
+  const uint32_t max_tiles = (uint32_t)((n + kRowsTile - 1) / kRowsTile);
+  KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
+  KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
+  KS_ENSURE(h, h->row_key, ((size_t)max_rows + 2) * 4);
+  KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
+  KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
+  RowsArgs r{};
+  r.skey = skey;
+  r.n_dev = nullptr;
+  r.n = (uint32_t)n;
+  r.tile_cnt = as<uint32_t>(h->tile_cnt);
+  r.row_start = as<uint32_t>(h->row_start);
+  r.row_key = as<uint32_t>(h->row_key);
+  r.row_of_kid = h->row_of_kid;
+  r.max_tiles = max_tiles;
+  r.max_rows = max_rows;
+  r.ctl = h->d_ctl;
+  const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_tiles, (uint32_t)h->sm_count * 8));
+  k_rows_count<<<grid, 256, 0, h->stream>>>(r);
+  k_rows_scan<<<1, 1024, 0, h->stream>>>(r);
+  k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
+  SegArgs s{};
+  for (int l = 0; l < kLanes; ++l) s.lane[l] = lanes[l];
+  s.n_lanes = n_lanes;
+  s.row_start = as<uint32_t>(h->row_start);
+  s.n_rows_dev = &h->d_ctl->n_rows;
+  s.max_rows = max_rows;
+  s.stats = as<RowStats>(h->stats);
+  s.big_rows = as<uint32_t>(h->big_rows);
+  s.ctl = h->d_ctl;
+  const int sgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 7) / 8, (uint32_t)h->sm_count * 16));
+  k_seg_small<<<sgrid, 256, 0, h->stream>>>(s);
+  k_seg_big<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
+__global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start, uint32_t n_rows, unsigned long long* out) {
+  const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const RowStats st = stats[r];
+  out[6 * (size_t)r + 0] = row_start[r + 1] - row_start[r];
+  out[6 * (size_t)r + 1] = st.sum[0];
+  out[6 * (size_t)r + 2] = st.mn[0];
+  out[6 * (size_t)r + 3] = st.mx[0];
+  out[6 * (size_t)r + 4] = st.lo[0];
+  out[6 * (size_t)r + 5] = st.hi[0];
+}
+
+float ev_ms(cudaEvent_t a, cudaEvent_t b) {
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, a, b);
+  return ms;
+}
+
+}  // namespace
+
+// =========================================================================================================
+extern "C" {
+
+int ks_version(void) { return KS_VERSION; }
+
+const char* ks_status_string(int status) {
+  switch (status < 0 ? -status : status) {
+    case KS_OK: return "ok";
+    case KS_ERR_ARG: return "bad argument";
+    case KS_ERR_CUDA: return "CUDA error";
+    case KS_ERR_RECORD: return "record with end_ns < start_ns or a duration of 2^31 ns or more";
+    case KS_ERR_NOT_ORDERED: return "records are not ordered by start_ns";
+    case KS_ERR_TOO_MANY_KEYS: return "more than 65,535 distinct kernel keys";
+    case KS_ERR_TABLE_FULL: return "more pair rows than max_pair_rows";
+    case KS_ERR_CAPACITY: return "output buffer too small";
+    case KS_ERR_WAIT: return "a bounded device-side wait ran out";
+    case KS_ERR_DUPLICATE: return "duplicate start_ns inside one file";
+    case KS_ERR_TOO_LARGE: return "too many items for one call";
+    default: return "unknown status";
+  }
+}
+
+ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+    g_null_error = "no such CUDA device";
+    return nullptr;
+  }
+  if (cudaSetDevice(device) != cudaSuccess) return nullptr;
+  ks_handle* h = new ks_handle();
+  h->device = device;
+  cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (cfg) h->cfg = *cfg;
+  if (h->cfg.max_pair_rows == 0) h->cfg.max_pair_rows = 1u << 22;
+  bool ok = true;
+  if (stream) {
+    h->stream = reinterpret_cast<cudaStream_t>(stream);
+  } else {
+    ok = ok && cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) == cudaSuccess;
+    h->own_stream = true;
+  }
+  auto alloc = [&](auto** p, size_t bytes) { ok = ok && cudaMalloc(reinterpret_cast<void**>(p), bytes) == cudaSuccess; };
+  alloc(&h->d_ctl, sizeof(Control));
+  ok = ok && cudaMallocHost(reinterpret_cast<void**>(&h->h_ctl), sizeof(Control)) == cudaSuccess;
+  alloc(&h->dict_keys, (size_t)kDictSlots * 8);
+  alloc(&h->dict_words, (size_t)kDictSlots * 32);
+  alloc(&h->dict_launches, (size_t)kDictSlots * 4);
+  alloc(&h->dict_solo, (size_t)kDictSlots * 4);
+  alloc(&h->kid_of_slot, (size_t)kDictSlots * 4);
+  alloc(&h->dkeys, (size_t)(kMaxKeys + 1) * 8);
+  alloc(&h->dslot, (size_t)(kMaxKeys + 1) * 4);
+  alloc(&h->drank, (size_t)(kMaxKeys + 1) * 4);
+  alloc(&h->slot_of_kid, (size_t)(kMaxKeys + 1) * 4);
+  alloc(&h->row_of_kid, (size_t)(kMaxKeys + 1) * 4);
+  alloc(&h->keys_sorted, (size_t)(kMaxKeys + 1) * 8);
+  alloc(&h->solo_ns, (size_t)(kMaxKeys + 1) * 8);
+  alloc(&h->key_rows, (size_t)(kMaxKeys + 1) * sizeof(ks_key_row));
+  for (auto& e : h->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+  if (ok && h->cfg.max_records) {
+    const size_t n = h->cfg.max_records;
+    ok = ok && !ensure(h, h->tl_start[0], n * 8) && !ensure(h, h->tl_dm[0], n * 8) && !ensure(h, h->solo_stream, n * 8);
+  }
+  if (ok && h->cfg.max_pairs) ok = !ensure_samples(h, h->cfg.max_pairs);
+  if (!ok) {
+    g_null_error = std::string("ks_create: ") + cudaGetErrorString(cudaGetLastError());
+    ks_destroy(h);
+    return nullptr;
+  }
+  return h;
+}
+
+void ks_destroy(ks_handle* h) {
+  if (!h) return;
+  cudaSetDevice(h->device);
+  if (h->stream) cudaStreamSynchronize(h->stream);
+  auto fr = [](void* p) { if (p) cudaFree(p); };
+  fr(h->d_ctl); fr(h->dict_keys); fr(h->dict_words); fr(h->dict_launches); fr(h->dict_solo); fr(h->kid_of_slot);
+  fr(h->dkeys); fr(h->dslot); fr(h->drank); fr(h->slot_of_kid); fr(h->row_of_kid); fr(h->keys_sorted); fr(h->solo_ns); fr(h->key_rows);
+  if (h->h_ctl) cudaFreeHost(h->h_ctl);
+  DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
+                    &h->skey[0], &h->skey[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
+                    &h->big_rows, &h->pair_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+  for (DevBuf* b : bufs) fr(b->p);
+  for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) fr(h->lane[s][l].p);
+  for (auto& e : h->ev) if (e) cudaEventDestroy(e);
+  if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
+  delete h;
+}
+
+const char* ks_last_error(ks_handle* h) { return h ? h->last_error.c_str() : g_null_error.c_str(); }
+void* ks_stream(ks_handle* h) { return h ? reinterpret_cast<void*>(h->stream) : nullptr; }
+
+// ---------------------------------------------------------------------------------------------------------
+int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info) {
+  if (!h) return -KS_ERR_ARG;
+  if ((!records && n) || (flags & ~(KS_ON_DEVICE | KS_ASSUME_TIME_ORDERED | KS_KEY_TYPE))) return fail(h, KS_ERR_ARG, "ks_build_table: bad argument");
+  if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_build_table: 2^30 records or more in one call");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const bool assume_ordered = (flags & KS_ASSUME_TIME_ORDERED) != 0;
+  h->n_pair_rows = h->n_key_rows = 0;
+  cudaEvent_t* ev = h->ev;
+
+  cudaEventRecord(ev[0], h->stream);
+  const unsigned char* d_rec = nullptr;
+  { int r = stage_in<unsigned char>(h, h->records, reinterpret_cast<const unsigned char*>(records), n * 48, (flags & KS_ON_DEVICE) != 0, &d_rec); if (r) return r; }
+  if (n && (reinterpret_cast<uintptr_t>(d_rec) & 15u)) return fail(h, KS_ERR_ARG, "ks_build_table: device records must be 16-byte aligned");
+  { int r = reset_run(h); if (r) return r; }
+  cudaEventRecord(ev[1], h->stream);
+  { int r = run_decode(h, d_rec, n, flags, nullptr); if (r) return r; }
+  cudaEventRecord(ev[2], h->stream);
+
+  // order the timeline (needs the decode's flags on the host unless the caller vouches for the order)
+  int tl = 0;
+  bool was_ordered = true;
+  if (!assume_ordered) {
+    { int r = read_ctl(h); if (r) return r; }
+    const int st = status_of_err(h->h_ctl->err, false);
+    if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
+    tl = order_timeline(h, n, &was_ordered);
+    if (tl < 0) return tl;
+  }
+  cudaEventRecord(ev[3], h->stream);
+
+  { int r = run_dict(h); if (r) return r; }
+  cudaEventRecord(ev[4], h->stream);
+
+  // samples: solo launches first, pairs appended by the join; grow and redo if the stream was too small
+  uint64_t cap = sample_capacity(h);
+  if (cap < std::max<uint64_t>(2 * n, 1u << 16)) {
+    cap = std::max<uint64_t>(2 * n, 1u << 16);
+    int r = ensure_samples(h, cap);
+    if (r) return r;
+  }
+  uint64_t n_samples = 0;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    SoloArgs s{};
+    s.solo_stream = as<unsigned long long>(h->solo_stream);
+    s.kid_of_slot = h->kid_of_slot;
+    s.skey = as<uint32_t>(h->skey[0]);
+    s.lane0 = as<uint32_t>(h->lane[0][0]);
+    s.lane1 = as<uint32_t>(h->lane[0][1]);
+    s.lane2 = as<uint32_t>(h->lane[0][2]);
+    s.capacity = cap;
+    s.ctl = h->d_ctl;
+    k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+    if (attempt == 0) cudaEventRecord(ev[5], h->stream);
+    { int r = run_join(h, tl, n, cap, nullptr, nullptr); if (r) return r; }
+    { int r = read_ctl(h); if (r) return r; }
+    const int st = status_of_err(h->h_ctl->err, assume_ordered);
+    if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
+    n_samples = h->h_ctl->n_pairs;
+    if (n_samples <= cap) break;
+    if (n_samples >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_build_table: 2^30 samples or more");
+    if (attempt == 1) return fail(h, KS_ERR_CAPACITY, "ks_build_table: sample stream still too small");
+    cap = n_samples + n_samples / 16;
+    int r = ensure_samples(h, cap);
+    if (r) return r;
+  }
+  cudaEventRecord(ev[6], h->stream);
+  const uint64_t nk = h->h_ctl->n_keys, n_solo = h->h_ctl->n_solo;
+
+  // K2: group the samples by sort key
+  uint32_t* keys[2] = {as<uint32_t>(h->skey[0]), as<uint32_t>(h->skey[1])};
+  uint32_t* vals[2][kLanes];
+  for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) vals[s][l] = as<uint32_t>(h->lane[s][l]);
+  const int end_bit = bit_length(nk + nk * nk);
+  const int cur = radix_sort<uint32_t, uint32_t, kLanes, 16>(h, keys, vals, n_samples, nullptr, 0, end_bit);
+  if (cur < 0) return cur;
+  cudaEventRecord(ev[7], h->stream);
+
+  // K4: rows, statistics, tables
+  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n_samples, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
+  const uint32_t* lanes[kLanes] = {vals[cur][0], vals[cur][1], vals[cur][2]};
+  { int r = run_rows_and_stats(h, keys[cur], lanes, kLanes, n_samples, max_rows); if (r) return r; }
+  cudaEventRecord(ev[8], h->stream);
+  KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
+  FinalArgs f{};
+  f.stats = as<RowStats>(h->stats);
+  f.row_start = as<uint32_t>(h->row_start);
+  f.row_key = as<uint32_t>(h->row_key);
+  f.row_of_kid = h->row_of_kid;
+  f.slot_of_kid = h->slot_of_kid;
+  f.keys_sorted = h->keys_sorted;
+  f.dict_words = h->dict_words;
+  f.dict_launches = h->dict_launches;
+  f.dict_solo = h->dict_solo;
+  f.solo_ns = h->solo_ns;
+  f.key_rows = h->key_rows;
+  f.pair_rows = as<ks_pair_row>(h->pair_rows);
+  f.max_pair_rows = max_rows;
+  f.ctl = h->d_ctl;
+  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
+  k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
+  KS_CUDA(h, cudaGetLastError());
+  cudaEventRecord(ev[9], h->stream);
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, assume_ordered);
+  if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
+
+  const Control& c = *h->h_ctl;
+  h->n_key_rows = c.n_keys;
+  h->n_pair_rows = c.n_rows - c.ticket2;
+  if (info) {
+    std::memset(info, 0, sizeof(*info));
+    info->n_records = n;
+    info->n_keys = c.n_keys;
+    info->n_solo = n_solo;
+    info->n_pairs = n_samples - n_solo;
+    info->n_rows = h->n_pair_rows;
+    info->max_duration_ns = c.max_dur;
+    info->min_start_ns = n ? c.min_start : 0;
+    info->max_start_ns = c.max_start;
+    info->was_time_ordered = was_ordered && !(c.err & kErrUnordered);
+    info->ms_stage_in = ev_ms(ev[0], ev[1]);
+    info->ms_decode = ev_ms(ev[1], ev[2]);
+    info->ms_order = ev_ms(ev[2], ev[3]);
+    info->ms_dict = ev_ms(ev[3], ev[5]);
+    info->ms_join = ev_ms(ev[5], ev[6]);
+    info->ms_sort = ev_ms(ev[6], ev[7]);
+    info->ms_reduce = ev_ms(ev[7], ev[8]);
+    info->ms_finalize = ev_ms(ev[8], ev[9]);
+    info->ms_total = ev_ms(ev[0], ev[9]);
+  }
+  return (int64_t)h->n_pair_rows;
+}
+
+int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows, uint32_t flags) {
+  if (!h || (!dst && h->n_pair_rows)) return -KS_ERR_ARG;
+  if (capacity_rows < h->n_pair_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_pair_rows: buffer too small");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = copy_out(h, dst, h->pair_rows.p, h->n_pair_rows * sizeof(ks_pair_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)h->n_pair_rows;
+}
+
+int64_t ks_copy_key_rows(ks_handle* h, ks_key_row* dst, uint64_t capacity_rows, uint32_t flags) {
+  if (!h || (!dst && h->n_key_rows)) return -KS_ERR_ARG;
+  if (capacity_rows < h->n_key_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_key_rows: buffer too small");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = copy_out(h, dst, h->key_rows, h->n_key_rows * sizeof(ks_key_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)h->n_key_rows;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+int64_t ks_hash_keys(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t* keys_out) {
+  if (!h || ((!records || !keys_out) && n)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  const unsigned char* d_rec = nullptr;
+  { int r = stage_in<unsigned char>(h, h->records, reinterpret_cast<const unsigned char*>(records), n * 48, dev, &d_rec); if (r) return r; }
+  unsigned long long* d_keys = reinterpret_cast<unsigned long long*>(keys_out);
+  if (!dev) { KS_ENSURE(h, h->keys_tmp, std::max<size_t>(n * 8, 16)); d_keys = as<unsigned long long>(h->keys_tmp); }
+  { int r = reset_run(h); if (r) return r; }
+  { int r = run_decode(h, d_rec, n, flags, d_keys); if (r) return r; }
+  if (!dev) { int r = copy_out(h, keys_out, d_keys, n * 8, false); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err & (kErrRecord | kErrWait | kErrTooManyKeys), false);
+  if (st) return fail(h, st, std::string("ks_hash_keys: ") + ks_status_string(st));
+  return (int64_t)n;
+}
+
+}  // extern "C"
+
+template <typename KeyT, int ITEMS>
+static int64_t sort_pairs_impl(ks_handle* h, KeyT* keys, KeyT* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags) {
+  const int width = (int)sizeof(KeyT) * 8;
+  if (!h || (!keys && n) || begin_bit < 0 || end_bit > width || begin_bit > end_bit) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n == 0 || begin_bit == end_bit) return (int64_t)n;
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  const size_t bytes = n * sizeof(KeyT);
+  KeyT* k[2];
+  KeyT* v[2][1];
+  KS_ENSURE(h, h->tmp[1], bytes);
+  k[1] = as<KeyT>(h->tmp[1]);
+  if (dev) { k[0] = keys; }
+  else { KS_ENSURE(h, h->tmp[0], bytes); k[0] = as<KeyT>(h->tmp[0]); KS_CUDA(h, cudaMemcpyAsync(k[0], keys, bytes, cudaMemcpyHostToDevice, h->stream)); }
+  v[0][0] = v[1][0] = nullptr;
+  if (vals) {
+    KS_ENSURE(h, h->tmp[3], bytes);
+    v[1][0] = as<KeyT>(h->tmp[3]);
+    if (dev) { v[0][0] = vals; }
+    else { KS_ENSURE(h, h->tmp[2], bytes); v[0][0] = as<KeyT>(h->tmp[2]); KS_CUDA(h, cudaMemcpyAsync(v[0][0], vals, bytes, cudaMemcpyHostToDevice, h->stream)); }
+  }
+  { int r = reset_run(h); if (r) return r; }
+  int cur;
+  if (vals) cur = radix_sort<KeyT, KeyT, 1, ITEMS>(h, k, v, n, nullptr, begin_bit, end_bit);
+  else cur = radix_sort<KeyT, KeyT, 0, ITEMS>(h, k, v, n, nullptr, begin_bit, end_bit);
+  if (cur < 0) return cur;
+  if (!dev || cur == 1) {
+    KS_CUDA(h, cudaMemcpyAsync(keys, k[cur], bytes, dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
+    if (vals) KS_CUDA(h, cudaMemcpyAsync(vals, v[cur][0], bytes, dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
+  }
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, false);
+  if (st) return fail(h, st, std::string("ks_sort_pairs: ") + ks_status_string(st));
+  return (int64_t)n;
+}
+
+extern "C" {
+
+int64_t ks_sort_pairs_u64(ks_handle* h, uint64_t* keys, uint64_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags) {
+  return sort_pairs_impl<unsigned long long, 8>(h, reinterpret_cast<unsigned long long*>(keys), reinterpret_cast<unsigned long long*>(vals), n, begin_bit, end_bit, flags);
+}
+int64_t ks_sort_pairs_u32(ks_handle* h, uint32_t* keys, uint32_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags) {
+  return sort_pairs_impl<uint32_t, 16>(h, keys, vals, n, begin_bit, end_bit, flags);
+}
+
+int64_t ks_sort_launches(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t* keys_out, uint64_t* start_out) {
+  if (!h || ((!records || !keys_out || !start_out) && n)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  const unsigned char* d_rec = nullptr;
+  { int r = stage_in<unsigned char>(h, h->records, reinterpret_cast<const unsigned char*>(records), n * 48, dev, &d_rec); if (r) return r; }
+  KS_ENSURE(h, h->keys_tmp, std::max<size_t>(n * 8, 16));
+  KS_ENSURE(h, h->tmp[4], std::max<size_t>(n * 8, 16));
+  KS_ENSURE(h, h->tl_start[1], std::max<size_t>(n * 8, 16));
+  { int r = reset_run(h); if (r) return r; }
+  { int r = run_decode(h, d_rec, n, flags, as<unsigned long long>(h->keys_tmp)); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  { const int st = status_of_err(h->h_ctl->err & (kErrRecord | kErrWait | kErrTooManyKeys), false); if (st) return fail(h, st, std::string("ks_sort_launches: ") + ks_status_string(st)); }
+  // by start_ns first (payload: the key), then stably by key: (key, start_ns) order
+  unsigned long long* a[2] = {as<unsigned long long>(h->tl_start[0]), as<unsigned long long>(h->tl_start[1])};
+  unsigned long long* b[2][1] = {{as<unsigned long long>(h->keys_tmp)}, {as<unsigned long long>(h->tmp[4])}};
+  int cur = 0;
+  if ((h->h_ctl->err & kErrUnordered) && n > 1) {
+    cur = radix_sort<unsigned long long, unsigned long long, 1, 8>(h, a, b, n, nullptr, 0, bit_length(h->h_ctl->min_start ^ h->h_ctl->max_start));
+    if (cur < 0) return cur;
+  }
+  unsigned long long* k2[2] = {b[cur][0], b[cur ^ 1][0]};
+  unsigned long long* v2[2][1] = {{a[cur]}, {a[cur ^ 1]}};
+  const int cur2 = radix_sort<unsigned long long, unsigned long long, 1, 8>(h, k2, v2, n, nullptr, 0, 64);
+  if (cur2 < 0) return cur2;
+  { int r = copy_out(h, keys_out, k2[cur2], n * 8, dev); if (r) return r; }
+  { int r = copy_out(h, start_out, v2[cur2][0], n * 8, dev); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  { const int st = status_of_err(h->h_ctl->err & kErrWait, false); if (st) return fail(h, st, "ks_sort_launches: bounded wait ran out"); }
+  return (int64_t)n;
+}
+
+int64_t ks_join_overlaps(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint32_t* idx_a, uint32_t* idx_b, uint64_t capacity) {
+  if (!h || (!records && n) || (capacity && (!idx_a || !idx_b))) return -KS_ERR_ARG;
+  if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_join_overlaps: 2^30 records or more");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  const unsigned char* d_rec = nullptr;
+  { int r = stage_in<unsigned char>(h, h->records, reinterpret_cast<const unsigned char*>(records), n * 48, dev, &d_rec); if (r) return r; }
+  { int r = reset_run(h); if (r) return r; }
+  { int r = run_decode(h, d_rec, n, flags, nullptr); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  { const int st = status_of_err(h->h_ctl->err, false); if (st) return fail(h, st, std::string("ks_join_overlaps: ") + ks_status_string(st)); }
+  bool was_ordered;
+  const int tl = order_timeline(h, n, &was_ordered);
+  if (tl < 0) return tl;
+  { int r = run_dict(h); if (r) return r; }
+  uint32_t *da = idx_a, *db = idx_b;
+  if (!dev) {
+    KS_ENSURE(h, h->tmp[0], std::max<size_t>(capacity * 4, 16));
+    KS_ENSURE(h, h->tmp[1], std::max<size_t>(capacity * 4, 16));
+    da = as<uint32_t>(h->tmp[0]);
+    db = as<uint32_t>(h->tmp[1]);
+  } else if (!capacity) {
+    KS_ENSURE(h, h->tmp[0], 16);
+    da = db = as<uint32_t>(h->tmp[0]);
+  }
+  { int r = run_join(h, tl, n, capacity, da, db); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  const uint64_t p = h->h_ctl->n_pairs;
+  if (!dev && p <= capacity) {
+    { int r = copy_out(h, idx_a, da, p * 4, false); if (r) return r; }
+    { int r = copy_out(h, idx_b, db, p * 4, false); if (r) return r; }
+    KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  }
+  return (int64_t)p;
+}
+
+int64_t ks_segment_stats(ks_handle* h, const uint32_t* values, const uint64_t* offsets, uint64_t n_segments, uint32_t flags, uint64_t* out) {
+  if (!h || !offsets || (n_segments && !out)) return -KS_ERR_ARG;
+  if (n_segments >= (1ull << 31)) return fail(h, KS_ERR_TOO_LARGE, "ks_segment_stats: too many segments");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n_segments == 0) return 0;
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  uint64_t n_values;
+  const unsigned long long* d_off = nullptr;
+  { int r = stage_in<unsigned long long>(h, h->tmp[0], reinterpret_cast<const unsigned long long*>(offsets), n_segments + 1, dev, &d_off); if (r) return r; }
+  if (dev) { KS_CUDA(h, cudaMemcpyAsync(&n_values, offsets + n_segments, 8, cudaMemcpyDeviceToHost, h->stream)); KS_CUDA(h, cudaStreamSynchronize(h->stream)); }
+  else n_values = offsets[n_segments];
+  if (n_values >= (1ull << 32)) return fail(h, KS_ERR_TOO_LARGE, "ks_segment_stats: 2^32 values or more");
+  if (!values && n_values) return -KS_ERR_ARG;
+  const uint32_t* d_val = nullptr;
+  { int r = stage_in<uint32_t>(h, h->tmp[1], values, n_values, dev, &d_val); if (r) return r; }
+  { int r = reset_run(h); if (r) return r; }
+  const uint32_t rows = (uint32_t)n_segments;
+  KS_ENSURE(h, h->row_start, ((size_t)rows + 2) * 4);
+  KS_ENSURE(h, h->stats, ((size_t)rows + 1) * sizeof(RowStats));
+  KS_ENSURE(h, h->big_rows, ((size_t)rows + 1) * 4);
+  KS_ENSURE(h, h->tmp[2], (size_t)rows * 48);
+  k_offsets_to_u32<<<(rows + 1 + 255) / 256, 256, 0, h->stream>>>(d_off, rows + 1, as<uint32_t>(h->row_start));
+  h->h_ctl->n_rows = rows;
+  KS_CUDA(h, cudaMemcpyAsync(&h->d_ctl->n_rows, &h->h_ctl->n_rows, 4, cudaMemcpyHostToDevice, h->stream));
+  SegArgs s{};
+  s.lane[0] = d_val;
+  s.n_lanes = 1;
+  s.row_start = as<uint32_t>(h->row_start);
+  s.n_rows_dev = &h->d_ctl->n_rows;
+  s.max_rows = rows;
+  s.stats = as<RowStats>(h->stats);
+  s.big_rows = as<uint32_t>(h->big_rows);
+  s.ctl = h->d_ctl;
+  const int sgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((rows + 7) / 8, (uint32_t)h->sm_count * 16));
+  k_seg_small<<<sgrid, 256, 0, h->stream>>>(s);
+  k_seg_big<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+  unsigned long long* d_out = dev ? reinterpret_cast<unsigned long long*>(out) : as<unsigned long long>(h->tmp[2]);
+  k_stats_to_u64<<<(rows + 255) / 256, 256, 0, h->stream>>>(as<RowStats>(h->stats), as<uint32_t>(h->row_start), rows, d_out);
+  KS_CUDA(h, cudaGetLastError());
+  if (!dev) { int r = copy_out(h, out, d_out, (size_t)rows * 48, false); if (r) return r; }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)n_segments;
+}
+
+int64_t ks_count_batches(ks_handle* h, const uint64_t* start1, uint64_t n1, const uint64_t* start2, uint64_t n2, uint32_t flags, uint64_t out[2]) {
+  if (!h || !out || (!start1 && n1) || (!start2 && n2)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  { int r = reset_run(h); if (r) return r; }
+  // private copies: the sort works in place
+  unsigned long long* s[2][2];
+  const uint64_t* src[2] = {start1, start2};
+  const uint64_t cnt[2] = {n1, n2};
+  for (int f = 0; f < 2; ++f) {
+    KS_ENSURE(h, h->tmp[2 * f], std::max<size_t>(cnt[f] * 8, 16));
+    KS_ENSURE(h, h->tmp[2 * f + 1], std::max<size_t>(cnt[f] * 8, 16));
+    s[f][0] = as<unsigned long long>(h->tmp[2 * f]);
+    s[f][1] = as<unsigned long long>(h->tmp[2 * f + 1]);
+    if (cnt[f]) KS_CUDA(h, cudaMemcpyAsync(s[f][0], src[f], cnt[f] * 8, dev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    if (cnt[f]) k_minmax_u64<<<h->sm_count * 2, 256, 0, h->stream>>>(s[f][0], cnt[f], h->d_ctl);
+  }
+  { int r = read_ctl(h); if (r) return r; }
+  const int end_bit = bit_length(h->h_ctl->min_start ^ h->h_ctl->max_start);
+  const unsigned long long* sorted[2];
+  for (int f = 0; f < 2; ++f) {
+    unsigned long long* k[2] = {s[f][0], s[f][1]};
+    unsigned long long* v[2][1] = {{nullptr}, {nullptr}};
+    const int cur = radix_sort<unsigned long long, unsigned long long, 0, 8>(h, k, v, cnt[f], nullptr, 0, end_bit);
+    if (cur < 0) return cur;
+    sorted[f] = k[cur];
+  }
+  if (n1 || n2) k_count_batches<<<h->sm_count * 4, 256, 0, h->stream>>>(sorted[0], n1, sorted[1], n2, h->d_ctl);
+  KS_CUDA(h, cudaGetLastError());
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, false);
+  if (st) return fail(h, st, std::string("ks_count_batches: ") + ks_status_string(st));
+  const uint64_t both = h->h_ctl->batches_both;
+  out[0] = n1 + n2 - 2 * both;
+  out[1] = both;
+  return (int64_t)(out[0] + out[1]);
+}
+
+int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double* launches, const double* values, uint64_t rows, uint32_t cols,
+                              uint32_t n_groups, uint32_t flags, double* out_total, double* out_means) {
+  if (!h || ((!group || !launches) && rows) || (!values && rows && cols) || (n_groups && (!out_total || (!out_means && cols)))) return -KS_ERR_ARG;
+  if (rows >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_combine_duplicates: too many rows");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n_groups == 0) return 0;
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  { int r = reset_run(h); if (r) return r; }
+  // sort row indices by group (stable) -> order[]
+  const size_t rb = std::max<size_t>(rows * 4, 16);
+  DevBuf* t = h->tmp;
+  KS_ENSURE(h, t[0], rb); KS_ENSURE(h, t[1], rb); KS_ENSURE(h, t[2], rb); KS_ENSURE(h, t[3], rb);
+  uint32_t* k[2] = {as<uint32_t>(t[0]), as<uint32_t>(t[1])};
+  uint32_t* v[2][1] = {{as<uint32_t>(t[2])}, {as<uint32_t>(t[3])}};
+  if (rows) {
+    KS_CUDA(h, cudaMemcpyAsync(k[0], group, rows * 4, dev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    k_iota<<<(unsigned)((rows + 255) / 256), 256, 0, h->stream>>>(v[0][0], (uint32_t)rows);
+  }
+  const int cur = radix_sort<uint32_t, uint32_t, 1, 16>(h, k, v, rows, nullptr, 0, bit_length(n_groups ? n_groups - 1 : 0));
+  if (cur < 0) return cur;
+  KS_ENSURE(h, t[4], ((size_t)n_groups + 2) * 4);
+  uint32_t* seg = as<uint32_t>(t[4]);
+  k_group_offsets<<<(unsigned)((rows + 1 + 255) / 256), 256, 0, h->stream>>>(k[cur], (uint32_t)rows, n_groups, seg);
+  const double *d_l = nullptr, *d_v = nullptr;
+  { int r = stage_in<double>(h, h->keys_tmp, launches, rows, dev, &d_l); if (r) return r; }
+  { int r = stage_in<double>(h, h->tl_start[1], values, rows * cols, dev, &d_v); if (r) return r; }
+  double *d_tot = out_total, *d_mean = out_means;
+  if (!dev) {
+    KS_ENSURE(h, t[5], ((size_t)n_groups * (cols + 1)) * 8 + 16);
+    d_tot = as<double>(t[5]);
+    d_mean = d_tot + n_groups;
+  }
+  const uint64_t threads = (uint64_t)n_groups * (cols + 1);
+  k_combine_duplicates<<<(unsigned)((threads + 255) / 256), 256, 0, h->stream>>>(v[cur][0], seg, d_l, d_v, cols, n_groups, d_tot, d_mean);
+  KS_CUDA(h, cudaGetLastError());
+  if (!dev) {
+    { int r = copy_out(h, out_total, d_tot, (size_t)n_groups * 8, false); if (r) return r; }
+    { int r = copy_out(h, out_means, d_mean, (size_t)n_groups * cols * 8, false); if (r) return r; }
+  }
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, false);
+  if (st) return fail(h, st, std::string("ks_combine_duplicates: ") + ks_status_string(st));
+  return (int64_t)n_groups;
+}
+
+}  // extern "C"

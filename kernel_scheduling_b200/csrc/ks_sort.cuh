@@ -1,0 +1,238 @@
+// ks_sort.cuh -- K2: stable least-significant-digit radix sort, one sweep over the data per 8-bit digit.
+//
+// Per pass every CTA takes tiles of 256 x ITEMS keys from a ticket counter (so a tile only ever waits for tiles
+// that already started), ranks the keys of a tile by digit with warp match operations and per-warp digit
+// counters in shared memory, learns the number of equal digits in all earlier tiles by decoupled look-back over
+// a per-tile status array (aggregate / inclusive-prefix words with the flag in the top two bits), stages keys
+// and payload lanes in shared memory in digit order and writes them out in runs.  One histogram kernel in front
+// reads the keys once and counts the digits of every pass.
+//
+// Every wait is bounded (kSpinLimit polls); a wait that runs out sets kErrWait in the error word and the CTA
+// carries on with a wrong offset, so the kernel always terminates and the host reports the failure.
+//
+// The element count may live in device memory (n_dev != nullptr), so a sort can be queued behind the kernel that
+// produces its input without a host round trip.
+#pragma once
+
+#include "ks_common.cuh"
+
+namespace ks {
+
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr uint32_t kFlagAgg = 1u << 30;
+constexpr uint32_t kFlagPrefix = 2u << 30;
+constexpr uint32_t kFlagMask = 3u << 30;
+constexpr uint32_t kCountMask = ~kFlagMask;
+constexpr uint64_t kSortMaxItems = 1ull << 30;
+
+template <typename KeyT, typename ValT, int NV>
+struct SortPassArgs {
+  const KeyT* kin;
+  KeyT* kout;
+  const ValT* vin[NV > 0 ? NV : 1];
+  ValT* vout[NV > 0 ? NV : 1];
+  const uint32_t* n_dev;  // element count in device memory, or nullptr to use n
+  uint32_t n;
+  int shift;
+  int bits;                // 1..8
+  const uint32_t* gbase;   // [256] exclusive digit offsets of this pass
+  uint32_t* lookback;      // [tiles][256], zeroed before the pass
+  uint32_t* ticket;        // zeroed before the pass
+  uint32_t* err;
+};
+
+template <typename KeyT>
+__device__ __forceinline__ uint32_t digit_of(KeyT k, int shift, uint32_t mask) {
+  return (uint32_t)(k >> shift) & mask;
+}
+
+// ---- histogram of every pass's digits in one read of the keys
+template <typename KeyT>
+__global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ keys, const uint32_t* n_dev, uint32_t n, int begin_bit, int end_bit,
+                                                    uint32_t* __restrict__ hist /*[passes][256]*/) {
+  __shared__ uint32_t sh[8 * 256];
+  if (n_dev) n = *n_dev;
+  const int passes = (end_bit - begin_bit + 7) / 8;
+  for (int i = threadIdx.x; i < passes * 256; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const uint32_t stride = gridDim.x * blockDim.x;
+  // whole warps iterate together so that the match below always sees 32 lanes
+  const uint32_t n_round = (n + 31u) & ~31u;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
+    const bool valid = i < n;
+    const KeyT k = valid ? keys[i] : (KeyT)0;
+    for (int p = 0; p < passes; ++p) {
+      const int shift = begin_bit + 8 * p;
+      const int bits = min(8, end_bit - shift);
+      const uint32_t d = digit_of(k, shift, (1u << bits) - 1u);
+      const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? d : 0xFFFFu);
+      if (valid && (same & lanemask_lt()) == 0) atomicAdd(&sh[p * 256 + d], (uint32_t)__popc(same));
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * 256; i += blockDim.x)
+    if (sh[i]) atomicAdd(&hist[i], sh[i]);
+}
+
+// ---- exclusive scan of each pass's 256 counters (one CTA of 256 threads)
+__global__ void __launch_bounds__(256) k_radix_scan_hist(const uint32_t* __restrict__ hist, uint32_t* __restrict__ gbase, int passes) {
+  __shared__ uint32_t warp_tot[8];
+  for (int p = 0; p < passes; ++p) {
+    const uint32_t v = hist[p * 256 + threadIdx.x];
+    const uint32_t inc = warp_incl_scan(v);
+    if (lane_id() == 31) warp_tot[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    uint32_t off = 0;
+    for (uint32_t w = 0; w < (threadIdx.x >> 5); ++w) off += warp_tot[w];
+    gbase[p * 256 + threadIdx.x] = off + inc - v;
+    __syncthreads();
+  }
+}
+
+// ---- one pass
+template <typename KeyT, typename ValT, int NV, int ITEMS>
+__global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassArgs<KeyT, ValT, NV> a) {
+  constexpr int TILE = kSortThreads * ITEMS;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* warp_hist = reinterpret_cast<uint32_t*>(smem_raw);             // [warps][256]
+  uint32_t* s_gpos = warp_hist + kSortWarps * 256;                          // [256] global position of staged index 0 of a digit
+  uint32_t* s_misc = s_gpos + 256;                                          // [16]
+  KeyT* s_keys = reinterpret_cast<KeyT*>(s_misc + 16);                      // [TILE]
+  ValT* s_vals = reinterpret_cast<ValT*>(s_keys + TILE);                    // [TILE]
+
+  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t ntiles = (n + TILE - 1) / TILE;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const uint32_t dmask = (1u << a.bits) - 1u;
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) s_misc[0] = atomicAdd(a.ticket, 1u);
+    for (int i = tid; i < kSortWarps * 256; i += kSortThreads) warp_hist[i] = 0;
+    __syncthreads();
+    const uint32_t tile = s_misc[0];
+    if (tile >= ntiles) break;
+    const uint32_t tile_base = tile * TILE;
+    const uint32_t tile_n = min((uint32_t)TILE, n - tile_base);
+
+    // -- load keys, warp-striped: item i of lane l of warp w sits at w*32*ITEMS + i*32 + l
+    KeyT key[ITEMS];
+    uint32_t rank[ITEMS];
+    const uint32_t wbase = warp * 32 * ITEMS;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      key[i] = li < tile_n ? a.kin[tile_base + li] : (KeyT)0;
+    }
+    // -- rank within the warp, digit by digit in item order (keeps the sort stable)
+    uint32_t* wh = warp_hist + warp * 256;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      const bool valid = li < tile_n;
+      const uint32_t d = digit_of(key[i], a.shift, dmask);
+      const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? d : 0xFFFFu);
+      const uint32_t before = __popc(same & lanemask_lt());
+      uint32_t pre = 0;
+      if (valid) pre = wh[d];
+      __syncwarp();
+      if (valid && before == 0) wh[d] = pre + __popc(same);
+      __syncwarp();
+      rank[i] = pre + before;
+    }
+    __syncthreads();
+
+    // -- per digit (thread d): exclusive offsets of the warps, the tile's count, look-back
+    {
+      const uint32_t d = tid;
+      uint32_t acc = 0;
+#pragma unroll
+      for (int w = 0; w < kSortWarps; ++w) {
+        const uint32_t t = warp_hist[w * 256 + d];
+        warp_hist[w * 256 + d] = acc;
+        acc += t;
+      }
+      uint32_t excl = 0;
+      volatile uint32_t* lb = a.lookback + (size_t)tile * 256 + d;
+      if (tile == 0) {
+        *lb = acc | kFlagPrefix;
+      } else {
+        *lb = acc | kFlagAgg;
+        uint32_t t = tile - 1, spins = 0;
+        while (true) {
+          const uint32_t v = ld_volatile_u32(a.lookback + (size_t)t * 256 + d);
+          const uint32_t f = v & kFlagMask;
+          if (f == 0) {
+            if (++spins > kSpinLimit) { atomicOr(a.err, kErrWait); break; }
+            __nanosleep(20);
+            continue;
+          }
+          excl += v & kCountMask;
+          if (f == kFlagPrefix || t == 0) break;
+          --t;
+        }
+        *lb = ((excl + acc) & kCountMask) | kFlagPrefix;
+      }
+      // exclusive scan of the tile counts over the digits -> where each digit starts in the staging buffer
+      const uint32_t inc = warp_incl_scan(acc);
+      if (lane == 31) s_misc[1 + warp] = inc;
+      __syncthreads();
+      uint32_t off = 0;
+      for (uint32_t w = 0; w < warp; ++w) off += s_misc[1 + w];
+      const uint32_t dstart = off + inc - acc;
+      s_gpos[d] = a.gbase[d] + excl - dstart;
+      // fold the digit start into the warp offsets so the item loop needs one lookup
+#pragma unroll
+      for (int w = 0; w < kSortWarps; ++w) warp_hist[w * 256 + d] += dstart;
+    }
+    __syncthreads();
+
+    // -- stage keys in digit order
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      if (li < tile_n) {
+        const uint32_t d = digit_of(key[i], a.shift, dmask);
+        rank[i] += wh[d];
+        s_keys[rank[i]] = key[i];
+      }
+    }
+    __syncthreads();
+    uint32_t outpos[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t si = i * kSortThreads + tid;
+      if (si < tile_n) {
+        const KeyT k = s_keys[si];
+        outpos[i] = s_gpos[digit_of(k, a.shift, dmask)] + si;
+        a.kout[outpos[i]] = k;
+      }
+    }
+    // -- payload lanes through the same permutation
+    if constexpr (NV > 0) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const uint32_t li = wbase + i * 32 + lane;
+          if (li < tile_n) s_vals[rank[i]] = a.vin[v][tile_base + li];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const uint32_t si = i * kSortThreads + tid;
+          if (si < tile_n) a.vout[v][outpos[i]] = s_vals[si];
+        }
+      }
+    }
+  }
+}
+
+template <typename KeyT, typename ValT, int ITEMS>
+constexpr size_t sort_smem_bytes() {
+  return (kSortWarps * 256 + 256 + 16) * sizeof(uint32_t) + (size_t)kSortThreads * ITEMS * (sizeof(KeyT) + sizeof(ValT));
+}
+
+}  // namespace ks

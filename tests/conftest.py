@@ -1,0 +1,22 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def builder():
+    """One library handle for the GPU tests; fails loudly if the CUDA library is missing."""
+    from kernel_scheduling_b200.pair_table import PairTableBuilder
+
+    b = PairTableBuilder(device=0)
+    yield b
+    b.close()

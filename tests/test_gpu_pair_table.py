@@ -1,0 +1,104 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle on seeded traces."""
+import numpy as np
+import pytest
+
+from kernel_scheduling_b200 import trace
+from kernel_scheduling_b200.records import RECORD_DTYPE, pack_records
+from oracle import pair_table_oracle as O
+from tests.helpers import assert_tables_match
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("cfg,n", [("c1", 200_000), ("c2", 400_000), ("c3", 300_000), ("c4", 300_000)])
+@pytest.mark.parametrize("ordered", [True, False])
+def test_pair_table_matches_oracle(builder, cfg, n, ordered):
+    rec = trace.generate(trace.config(cfg, n))
+    if not ordered:
+        rec = trace.shuffled(rec)
+    keys, pairs = builder.build(rec, time_ordered=ordered)
+    okeys, opairs = O.build_pair_table(rec)
+    assert_tables_match(keys, pairs, okeys, opairs)
+    assert builder.info["n_pairs"] == int(opairs["count"].sum())
+    assert builder.info["was_time_ordered"] == int(ordered)
+
+
+def test_type_keys(builder):
+    rec = trace.generate(trace.config("c1", 50_000))
+    keys, pairs = builder.build(rec, time_ordered=True, key_type=True)
+    okeys, opairs = O.build_pair_table(rec, key_mode=O.KEY_TYPE)
+    assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_interleaved_solo_and_missing_baselines(builder):
+    spec = trace.config("c1", 60_000)
+    spec.solo_fraction = 0.02  # many keys end up without a solo launch: NaN sides
+    rec = trace.generate(spec, interleave_solo=True)
+    keys, pairs = builder.build(rec, time_ordered=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert (opairs["flags"] != 3).any() and (opairs["flags"] == 3).any()
+    assert_tables_match(keys, pairs, okeys, opairs)
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 31, 32, 33, 255, 256, 257, 1023, 1024, 1025, 2049])
+def test_small_and_ragged_sizes(builder, n):
+    rec = trace.generate(trace.config("c1", max(n, 1)))[:n]
+    keys, pairs = builder.build(rec, time_ordered=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_brute_force_agreement_with_ties_and_zero_durations(builder):
+    rng = np.random.default_rng(5)
+    n = 700
+    start = np.sort(rng.integers(1000, 1400, n)).astype(np.uint64)  # many equal start_ns
+    dur = rng.integers(0, 40, n).astype(np.uint64)  # including zero-length launches
+    tenant = rng.integers(0, 3, n)
+    solo = rng.random(n) < 0.3
+    name = rng.integers(0, 6, n)
+    rec = pack_records(name, np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, solo, start, start + dur)
+    keys, pairs = builder.build(rec)
+    okeys, opairs = O.build_pair_table_bruteforce(rec)
+    bkeys, bpairs = O.build_pair_table(rec)
+    assert_tables_match(keys, pairs, bkeys, bpairs)
+    for c in ("key_a", "key_b", "count", "median_a", "median_b", "min_a", "max_b", "efficiency"):
+        assert np.array_equal(pairs[c], opairs[c], equal_nan=True), c
+
+
+def test_hot_pair_large_segments(builder):
+    # two keys only: every pair lands in one row, so the CTA-per-row selection path carries the medians
+    rng = np.random.default_rng(9)
+    n = 120_000
+    tenant = (np.arange(n) % 2)
+    dur = rng.integers(500, 5000, n).astype(np.uint64)
+    start = (np.cumsum(rng.integers(100, 1500, n))).astype(np.uint64)
+    solo = np.zeros(n, bool)
+    solo[:2000] = True
+    rec = pack_records(tenant, np.ones((n, 3)), np.ones((n, 3)) * 64, np.zeros(n), tenant, solo, start, start + dur)
+    keys, pairs = builder.build(rec)
+    okeys, opairs = O.build_pair_table(rec)
+    assert len(opairs["count"]) == 1 and opairs["count"][0] > 50_000
+    assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_error_statuses(builder):
+    from kernel_scheduling_b200 import _lib
+
+    rec = trace.generate(trace.config("c1", 5000))
+    bad = rec.copy()
+    bad["end_ns"][17] = bad["start_ns"][17] - 1
+    with pytest.raises(_lib.KsError) as e:
+        builder.build(bad)
+    assert e.value.status == _lib.ERR_RECORD
+    long = rec.copy()
+    long["end_ns"][5] = long["start_ns"][5] + (1 << 31)
+    with pytest.raises(_lib.KsError) as e:
+        builder.build(long)
+    assert e.value.status == _lib.ERR_RECORD
+    with pytest.raises(_lib.KsError) as e:
+        builder.build(trace.shuffled(rec), time_ordered=True)
+    assert e.value.status == _lib.ERR_NOT_ORDERED
+    # the handle stays usable after an error
+    keys, pairs = builder.build(rec, time_ordered=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert_tables_match(keys, pairs, okeys, opairs)
