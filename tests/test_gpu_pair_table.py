@@ -42,7 +42,7 @@ def test_interleaved_solo_and_missing_baselines(builder):
 
 @pytest.mark.parametrize("n", [0, 1, 2, 31, 32, 33, 255, 256, 257, 1023, 1024, 1025, 2049])
 def test_small_and_ragged_sizes(builder, n):
-    rec = trace.generate(trace.config("c1", max(n, 1)))[:n]
+    rec = trace.generate(trace.config("c1", 4096), interleave_solo=True)[:n]
     keys, pairs = builder.build(rec, time_ordered=True)
     okeys, opairs = O.build_pair_table(rec)
     assert_tables_match(keys, pairs, okeys, opairs)

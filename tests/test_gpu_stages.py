@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("n", [0, 1, 255, 256, 257, 100_003])
 @pytest.mark.parametrize("key_type", [False, True])
 def test_hash_keys(builder, n, key_type):
-    rec = trace.generate(trace.config("c3", max(n, 1)))[:n]
+    rec = trace.generate(trace.config("c3", max(n, 4096)))[:n]
     got = builder.hash_keys(rec, key_type=key_type)
     assert np.array_equal(got, O.kernel_keys(rec, O.KEY_TYPE if key_type else O.KEY_SHAPE))
 
