@@ -109,6 +109,8 @@ void ks_destroy(ks_handle* h);
 const char* ks_last_error(ks_handle* h);
 /* the stream the handle launches on (for timing with events) */
 void* ks_stream(ks_handle* h);
+/* kernels of this library launched through the handle so far (cumulative) */
+uint64_t ks_launch_count(ks_handle* h);
 
 /* ---- the whole path.  Stands where the reference runs its offline post-processing over the agents' logs
  * (scheduler/postprocess.py:8-41 and the absent make_pair_eff.py named at scheduler_daemon.cpp:5,193,848).

@@ -49,10 +49,12 @@ struct ks_handle {
   DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
   DevBuf skey[2], lane[2][kLanes];
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
+  DevBuf large_rows, chunk_row, chunk_idx, large_hist;
   DevBuf tmp[6];
 
   // results of the last ks_build_table
   uint64_t n_pair_rows = 0, n_key_rows = 0;
+  uint64_t launches = 0;  // kernels launched so far (cumulative)
   cudaEvent_t ev[12]{};
 };
 
@@ -135,6 +137,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
   const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 8);
   k_radix_hist<KeyT><<<hist_grid, 256, 0, h->stream>>>(keys[0], n_dev, (uint32_t)n, begin_bit, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
+  h->launches += 2 + passes;
   auto kern = k_onesweep_pass<KeyT, ValT, NV, ITEMS>;
   constexpr size_t smem = sort_smem_bytes<KeyT, ValT, ITEMS>();
   static bool attr_set = false;
@@ -221,6 +224,7 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
   const uint64_t ntiles = (n + kDecodeThreads - 1) / kDecodeThreads;
   const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 3);
   k_decode_hash<<<grid, kDecodeThreads, decode_smem_bytes(), h->stream>>>(a);
+  ++h->launches;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -250,6 +254,7 @@ int run_dict(ks_handle* h) {
   k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
   k_dict_rank<<<dim3((kMaxKeys + 255) / 256, kRankSplit), 256, 0, h->stream>>>(d);
   k_dict_place<<<(kMaxKeys + 255) / 256, 256, 0, h->stream>>>(d);
+  h->launches += 3;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -295,6 +300,49 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
   const unsigned grid = (unsigned)((n + kJoinTile - 1) / kJoinTile);
   if (idx_a) k_join<true><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
   else k_join<false><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
+// K4 core: integer statistics of every row (three size classes, see ks_segstats.cuh)
+int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n_values, uint32_t max_rows) {
+  const uint32_t max_large = (uint32_t)(n_values / kMidMax) + 1;
+  const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
+  KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
+  KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
+  KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
+  KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
+  KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
+  KS_ENSURE(h, h->large_hist, (size_t)max_large * 2 * kLanes * 256 * 4);
+  SegArgs s{};
+  for (int l = 0; l < kLanes; ++l) s.lane[l] = lanes[l];
+  s.n_lanes = n_lanes;
+  s.row_start = as<uint32_t>(h->row_start);
+  s.n_rows_dev = &h->d_ctl->n_rows;
+  s.max_rows = max_rows;
+  s.stats = as<RowStats>(h->stats);
+  s.mid_rows = as<uint32_t>(h->big_rows);
+  s.large = as<LargeRow>(h->large_rows);
+  s.chunk_row = as<uint32_t>(h->chunk_row);
+  s.chunk_idx = as<uint32_t>(h->chunk_idx);
+  s.large_hist = as<uint32_t>(h->large_hist);
+  s.max_large = max_large;
+  s.max_chunks = max_chunks;
+  s.ctl = h->d_ctl;
+  const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 7) / 8, (uint32_t)h->sm_count * 16));
+  k_seg_classify<<<cgrid, 256, 0, h->stream>>>(s);
+  k_seg_mid<<<h->sm_count * 8, 256, 0, h->stream>>>(s);
+  const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 8));
+  k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
+  k_segL_init<<<(max_large * 2 * kLanes + 255) / 256, 256, 0, h->stream>>>(s);
+  for (int r = 0; r < kLargeRounds; ++r) {
+    s.round = r;
+    k_segL_hist<<<lgrid, 256, 0, h->stream>>>(s);
+    k_segL_resolve<<<(int)std::min<uint32_t>(max_large, (uint32_t)h->sm_count * 8), 2 * kLanes * 32, 0, h->stream>>>(s);
+  }
+  k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
+  h->launches += 5 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -305,8 +353,6 @@ int run_rows_and_stats(ks_handle* h, const uint32_t* skey, const uint32_t* const
   KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
   KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
   KS_ENSURE(h, h->row_key, ((size_t)max_rows + 2) * 4);
-  KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
-  KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
   RowsArgs r{};
   r.skey = skey;
   r.n_dev = nullptr;
@@ -322,20 +368,9 @@ int run_rows_and_stats(ks_handle* h, const uint32_t* skey, const uint32_t* const
   k_rows_count<<<grid, 256, 0, h->stream>>>(r);
   k_rows_scan<<<1, 1024, 0, h->stream>>>(r);
   k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
-  SegArgs s{};
-  for (int l = 0; l < kLanes; ++l) s.lane[l] = lanes[l];
-  s.n_lanes = n_lanes;
-  s.row_start = as<uint32_t>(h->row_start);
-  s.n_rows_dev = &h->d_ctl->n_rows;
-  s.max_rows = max_rows;
-  s.stats = as<RowStats>(h->stats);
-  s.big_rows = as<uint32_t>(h->big_rows);
-  s.ctl = h->d_ctl;
-  const int sgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 7) / 8, (uint32_t)h->sm_count * 16));
-  k_seg_small<<<sgrid, 256, 0, h->stream>>>(s);
-  k_seg_big<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+  h->launches += 3;
   KS_CUDA(h, cudaGetLastError());
-  return 0;
+  return run_segment_stats(h, lanes, n_lanes, n, max_rows);
 }
 
 __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start, uint32_t n_rows, unsigned long long* out) {
@@ -439,7 +474,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->skey[0], &h->skey[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) fr(h->lane[s][l].p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
@@ -449,6 +484,7 @@ void ks_destroy(ks_handle* h) {
 
 const char* ks_last_error(ks_handle* h) { return h ? h->last_error.c_str() : g_null_error.c_str(); }
 void* ks_stream(ks_handle* h) { return h ? reinterpret_cast<void*>(h->stream) : nullptr; }
+uint64_t ks_launch_count(ks_handle* h) { return h ? h->launches : 0; }
 
 // ---------------------------------------------------------------------------------------------------------
 int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info) {
@@ -503,8 +539,10 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     s.capacity = cap;
     s.ctl = h->d_ctl;
     k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+    ++h->launches;
     if (attempt == 0) cudaEventRecord(ev[5], h->stream);
     { int r = run_join(h, tl, n, cap, nullptr, nullptr); if (r) return r; }
+    cudaEventRecord(ev[6], h->stream);
     { int r = read_ctl(h); if (r) return r; }
     const int st = status_of_err(h->h_ctl->err, assume_ordered);
     if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
@@ -516,7 +554,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     int r = ensure_samples(h, cap);
     if (r) return r;
   }
-  cudaEventRecord(ev[6], h->stream);
+  cudaEventRecord(ev[10], h->stream);
   const uint64_t nk = h->h_ctl->n_keys, n_solo = h->h_ctl->n_solo;
 
   // K2: group the samples by sort key
@@ -551,6 +589,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   f.ctl = h->d_ctl;
   if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
   k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
+  h->launches += nk ? 2 : 1;
   KS_CUDA(h, cudaGetLastError());
   cudaEventRecord(ev[9], h->stream);
   { int r = read_ctl(h); if (r) return r; }
@@ -576,7 +615,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     info->ms_order = ev_ms(ev[2], ev[3]);
     info->ms_dict = ev_ms(ev[3], ev[5]);
     info->ms_join = ev_ms(ev[5], ev[6]);
-    info->ms_sort = ev_ms(ev[6], ev[7]);
+    info->ms_sort = ev_ms(ev[10], ev[7]);
     info->ms_reduce = ev_ms(ev[7], ev[8]);
     info->ms_finalize = ev_ms(ev[8], ev[9]);
     info->ms_total = ev_ms(ev[0], ev[9]);
@@ -753,24 +792,12 @@ int64_t ks_segment_stats(ks_handle* h, const uint32_t* values, const uint64_t* o
   { int r = reset_run(h); if (r) return r; }
   const uint32_t rows = (uint32_t)n_segments;
   KS_ENSURE(h, h->row_start, ((size_t)rows + 2) * 4);
-  KS_ENSURE(h, h->stats, ((size_t)rows + 1) * sizeof(RowStats));
-  KS_ENSURE(h, h->big_rows, ((size_t)rows + 1) * 4);
   KS_ENSURE(h, h->tmp[2], (size_t)rows * 48);
   k_offsets_to_u32<<<(rows + 1 + 255) / 256, 256, 0, h->stream>>>(d_off, rows + 1, as<uint32_t>(h->row_start));
   h->h_ctl->n_rows = rows;
   KS_CUDA(h, cudaMemcpyAsync(&h->d_ctl->n_rows, &h->h_ctl->n_rows, 4, cudaMemcpyHostToDevice, h->stream));
-  SegArgs s{};
-  s.lane[0] = d_val;
-  s.n_lanes = 1;
-  s.row_start = as<uint32_t>(h->row_start);
-  s.n_rows_dev = &h->d_ctl->n_rows;
-  s.max_rows = rows;
-  s.stats = as<RowStats>(h->stats);
-  s.big_rows = as<uint32_t>(h->big_rows);
-  s.ctl = h->d_ctl;
-  const int sgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((rows + 7) / 8, (uint32_t)h->sm_count * 16));
-  k_seg_small<<<sgrid, 256, 0, h->stream>>>(s);
-  k_seg_big<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+  const uint32_t* lanes1[kLanes] = {d_val, nullptr, nullptr};
+  { int r = run_segment_stats(h, lanes1, 1, n_values, rows); if (r) return r; }
   unsigned long long* d_out = dev ? reinterpret_cast<unsigned long long*>(out) : as<unsigned long long>(h->tmp[2]);
   k_stats_to_u64<<<(rows + 255) / 256, 256, 0, h->stream>>>(as<RowStats>(h->stats), as<uint32_t>(h->row_start), rows, d_out);
   KS_CUDA(h, cudaGetLastError());

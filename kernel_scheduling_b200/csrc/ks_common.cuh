@@ -47,7 +47,8 @@ struct Control {
   unsigned long long max_start;
   unsigned long long scratch0;
   unsigned long long batches_both;  // ks_count_batches
-  unsigned long long pad[3];
+  unsigned long long pad[4];         // large-row selection: unresolved states per round
+  unsigned long long pad2[3];
 };
 
 // ---------------------------------------------------------------------------------------------------------

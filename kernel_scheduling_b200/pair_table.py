@@ -43,6 +43,10 @@ class PairTableBuilder:
     def stream(self) -> int:
         return int(self._lib.ks_stream(self._h) or 0)
 
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.ks_launch_count(self._h))
+
     def _check(self, r, what):
         if r < 0:
             raise _lib.KsError(int(-r), f"{what}: {self._lib.ks_last_error(self._h).decode()}")
