@@ -49,7 +49,7 @@ struct ks_handle {
   DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
   DevBuf skey[2], lane[2][kLanes];
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
-  DevBuf large_rows, chunk_row, chunk_idx, large_hist;
+  DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows;
   DevBuf tmp[6];
 
   // results of the last ks_build_table
@@ -134,7 +134,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
   uint32_t* hist = as<uint32_t>(h->hist);
   uint32_t* gbase = hist + 8 * 256;
   KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
-  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 8);
+  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 64 - 1) / (256 * 64), (uint64_t)h->sm_count * 2);
   k_radix_hist<KeyT><<<hist_grid, 256, 0, h->stream>>>(keys[0], n_dev, (uint32_t)n, begin_bit, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
@@ -311,6 +311,7 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
   const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
   KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
   KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
+  KS_ENSURE(h, h->small_rows, ((size_t)max_rows + 1) * 4);
   KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
   KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
@@ -323,6 +324,7 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
   s.max_rows = max_rows;
   s.stats = as<RowStats>(h->stats);
   s.mid_rows = as<uint32_t>(h->big_rows);
+  s.small_rows = as<uint32_t>(h->small_rows);
   s.large = as<LargeRow>(h->large_rows);
   s.chunk_row = as<uint32_t>(h->chunk_row);
   s.chunk_idx = as<uint32_t>(h->chunk_idx);
@@ -330,8 +332,9 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
   s.max_large = max_large;
   s.max_chunks = max_chunks;
   s.ctl = h->d_ctl;
-  const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 7) / 8, (uint32_t)h->sm_count * 16));
+  const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 255) / 256, (uint32_t)h->sm_count * 8));
   k_seg_classify<<<cgrid, 256, 0, h->stream>>>(s);
+  k_seg_small<<<h->sm_count * 8, 256, 0, h->stream>>>(s);
   k_seg_mid<<<h->sm_count * 8, 256, 0, h->stream>>>(s);
   const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 8));
   k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
@@ -342,7 +345,7 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
     k_segL_resolve<<<(int)std::min<uint32_t>(max_large, (uint32_t)h->sm_count * 8), 2 * kLanes * 32, 0, h->stream>>>(s);
   }
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
-  h->launches += 5 + 2 * kLargeRounds;
+  h->launches += 6 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -474,7 +477,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->skey[0], &h->skey[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) fr(h->lane[s][l].p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);

@@ -48,7 +48,9 @@ struct Control {
   unsigned long long scratch0;
   unsigned long long batches_both;  // ks_count_batches
   unsigned long long pad[4];         // large-row selection: unresolved states per round
-  unsigned long long pad2[3];
+  uint32_t n_small;      // rows handed to the warp-per-row kernel
+  uint32_t pad32;
+  unsigned long long pad2[2];
 };
 
 // ---------------------------------------------------------------------------------------------------------

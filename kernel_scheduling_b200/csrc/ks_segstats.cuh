@@ -4,8 +4,9 @@
 // Rows differ in size by six orders of magnitude (most key pairs meet a few times, the hottest pair owns percent of
 // all samples), so three size classes share the work:
 //
-//   small  (n <= 32)      k_seg_classify handles them in place: one warp per row, shuffle reductions and a 32-wide
-//                         bitonic network; larger rows are pushed onto the mid / large work lists.
+//   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
+//                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
+//   small  (n <= 32)      k_seg_small: one warp per row, shuffle reductions and a 32-wide bitonic network.
 //   mid    (n <= 2048)    k_seg_mid: one warp per (row, lane).  Reductions, then a radix select over (value - min):
 //                         only the bits in which the row's values can differ are walked, 8 per round, with a
 //                         256-bin histogram in the warp's own shared memory -- no block-wide barrier anywhere.
@@ -50,6 +51,7 @@ struct SegArgs {
   const uint32_t* n_rows_dev;
   uint32_t max_rows;
   RowStats* stats;
+  uint32_t* small_rows;    // [max_rows]
   uint32_t* mid_rows;      // [max_rows]
   LargeRow* large;         // [max_large]
   uint32_t* chunk_row;     // [max_chunks] index into large[]
@@ -106,47 +108,75 @@ __device__ __forceinline__ void warp_pick_bin(const uint32_t* bins, uint32_t k, 
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// One thread per row.  Rows of up to four samples (most rows of a Zipf-distributed trace) are finished right here with
+// a five-comparator sorting network in registers; the others go to the work list of their size class.
+__device__ __forceinline__ void push_row(uint32_t* list, uint32_t* counter, bool mine, uint32_t row) {
+  const uint32_t ballot = __ballot_sync(__activemask(), mine);
+  if (!mine) return;
+  const uint32_t first = __ffs(ballot) - 1;
+  uint32_t base = 0;
+  if (lane_id() == first) base = atomicAdd(counter, (uint32_t)__popc(ballot));
+  base = __shfl_sync(ballot, base, first);
+  list[base + __popc(ballot & lanemask_lt())] = row;
+}
+
 __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
   const uint32_t n_rows = min(*a.n_rows_dev, a.max_rows);
-  const uint32_t lane = lane_id();
-  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-  for (uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows; row += warps) {
-    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+  const uint32_t n_round = (n_rows + 31u) & ~31u;  // whole warps take part in the list pushes
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n_round; row += gridDim.x * blockDim.x) {
+    const bool valid = row < n_rows;
+    const uint32_t s = valid ? a.row_start[row] : 0, cnt = valid ? a.row_start[row + 1] - s : 0;
+    push_row(a.small_rows, &a.ctl->n_small, valid && cnt > 4 && cnt <= kSmallSegment, row);
+    push_row(a.mid_rows, &a.ctl->n_big, valid && cnt > kSmallSegment && cnt <= kMidMax, row);
+    if (!valid) continue;
     RowStats* st = a.stats + row;
     if (cnt == 0) {  // only the stage API can hand in an empty segment
-      if (lane < (uint32_t)a.n_lanes) { st->sum[lane] = 0; st->mn[lane] = 0; st->mx[lane] = 0; st->lo[lane] = 0; st->hi[lane] = 0; }
-      continue;
-    }
-    if (cnt > kMidMax) {
-      uint32_t l = 0, cbase = 0;
+      for (int l = 0; l < a.n_lanes; ++l) { st->sum[l] = 0; st->mn[l] = 0; st->mx[l] = 0; st->lo[l] = 0; st->hi[l] = 0; }
+    } else if (cnt <= 4) {
+      for (int l = 0; l < a.n_lanes; ++l) {
+        const uint32_t* v = a.lane[l] + s;
+        uint32_t x0 = v[0], x1 = cnt > 1 ? v[1] : 0xFFFFFFFFu, x2 = cnt > 2 ? v[2] : 0xFFFFFFFFu, x3 = cnt > 3 ? v[3] : 0xFFFFFFFFu;
+        const unsigned long long sum = (unsigned long long)x0 + (cnt > 1 ? x1 : 0u) + (cnt > 2 ? x2 : 0u) + (cnt > 3 ? x3 : 0u);
+        uint32_t t;
+#define KS_CSWAP(p, q) t = min(p, q); q = max(p, q); p = t;
+        KS_CSWAP(x0, x1) KS_CSWAP(x2, x3) KS_CSWAP(x0, x2) KS_CSWAP(x1, x3) KS_CSWAP(x1, x2)
+#undef KS_CSWAP
+        const uint32_t srt[4] = {x0, x1, x2, x3};
+        st->sum[l] = sum;
+        st->mn[l] = x0;
+        st->mx[l] = srt[cnt - 1];
+        st->lo[l] = srt[(cnt - 1) >> 1];
+        st->hi[l] = srt[cnt >> 1];
+      }
+    } else if (cnt > kMidMax) {
       const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
-      if (lane == 0) {
-        l = atomicAdd(&a.ctl->ticket, 1u);
-        cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
-      }
-      l = __shfl_sync(0xFFFFFFFFu, l, 0);
-      cbase = __shfl_sync(0xFFFFFFFFu, cbase, 0);
-      if (l >= a.max_large || cbase + nch > a.max_chunks) { if (lane == 0) atomicOr(&a.ctl->err, kErrTooLarge); continue; }
-      if (lane == 0) {
-        LargeRow* L = a.large + l;
-        L->row = row; L->start = s; L->cnt = cnt;
-        for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
-      }
-      for (uint32_t c = lane; c < nch; c += 32) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
-      for (uint32_t i = lane; i < 2 * kLanes * 256; i += 32) a.large_hist[(size_t)l * 2 * kLanes * 256 + i] = 0;
-      continue;
+      const uint32_t l = atomicAdd(&a.ctl->ticket, 1u);
+      const uint32_t cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
+      if (l >= a.max_large || cbase + nch > a.max_chunks) { atomicOr(&a.ctl->err, kErrTooLarge); continue; }
+      LargeRow* L = a.large + l;
+      L->row = row; L->start = s; L->cnt = cnt;
+      for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
+      for (uint32_t c = 0; c < nch; ++c) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
     }
-    if (cnt > kSmallSegment) {
-      if (lane == 0) a.mid_rows[atomicAdd(&a.ctl->n_big, 1u)] = row;
-      continue;
-    }
+  }
+}
+
+// one warp per row of 5..32 samples: shuffle reductions and a 32-wide bitonic network
+__global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
+  const uint32_t n_small = min(a.ctl->n_small, a.max_rows);
+  const uint32_t lane = lane_id();
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+  for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_small; t += warps) {
+    const uint32_t row = a.small_rows[t];
+    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+    RowStats* st = a.stats + row;
     for (int l = 0; l < a.n_lanes; ++l) {
       const bool have = lane < cnt;
       const uint32_t v = have ? a.lane[l][s + lane] : 0u;
       const unsigned long long sum = warp_sum64(v);
       const uint32_t mx = warp_max(v);
-      const uint32_t mn = warp_min(have ? v : 0xFFFFFFFFu);
       const uint32_t sorted = bitonic_sort32(have ? v : 0xFFFFFFFFu);
+      const uint32_t mn = __shfl_sync(0xFFFFFFFFu, sorted, 0);
       const uint32_t lo = __shfl_sync(0xFFFFFFFFu, sorted, (cnt - 1) >> 1);
       const uint32_t hi = __shfl_sync(0xFFFFFFFFu, sorted, cnt >> 1);
       if (lane == 0) { st->sum[l] = sum; st->mn[l] = mn; st->mx[l] = mx; st->lo[l] = lo; st->hi[l] = hi; }
@@ -264,6 +294,8 @@ __global__ void __launch_bounds__(256) k_segL_init(const SegArgs a) {
   if (t >= n_large * 2 * kLanes) return;
   LargeRow* L = a.large + t / (2 * kLanes);
   const int v = (int)(t % (2 * kLanes)), l = v >> 1, which = v & 1;
+  uint32_t* gh = a.large_hist + (size_t)t * 256;
+  for (int i = 0; i < 256; ++i) gh[i] = 0;
   if (l >= a.n_lanes) { L->hi_bit[v] = -1; L->prefix[v] = 0; L->k[v] = 0; return; }
   L->prefix[v] = 0;
   L->k[v] = which ? (L->cnt >> 1) : ((L->cnt - 1) >> 1);
