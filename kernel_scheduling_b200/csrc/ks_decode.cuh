@@ -19,9 +19,9 @@
 namespace ks {
 
 constexpr int kDecodeThreads = 256;
-constexpr int kDecodeStages = 3;
+constexpr int kDecodeStages = 2;
 constexpr int kDecodeTileBytes = kDecodeThreads * 48;
-constexpr uint32_t kCtaCountSlots = 2048;  // per-CTA launch-count cache (open addressing on the dictionary slot)
+constexpr uint32_t kCtaCountSlots = 1024;  // per-CTA launch-count cache (open addressing on the dictionary slot)
 
 struct DecodeArgs {
   const unsigned char* records;
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
       }
       // launch counts: CTA-local cache first, global atomics when the cache is crowded
       const uint32_t c_all = __popc(same), c_solo = __popc(same & solo_ballot);
-      uint32_t h = (slot * 2654435761u) >> (32 - 11);
+      uint32_t h = (slot * 2654435761u) >> (32 - 10);
       bool cached = false;
       for (int probe = 0; probe < 8; ++probe) {
         const uint32_t old = atomicCAS(&cc_slot[h], 0u, slot + 1);

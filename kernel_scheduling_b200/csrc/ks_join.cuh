@@ -5,13 +5,13 @@
 // start_i < end_j (only false for a zero-length j that starts with i).  Every unordered pair is found once, from its
 // earlier member.
 //
-// A CTA stages a tile of the timeline plus a look-ahead window in shared memory (dictionary slots already translated
-// to dense key ids).  Each thread finds, by binary search over the staged start times, where its launches' runs of
-// candidates end; an exclusive scan of the run lengths then lets the CTA walk the CANDIDATES, not the launches, in
-// strides of the block size (a load-balanced search: the owner of candidate q is found by binary search over the
-// scanned run offsets), so a 150 us kernel that overlaps forty short ones costs forty lanes one step instead of one
-// lane forty steps.  Valid candidates are compacted with ballots, the CTA reserves a contiguous range of the sample
-// stream with one counter update, and consecutive lanes write consecutive samples:
+// A CTA stages a tile of the timeline plus a look-ahead window in shared memory as separate start / duration / info
+// arrays (dictionary slots already translated to dense key ids).  Consecutive lanes take consecutive launches and
+// find where their run of candidates ends by a galloping search (most runs are empty or a few entries long).  An
+// exclusive scan of the run lengths numbers the CANDIDATES of the tile; every thread then takes an equal, contiguous
+// share of the candidates (merge-path style: one binary search for the owner of its first candidate, then a walk),
+// so a 150 us kernel that overlaps forty short ones is spread over many lanes.  Pass 0 counts the valid candidates,
+// one scan and one counter update reserve a contiguous range of the sample stream, pass 1 writes one sample per pair:
 //     sort key = n_keys + kid_a * n_keys + kid_b       (a = the launch of the lower tenant)
 //     lane 0 = duration of a, lane 1 = duration of b, lane 2 = max(end) - min(start)
 // Runs that leave the staged window (a launch longer than the look-ahead) are finished by their owner from global
@@ -26,6 +26,7 @@ constexpr int kJoinThreads = 256;
 constexpr int kJoinPerThread = 4;
 constexpr int kJoinTile = kJoinThreads * kJoinPerThread;  // 1024 launches per CTA
 constexpr int kJoinAhead = 512;                           // look-ahead window
+constexpr int kJoinWindow = kJoinTile + kJoinAhead;
 
 struct JoinArgs {
   const unsigned long long* tl_start;
@@ -48,13 +49,16 @@ struct JoinEntry {
   uint32_t info;  // kid | tenant << 16 | solo << 24
 };
 
+__device__ __forceinline__ uint32_t join_info(const JoinArgs& a, uint32_t meta) {
+  return __ldg(a.kid_of_slot + (meta & kMetaSlotMask)) | ((meta >> 24) << 16) | (((meta >> 23) & 1u) << 24);
+}
+
 __device__ __forceinline__ JoinEntry join_entry(const JoinArgs& a, uint64_t j) {
   JoinEntry e;
   e.start = a.tl_start[j];
   const unsigned long long dm = a.tl_dm[j];
   e.dur = (uint32_t)dm;
-  const uint32_t meta = (uint32_t)(dm >> 32);
-  e.info = __ldg(a.kid_of_slot + (meta & kMetaSlotMask)) | ((meta >> 24) << 16) | (((meta >> 23) & 1u) << 24);
+  e.info = join_info(a, (uint32_t)(dm >> 32));
   return e;
 }
 
@@ -82,47 +86,61 @@ __device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long 
 
 template <bool kIndexOutput>
 __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  JoinEntry* win = reinterpret_cast<JoinEntry*>(smem_raw);                    // [kJoinTile + kJoinAhead]
-  uint32_t* run_off = reinterpret_cast<uint32_t*>(win + kJoinTile + kJoinAhead);  // [kJoinTile + 1] exclusive run offsets
+  __shared__ unsigned long long s_start[kJoinWindow];
+  __shared__ uint32_t s_dur[kJoinWindow];
+  __shared__ uint32_t s_info[kJoinWindow];
+  __shared__ __align__(16) uint32_t run_off[kJoinTile + 4];  // run lengths, then their exclusive scan
   __shared__ uint32_t warp_tot[kJoinThreads / 32];
+  __shared__ uint32_t warp_tot2[kJoinThreads / 32];
   __shared__ unsigned long long s_base;
   __shared__ uint32_t s_spill;
 
   const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
   const uint64_t t0 = (uint64_t)blockIdx.x * kJoinTile;
   if (t0 >= a.n) return;
-  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, a.n - t0);                 // launches of this tile
-  const uint32_t wn = (uint32_t)min((uint64_t)(kJoinTile + kJoinAhead), a.n - t0);  // staged entries
-  for (uint32_t i = tid; i < wn; i += kJoinThreads) win[i] = join_entry(a, t0 + i);
+  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, a.n - t0);    // launches of this tile
+  const uint32_t wn = (uint32_t)min((uint64_t)kJoinWindow, a.n - t0);  // staged entries
+  for (uint32_t i = tid; i < wn; i += kJoinThreads) {
+    s_start[i] = a.tl_start[t0 + i];
+    const unsigned long long dm = a.tl_dm[t0 + i];
+    s_dur[i] = (uint32_t)dm;
+    s_info[i] = join_info(a, (uint32_t)(dm >> 32));
+  }
   if (tid == 0) s_spill = 0;
   __syncthreads();
   const uint32_t nk = a.ctl->n_keys;
+  auto entry = [&](uint32_t i) -> JoinEntry { JoinEntry e; e.start = s_start[i]; e.dur = s_dur[i]; e.info = s_info[i]; return e; };
 
-  // ---- run length of every launch of the tile inside the window: candidates (li, li + 1 .. hi - 1)
-  // thread t owns launches 4t .. 4t+3 so that the scan below is a plain blocked scan
-  uint32_t len[kJoinPerThread], mine = 0;
+  // ---- run length of every launch of the tile inside the window (consecutive lanes, consecutive launches)
   bool spills = false;
 #pragma unroll
   for (int k = 0; k < kJoinPerThread; ++k) {
-    const uint32_t li = tid * kJoinPerThread + k;
-    len[k] = 0;
-    if (li < tn) {
-      const JoinEntry ei = win[li];
-      if (!(ei.info >> 24) && ei.dur) {
-        const unsigned long long end_i = ei.start + ei.dur;
-        uint32_t lo = li + 1, hi = wn;  // first staged entry with start >= end_i
-        while (lo < hi) {
-          const uint32_t mid = (lo + hi) >> 1;
-          if (win[mid].start < end_i) lo = mid + 1; else hi = mid;
-        }
-        len[k] = lo - (li + 1);
-        if (lo == wn && t0 + wn < a.n) spills = true;  // the run may go on behind the window
+    const uint32_t li = k * kJoinThreads + tid;
+    uint32_t len = 0;
+    if (li < tn && !(s_info[li] >> 24) && s_dur[li]) {
+      const unsigned long long end_i = s_start[li] + s_dur[li];
+      // gallop: [lo, hi) brackets the first staged entry with start >= end_i
+      uint32_t lo = li + 1, step = 1, hi = lo;
+      while (hi < wn && s_start[hi] < end_i) { lo = hi + 1; hi += step; step <<= 1; }
+      hi = min(hi, wn);
+      while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (s_start[mid] < end_i) lo = mid + 1; else hi = mid;
       }
+      len = lo - (li + 1);
+      if (lo == wn && t0 + wn < a.n) spills = true;  // the run may go on behind the window
     }
-    mine += len[k];
+    run_off[li] = len;
   }
   if (spills) atomicOr(&s_spill, 1u);
+  __syncthreads();
+  // ---- exclusive scan of the run lengths (thread t scans launches 4t .. 4t+3)
+  uint32_t len4[kJoinPerThread], mine = 0;
+  {
+    const uint4 v = *reinterpret_cast<const uint4*>(run_off + tid * kJoinPerThread);
+    len4[0] = v.x; len4[1] = v.y; len4[2] = v.z; len4[3] = v.w;
+    mine = v.x + v.y + v.z + v.w;
+  }
   const uint32_t inc = warp_incl_scan(mine);
   if (lane == 31) warp_tot[warp] = inc;
   __syncthreads();
@@ -131,103 +149,82 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
     if (w < warp) off += warp_tot[w];
     total += warp_tot[w];
   }
-#pragma unroll
-  for (int k = 0; k < kJoinPerThread; ++k) {
-    run_off[tid * kJoinPerThread + k] = off;
-    off += len[k];
+  {
+    uint4 o;
+    o.x = off; o.y = off + len4[0]; o.z = o.y + len4[1]; o.w = o.z + len4[2];
+    *reinterpret_cast<uint4*>(run_off + tid * kJoinPerThread) = o;
   }
-  if (tid == kJoinThreads - 1) run_off[kJoinTile] = total;
+  if (tid == 0) run_off[kJoinTile] = total;
   __syncthreads();
   const bool any_spill = s_spill != 0;
 
-  auto owner_of = [&](uint32_t q) -> uint32_t {  // last launch whose run starts at or before candidate q
+  // ---- this thread's share of the candidates: [c0, c1)
+  const uint32_t per = (total + kJoinThreads - 1) / kJoinThreads;
+  const uint32_t c0 = min(total, tid * per), c1 = min(total, c0 + per);
+  uint32_t owner0 = 0;
+  if (c0 < c1) {  // last launch whose run starts at or before candidate c0
     uint32_t lo = 0, hi = kJoinTile;
     while (lo + 1 < hi) {
       const uint32_t mid = (lo + hi) >> 1;
-      if (run_off[mid] <= q) lo = mid; else hi = mid;
+      if (run_off[mid] <= c0) lo = mid; else hi = mid;
     }
-    return lo;
-  };
+    owner0 = lo;
+  }
 
-  // ---- pass 0 counts the valid candidates, pass 1 writes them (block-ordered compaction)
-  uint32_t n_valid = 0, spill_valid = 0;
-  unsigned long long out_base = 0;
+  uint32_t n_valid = 0, spill_before = 0;
+  unsigned long long out = 0;
   for (int pass = 0; pass < 2; ++pass) {
-    uint32_t running = 0;  // valid candidates of earlier rounds (pass 1)
-    for (uint32_t q0 = 0; q0 < total; q0 += kJoinThreads) {
-      const uint32_t q = q0 + tid;
-      bool ok = false;
-      uint32_t li = 0, lj = 0;
-      if (q < total) {
-        li = owner_of(q);
-        lj = li + 1 + (q - run_off[li]);
-        ok = join_pair_ok(win[li], win[lj]);
-      }
-      const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, ok);
-      if (pass == 0) {
-        if (lane == 0) n_valid += __popc(ballot);
-      } else {
-        __syncthreads();
-        if (lane == 0) warp_tot[warp] = __popc(ballot);
-        __syncthreads();
-        uint32_t before = running, round_total = 0;
-        for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
-          if (w < warp) before += warp_tot[w];
-          round_total += warp_tot[w];
-        }
-        if (ok) join_emit<kIndexOutput>(a, out_base + before + __popc(ballot & lanemask_lt()), win[li], win[lj], t0 + li, t0 + lj, nk);
-        running += round_total;
-      }
+    uint32_t li = owner0;
+    JoinEntry ei = entry(li);
+    for (uint32_t q = c0; q < c1; ++q) {
+      while (run_off[li + 1] <= q) { ++li; ei = entry(li); }
+      const uint32_t lj = li + 1 + (q - run_off[li]);
+      const JoinEntry ej = entry(lj);
+      if (!join_pair_ok(ei, ej)) continue;
+      if (pass == 0) ++n_valid;
+      else { join_emit<kIndexOutput>(a, out, ei, ej, t0 + li, t0 + lj, nk); ++out; }
     }
     // runs that continue behind the window: their owner walks the rest from global memory
     uint32_t spill_cnt = 0;
     if (any_spill) {
 #pragma unroll 1
       for (int k = 0; k < kJoinPerThread; ++k) {
-        const uint32_t li = tid * kJoinPerThread + k;
-        if (!(li < tn && li + 1 + len[k] == wn)) continue;  // only runs that reached the end of the window
-        const JoinEntry ei = win[li];
-        if ((ei.info >> 24) || !ei.dur) continue;
-        const unsigned long long end_i = ei.start + ei.dur;
+        const uint32_t sl = tid * kJoinPerThread + k;
+        if (!(sl < tn && sl + 1 + len4[k] == wn)) continue;  // only runs that reached the end of the window
+        const JoinEntry es = entry(sl);
+        if ((es.info >> 24) || !es.dur) continue;
+        const unsigned long long end_s = es.start + es.dur;
         for (uint64_t j = t0 + wn; j < a.n; ++j) {
           const JoinEntry ej = join_entry(a, j);
-          if (ej.start >= end_i) break;
-          if (!join_pair_ok(ei, ej)) continue;
-          if (pass == 1) join_emit<kIndexOutput>(a, out_base + n_valid + spill_valid + spill_cnt, ei, ej, t0 + li, j, nk);
+          if (ej.start >= end_s) break;
+          if (!join_pair_ok(es, ej)) continue;
+          if (pass == 1) join_emit<kIndexOutput>(a, s_base + spill_before + spill_cnt, es, ej, t0 + sl, j, nk);
           ++spill_cnt;
         }
       }
     }
     if (pass == 0) {
-      // totals: window candidates (lane 0 of each warp holds its warp's count) and spilled ones (every thread)
-      n_valid = __shfl_sync(0xFFFFFFFFu, n_valid, 0);
+      // one scan over (window pairs, spilled pairs) per thread; window pairs first, spilled pairs behind all of them
+      const uint32_t vinc = warp_incl_scan(n_valid), sinc = warp_incl_scan(spill_cnt);
       __syncthreads();
-      if (lane == 0) warp_tot[warp] = n_valid;
+      if (lane == 31) { warp_tot[warp] = vinc; warp_tot2[warp] = sinc; }
       __syncthreads();
-      uint32_t cta_valid = 0;
-      for (uint32_t w = 0; w < kJoinThreads / 32; ++w) cta_valid += warp_tot[w];
-      n_valid = cta_valid;
-      uint32_t cta_spill = 0;
-      if (any_spill) {
-        const uint32_t sinc = warp_incl_scan(spill_cnt);
-        __syncthreads();
-        if (lane == 31) warp_tot[warp] = sinc;
-        __syncthreads();
-        spill_valid = sinc - spill_cnt;
-        for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
-          if (w < warp) spill_valid += warp_tot[w];
-          cta_spill += warp_tot[w];
-        }
+      uint32_t vbefore = vinc - n_valid, sbefore = sinc - spill_cnt, vtotal = 0, stotal = 0;
+      for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
+        if (w < warp) { vbefore += warp_tot[w]; sbefore += warp_tot2[w]; }
+        vtotal += warp_tot[w];
+        stotal += warp_tot2[w];
       }
       __syncthreads();
-      if (tid == 0) s_base = (cta_valid + cta_spill) ? atomicAdd(&a.ctl->n_pairs, (unsigned long long)(cta_valid + cta_spill)) : 0ull;
+      if (tid == 0) s_base = (vtotal + stotal) ? atomicAdd(&a.ctl->n_pairs, (unsigned long long)(vtotal + stotal)) : 0ull;
       __syncthreads();
-      if (cta_valid + cta_spill == 0) return;
-      out_base = s_base;
+      if (vtotal + stotal == 0) return;
+      out = s_base + vbefore;
+      spill_before = vtotal + sbefore;
     }
   }
 }
 
-constexpr size_t join_smem_bytes() { return (size_t)(kJoinTile + kJoinAhead) * sizeof(JoinEntry) + (kJoinTile + 1) * sizeof(uint32_t); }
+constexpr size_t join_smem_bytes() { return 0; }
 
 }  // namespace ks
