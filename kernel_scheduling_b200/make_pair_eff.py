@@ -1,0 +1,128 @@
+"""Agent timing logs in, ``pair_eff.tsv`` / ``kernel_us.tsv`` out -- the program the reference's daemon names as
+``make_pair_eff.py`` (scheduler/scheduler_daemon.cpp:5, :193, :848) but does not ship.
+
+    python -m kernel_scheduling_b200.make_pair_eff --corun a.tsv b.tsv [...] --solo sa.tsv sb.tsv [...] --out-dir DIR
+
+Input: the 17-column logs the agent writes (scheduler/agent.cpp:692-705), one file per process; ``--solo`` files
+come from a one-kernel-at-a-time run (profiling/pairprof_daemon.cpp:46).  Rows without ``end_ns`` (no completion
+callback, agent.cpp:702) are dropped.  Kernel symbols are reduced to their short names (kernel_key.hpp) and
+numbered; the ``model`` column is the tenant.
+
+Output, in the layout ``load_pair_eff`` / ``load_kernel_us`` parse (scheduler_daemon.cpp:193-202, :230-264):
+SHAPE rows (with grid) and TYPE rows (grid ``*``) in the same files; ``gangs`` = how often the pair overlapped;
+extra statistic columns are appended after the ones the daemon reads (it finds columns by name and ignores others).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import re
+
+import numpy as np
+import pandas as pd
+
+from . import _lib
+from .pair_table import PairTableBuilder
+from .records import pack_records
+
+_DIMS = re.compile(r"\d+")
+
+
+def _dims(col: pd.Series) -> np.ndarray:
+    """'(x, y, z)' or 'x,y,z' -> (n, 3) uint32 (scheduler_daemon.cpp:214-219 accepts both spellings)."""
+    uniq = {s: [int(v) for v in _DIMS.findall(str(s))][:3] for s in col.unique()}
+    bad = [s for s, v in uniq.items() if len(v) != 3]
+    if bad:
+        raise ValueError(f"not a dimension triple: {bad[0]!r}")
+    return np.array([uniq[s] for s in col], dtype=np.uint32).reshape(len(col), 3)
+
+
+class TraceIngest:
+    """Turns timing frames into launch records, numbering kernel names and models as it goes."""
+
+    def __init__(self):
+        self.names: list[str] = []
+        self._name_id: dict[str, int] = {}
+        self._base_cache: dict[str, str] = {}
+        self.models: list[str] = []
+
+    def _name_ids(self, symbols: pd.Series) -> np.ndarray:
+        ids = {}
+        for sym in symbols.unique():
+            base = self._base_cache.get(sym)
+            if base is None:
+                base = self._base_cache[sym] = _lib.function_base(str(sym))
+            if base not in self._name_id:
+                self._name_id[base] = len(self.names)
+                self.names.append(base)
+            ids[sym] = self._name_id[base]
+        return symbols.map(ids).to_numpy(dtype=np.uint32)
+
+    def records(self, frame: pd.DataFrame, solo: bool) -> np.ndarray:
+        f = frame[frame["end_ns"].notna()]
+        tenants = []
+        for m in f["model"].astype(str):
+            if m not in self.models:
+                self.models.append(m)
+            tenants.append(self.models.index(m))
+        n = len(f)
+        return pack_records(
+            self._name_ids(f["kernel_name"]), _dims(f["grid"]), _dims(f["block"]), np.zeros(n, np.uint32), np.array(tenants, dtype=np.uint32),
+            np.full(n, solo), f["start_ns"].to_numpy(dtype=np.uint64), f["end_ns"].to_numpy(dtype=np.uint64))
+
+
+def _xyz(v) -> str:
+    return f"{int(v[0])},{int(v[1])},{int(v[2])}"
+
+
+def write_tables(out_dir, tables, names, models):
+    """tables: [(key_rows, pair_rows, is_type)]. Writes kernel_us.tsv and pair_eff.tsv into out_dir."""
+    os.makedirs(out_dir, exist_ok=True)
+    us_path, eff_path = os.path.join(out_dir, "kernel_us.tsv"), os.path.join(out_dir, "pair_eff.tsv")
+    with open(us_path, "w") as fu, open(eff_path, "w") as fe:
+        fu.write("model\tkernel\tblock\tgrid\tsolo_us\tlaunches\tsolo_launches\n")
+        fe.write("model_a\tkernel_a\tblock_a\tgrid_a\tmodel_b\tkernel_b\tblock_b\tgrid_b\tefficiency\tgangs"
+                 "\tslowdown_median_a\tslowdown_mean_a\tslowdown_min_a\tslowdown_max_a\tslowdown_median_b\tslowdown_mean_b\tslowdown_min_b\tslowdown_max_b\n")
+        for keys, pairs, is_type in tables:
+            ident = {}
+            for r in keys:
+                grid = "*" if is_type else _xyz(r["grid"])
+                ident[int(r["key"])] = (models[int(r["tenant"])], names[int(r["name_id"])], _xyz(r["block"]), grid)
+                if np.isfinite(r["solo_ns"]):
+                    fu.write("\t".join(ident[int(r["key"])]) + f"\t{float(r['solo_ns']) / 1e3!r}\t{int(r['launches'])}\t{int(r['solo_launches'])}\n")
+            for p in pairs:
+                if not np.isfinite(p["efficiency"]):
+                    continue  # a pair without both solo times has no efficiency: the daemon would skip the row anyway
+                stats = "\t".join(repr(float(p[c])) for c in ("median_a", "mean_a", "min_a", "max_a", "median_b", "mean_b", "min_b", "max_b"))
+                fe.write("\t".join(ident[int(p["key_a"])]) + "\t" + "\t".join(ident[int(p["key_b"])]) + f"\t{float(p['efficiency'])!r}\t{int(p['count'])}\t{stats}\n")
+    return us_path, eff_path
+
+
+def build_tables(records: np.ndarray, builder: PairTableBuilder | None = None):
+    """-> [(key_rows, pair_rows, is_type)] for the SHAPE keys and the TYPE keys."""
+    own = builder is None
+    b = builder or PairTableBuilder()
+    try:
+        return [(*b.build(records, key_type=t), t) for t in (False, True)]
+    finally:
+        if own:
+            b.close()
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--corun", nargs="+", required=True)
+    ap.add_argument("--solo", nargs="*", default=[])
+    ap.add_argument("--out-dir", default=".")
+    args = ap.parse_args(argv)
+    ing = TraceIngest()
+    parts = [ing.records(pd.read_csv(p, sep="\t"), solo=False) for p in args.corun]
+    parts += [ing.records(pd.read_csv(p, sep="\t"), solo=True) for p in args.solo]
+    rec = np.concatenate(parts)
+    us, eff = write_tables(args.out_dir, build_tables(rec), ing.names, ing.models)
+    print(f"{len(rec)} launches, {len(ing.names)} kernel names, {len(ing.models)} models -> {us}, {eff}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,71 @@
+"""GPU: the reference-facing entry points against the reference's own outputs (golden vectors)."""
+import contextlib
+import io
+import json
+import os
+
+import numpy as np
+import pandas as pd
+import pytest
+
+from kernel_scheduling_b200 import make_pair_eff as M
+from kernel_scheduling_b200 import postprocess, profile_postprocess
+from oracle import pair_table_oracle as O
+from tests.test_host_logic import oracle_tables_as_rows, synthetic_timing_frames
+from tests.golden.make_golden import timing_frame
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_postprocess_cli_prints_what_the_reference_prints(tmp_path):
+    for c in json.load(open(os.path.join(GOLDEN, "postprocess_cases.json"))):
+        a, b = str(tmp_path / "a.tsv"), str(tmp_path / "b.tsv")
+        timing_frame(np.array(c["start1"], dtype=np.int64), "qwen").to_csv(a, sep="\t", index=False)
+        timing_frame(np.array(c["start2"], dtype=np.int64), "whisper").to_csv(b, sep="\t", index=False)
+        buf = io.StringIO()
+        if c["assertion"]:
+            with pytest.raises(AssertionError), contextlib.redirect_stdout(buf):
+                postprocess.main([a, b])
+        else:
+            with contextlib.redirect_stdout(buf):
+                assert postprocess.main([a, b]) == 0
+            assert buf.getvalue() == c["stdout"], c["name"]
+
+
+@pytest.mark.parametrize("case", [0, 1])
+def test_combine_duplicates_frame_equals_reference_csv(builder, case, tmp_path):
+    df = pd.read_csv(os.path.join(GOLDEN, f"combine_in_{case}.csv"))
+    want = pd.read_csv(os.path.join(GOLDEN, f"combine_out_{case}.csv"))
+    got = profile_postprocess.combine_duplicates(df, builder)
+    assert list(got.columns) == list(want.columns)
+    assert got["Kernel"].tolist() == want["Kernel"].tolist() and got["Block"].tolist() == want["Block"].tolist()
+    assert got["Launches"].tolist() == want["Launches"].tolist()
+    vals = [c for c in want.columns if c not in ("Kernel", "Block", "Launches")]
+    assert np.allclose(got[vals].to_numpy(), want[vals].to_numpy(), rtol=1e-12, atol=0, equal_nan=True)
+    out = str(tmp_path / "o.csv")
+    assert profile_postprocess.main([os.path.join(GOLDEN, f"combine_in_{case}.csv"), out]) == 0
+    assert np.allclose(pd.read_csv(out)[vals].to_numpy(), want[vals].to_numpy(), rtol=1e-12, atol=0, equal_nan=True)
+
+
+def test_make_pair_eff_end_to_end(tmp_path):
+    rec, frames = synthetic_timing_frames(5000)
+    paths = {}
+    for (model, solo), f in frames.items():
+        paths[(model, solo)] = str(tmp_path / f"{model}_{int(solo)}.tsv")
+        f.to_csv(paths[(model, solo)], sep="\t", index=False)
+    out = str(tmp_path / "out")
+    assert M.main(["--corun", paths[("qwen", False)], paths[("whisper", False)], "--solo", paths[("qwen", True)], paths[("whisper", True)], "--out-dir", out]) == 0
+    # expected files: the same ingest, tables from the oracle, same writer
+    ing = M.TraceIngest()
+    parts = [ing.records(pd.read_csv(paths[k], sep="\t"), k[1]) for k in (("qwen", False), ("whisper", False), ("qwen", True), ("whisper", True))]
+    r2 = np.concatenate(parts)
+    tables = [(*oracle_tables_as_rows(r2, O.KEY_SHAPE), False), (*oracle_tables_as_rows(r2, O.KEY_TYPE), True)]
+    want = str(tmp_path / "want")
+    M.write_tables(want, tables, ing.names, ing.models)
+    for name in ("kernel_us.tsv",):
+        assert open(os.path.join(out, name)).read() == open(os.path.join(want, name)).read()
+    got_eff, want_eff = pd.read_csv(os.path.join(out, "pair_eff.tsv"), sep="\t"), pd.read_csv(os.path.join(want, "pair_eff.tsv"), sep="\t")
+    exact = [c for c in got_eff.columns if "mean" not in c]
+    assert got_eff[exact].equals(want_eff[exact])
+    assert np.allclose(got_eff[["slowdown_mean_a", "slowdown_mean_b"]].to_numpy(), want_eff[["slowdown_mean_a", "slowdown_mean_b"]].to_numpy(), rtol=1e-6, atol=0)

@@ -1,0 +1,115 @@
+"""CPU: ingest of agent timing logs, the TSV emit, and acceptance of the emitted files by the reference's own loader."""
+import os
+import re
+import subprocess
+import time
+
+import numpy as np
+import pandas as pd
+import pytest
+
+from kernel_scheduling_b200 import make_pair_eff as M
+from kernel_scheduling_b200 import trace
+from kernel_scheduling_b200.records import KEY_ROW_DTYPE, PAIR_ROW_DTYPE
+from oracle import pair_table_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DAEMON = os.path.join(ROOT, "oracle", "_ref", "scheduler_daemon")
+
+
+def oracle_tables_as_rows(rec, key_mode):
+    """Oracle columns -> the structured arrays the library returns (so the emit can be tested without a GPU)."""
+    k, p = O.build_pair_table(rec, key_mode=key_mode)
+    keys = np.zeros(len(k["key"]), dtype=KEY_ROW_DTYPE)
+    for c in ("key", "name_id", "grid", "block", "smem", "tenant", "launches", "solo_launches", "solo_ns"):
+        keys[c] = k[c]
+    pairs = np.zeros(len(p["count"]), dtype=PAIR_ROW_DTYPE)
+    for c in p:
+        pairs[c] = p[c]
+    return keys, pairs
+
+
+def synthetic_timing_frames(n=3000):
+    """Two co-run and two solo agent logs with the 17 columns of scheduler/agent.cpp:692."""
+    rec = trace.generate(trace.config("c1", n))
+    solo = (rec["smem_word"] & (1 << 23)) != 0
+    ten = rec["smem_word"] >> 24
+    frames = {}
+    for t, model in enumerate(("qwen", "whisper")):
+        for s in (False, True):
+            r = rec[(ten == t) & (solo == s)]
+            m = len(r)
+            frames[(model, s)] = pd.DataFrame({
+                "kernel_id": np.arange(m), "kernel_us": (r["end_ns"] - r["start_ns"]) / 1e3, "prefetch_us": [""] * m, "prefetch_to_kernel_gap_us": [""] * m,
+                "hook_tag": ["unknown"] * m, "prefetch_bytes": [0] * m, "prefetched_tensors": [""] * m, "args_check": ["-"] * m,
+                "kernel_name": [f"void ns::kernel_{i}<float>(float*)" for i in r["name_id"]], "start_ns": r["start_ns"], "end_ns": r["end_ns"].astype("float64"),
+                "batch_id": np.arange(m) + 1, "batch_size": [1] * m, "batch_pos": [0] * m,
+                "block": [f"({b[0]}, {b[1]}, {b[2]})" for b in r["block"]], "model": [model] * m, "grid": [f"({g[0]}, {g[1]}, {g[2]})" for g in r["grid"]]})
+    return rec, frames
+
+
+def test_ingest_builds_equivalent_records():
+    rec, frames = synthetic_timing_frames()
+    f = frames[("qwen", False)].copy()
+    f.loc[5, "end_ns"] = np.nan  # a launch whose completion callback was never seen is dropped
+    ing = M.TraceIngest()
+    parts = [ing.records(f, False), ing.records(frames[("whisper", False)], False), ing.records(frames[("qwen", True)], True), ing.records(frames[("whisper", True)], True)]
+    got = np.concatenate(parts)
+    assert len(got) == len(rec) - 1 and ing.models == ["qwen", "whisper"]
+    assert all(re.fullmatch(r"kernel_\d+", n) for n in ing.names)
+    # same table as the original records up to the renumbering of names (and smem, which the logs do not carry)
+    ref = rec.copy()
+    ref["smem_word"] &= np.uint32(0xFF800000)
+    _, p_got = O.build_pair_table(got)
+    _, p_ref = O.build_pair_table(ref[np.isin(np.arange(len(ref)), np.flatnonzero((ref["smem_word"] >> 24 == 0) & ((ref["smem_word"] & (1 << 23)) == 0))[5:6], invert=True)])
+    assert sorted(p_got["count"].tolist()) == sorted(p_ref["count"].tolist())
+
+
+def test_emitted_tables_have_the_daemon_columns(tmp_path):
+    rec = trace.generate(trace.config("c1", 4000))
+    names = [f"k{i}" for i in range(int(rec["name_id"].max()) + 1)]
+    tables = [(*oracle_tables_as_rows(rec, O.KEY_SHAPE), False), (*oracle_tables_as_rows(rec, O.KEY_TYPE), True)]
+    us, eff = M.write_tables(str(tmp_path), tables, names, ["qwen", "whisper"])
+    du, de = pd.read_csv(us, sep="\t"), pd.read_csv(eff, sep="\t")
+    assert list(du.columns[:6]) == ["model", "kernel", "block", "grid", "solo_us", "launches"]
+    assert list(de.columns[:10]) == ["model_a", "kernel_a", "block_a", "grid_a", "model_b", "kernel_b", "block_b", "grid_b", "efficiency", "gangs"]
+    assert ((de["grid_a"] == "*") == (de["grid_b"] == "*")).all()  # both grids or neither (scheduler_daemon.cpp:240)
+    assert (de["model_a"] == "qwen").all() and (de["model_b"] == "whisper").all()
+    keys, pairs, _ = tables[0]
+    n_shape = int(np.isfinite(pairs["efficiency"]).sum())
+    assert (de["grid_a"] != "*").sum() == n_shape
+    row = de[de["grid_a"] != "*"].iloc[0]
+    assert float(row["efficiency"]) == pairs["efficiency"][np.isfinite(pairs["efficiency"])][0]  # repr() round-trips doubles
+
+
+@pytest.mark.skipif(not os.path.exists(DAEMON), reason="the reference daemon is only built where the reference tree is present")
+def test_reference_daemon_loads_the_emitted_tables(tmp_path):
+    rec = trace.generate(trace.config("c1", 4000))
+    names = [f"k{i}" for i in range(int(rec["name_id"].max()) + 1)]
+    tables = [(*oracle_tables_as_rows(rec, O.KEY_SHAPE), False), (*oracle_tables_as_rows(rec, O.KEY_TYPE), True)]
+    us, eff = M.write_tables(str(tmp_path), tables, names, ["qwen", "whisper"])
+    env = dict(os.environ, SCHED_MODE="eff", SCHED_PAIR_EFF_FILE=eff, SCHED_KERNEL_US_FILE=us, SCHED_LOG="off", SCHED_LOG_DIR=str(tmp_path))
+    proc = subprocess.Popen([DAEMON], env=env, stderr=subprocess.PIPE, stdout=subprocess.DEVNULL, text=True)
+    line = ""
+    try:
+        deadline = time.time() + 20
+        while time.time() < deadline:
+            out = proc.stderr.readline()
+            if not out:
+                break
+            if "type-pair rows" in out:
+                line = out
+                break
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+    m = re.search(r"(\d+) type-pair rows, (\d+) shape-pair rows.*SCHED_KERNEL_US_FILE: (\d+) rows", line)
+    assert m, f"the daemon did not report the tables: {line!r}"
+    n_type = int(np.isfinite(tables[1][1]["efficiency"]).sum())
+    n_shape = int(np.isfinite(tables[0][1]["efficiency"]).sum())
+    n_us = int(np.isfinite(tables[0][0]["solo_ns"]).sum()) + int(np.isfinite(tables[1][0]["solo_ns"]).sum())
+    assert (int(m.group(1)), int(m.group(2)), int(m.group(3))) == (n_type, n_shape, n_us)
+    assert "WARNING" not in line

@@ -1,0 +1,104 @@
+"""CPU: the oracle against the reference's own outputs (golden vectors) and against independent restatements."""
+import io
+import json
+import os
+
+import numpy as np
+import pandas as pd
+import pytest
+
+from kernel_scheduling_b200 import trace
+from kernel_scheduling_b200.records import RECORD_DTYPE, pack_records
+from oracle import pair_table_oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_record_layout_is_shared():
+    assert O.RECORD_DTYPE == RECORD_DTYPE and RECORD_DTYPE.itemsize == 48
+    assert [RECORD_DTYPE.fields[f][1] for f in ("name_id", "grid", "block", "smem_word", "start_ns", "end_ns")] == [0, 4, 16, 28, 32, 40]
+
+
+def test_mix64_known_answers():
+    # splitmix64 from seed 0 (published test vector): outputs mix64(1 * G), mix64(2 * G), mix64(3 * G)
+    g = 0x9E3779B97F4A7C15
+    got = O.mix64(np.array([g, (2 * g) % 2**64, (3 * g) % 2**64], dtype=np.uint64))
+    assert [int(x) for x in got] == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F]
+
+
+def test_kernel_key_fields():
+    rec = pack_records([7, 7, 7, 7, 8], [[1, 2, 3]] * 3 + [[9, 2, 3]] + [[1, 2, 3]], [[128, 1, 1]] * 5, [0, 0, 4096, 0, 0], [0, 1, 0, 0, 0],
+                       [False, True, False, False, False], np.arange(5) * 10 + 100, np.arange(5) * 10 + 105)
+    k = O.kernel_keys(rec)
+    assert len(set(k.tolist())) == 5  # tenant, smem, grid and name all enter the SHAPE key
+    rec2 = rec.copy()
+    rec2["smem_word"] ^= np.uint32(1 << 23)  # the solo flag does not
+    assert np.array_equal(O.kernel_keys(rec2), k)
+    kt = O.kernel_keys(rec, O.KEY_TYPE)
+    assert kt[0] == kt[2] == kt[3] and kt[0] != kt[1] and kt[0] != kt[4]  # TYPE: tenant + name + block only
+
+
+@pytest.mark.parametrize("interleave", [False, True])
+def test_vectorised_oracle_equals_brute_force(interleave):
+    rec = trace.generate(trace.config("c3", 1200), interleave_solo=interleave)
+    k1, p1 = O.build_pair_table(rec)
+    k2, p2 = O.build_pair_table_bruteforce(rec)
+    for c in ("key", "launches", "solo_launches", "solo_ns", "tenant"):
+        assert np.array_equal(k1[c], k2[c], equal_nan=True), c
+    assert len(p1["count"]) > 50
+    for c in p2:
+        if c.startswith(("sum", "mean")):
+            assert np.allclose(p1[c], p2[c], rtol=1e-12, atol=0, equal_nan=True), c
+        else:
+            assert np.array_equal(p1[c], p2[c], equal_nan=True), c
+
+
+def test_oracle_order_independent_and_rejects_bad_records():
+    rec = trace.generate(trace.config("c1", 3000))
+    _, p1 = O.build_pair_table(rec)
+    _, p2 = O.build_pair_table(trace.shuffled(rec))
+    for c in p1:
+        assert np.allclose(p1[c], p2[c], rtol=1e-12, atol=0, equal_nan=True) if p1[c].dtype.kind == "f" else np.array_equal(p1[c], p2[c]), c
+    bad = rec.copy()
+    bad["end_ns"][3] = bad["start_ns"][3] - 1
+    with pytest.raises(ValueError):
+        O.build_pair_table(bad)
+
+
+def test_count_batches_matches_reference_stdout():
+    cases = json.load(open(os.path.join(GOLDEN, "postprocess_cases.json")))
+    assert len(cases) >= 6
+    for c in cases:
+        s1, s2 = np.array(c["start1"], dtype=np.uint64), np.array(c["start2"], dtype=np.uint64)
+        if c["assertion"]:
+            with pytest.raises(ValueError):
+                O.count_batches(s1, s2)
+        else:
+            assert str(O.count_batches(s1, s2)) == c["stdout"].strip().splitlines()[-1], c["name"]
+
+
+@pytest.mark.parametrize("case", [0, 1])
+def test_combine_duplicates_matches_reference_csv(case):
+    df = pd.read_csv(os.path.join(GOLDEN, f"combine_in_{case}.csv"))
+    want = pd.read_csv(os.path.join(GOLDEN, f"combine_out_{case}.csv"))
+    excl = ["Launches", "Grid", "Shared Mem Pipe %", "Shared Mem Pipe % std", "Kernel", "Block"]
+    cols = [c for c in df.columns if c not in excl]
+    gk, gb, total, means = O.combine_duplicates(df["Kernel"].tolist(), df["Block"].tolist(), df["Launches"].to_numpy(), df[cols].to_numpy(dtype=np.float64))
+    assert gk == want["Kernel"].tolist() and gb == want["Block"].tolist()
+    assert np.array_equal(total, want["Launches"].to_numpy())
+    assert list(want.columns) == ["Kernel", "Block", "Launches"] + cols
+    assert np.allclose(means, want[cols].to_numpy(), rtol=1e-12, atol=0, equal_nan=True)
+
+
+def test_trace_generator_shapes():
+    spec = trace.config("c2", 200_000)
+    rec = trace.generate(spec)
+    assert len(rec) == 200_000 and (np.diff(rec["start_ns"].astype(np.int64)) >= 0).all()
+    solo = (rec["smem_word"] & (1 << 23)) != 0
+    assert abs(solo.mean() - 0.10) < 0.01
+    ten = rec["smem_word"] >> 24
+    for t in (0, 1):  # one launch in flight per tenant: its co-run intervals never overlap each other
+        m = (ten == t) & ~solo
+        assert (rec["start_ns"][m][1:] >= rec["end_ns"][m][:-1]).all()
+    k, p = O.build_pair_table(rec, check_bijection=False)
+    assert len(k["key"]) <= 2000 and 0.3 < p["count"].sum() / len(rec) < 0.7
