@@ -47,7 +47,7 @@ struct ks_handle {
 
   // growable
   DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
-  DevBuf skey[2], lane[2][kLanes];
+  DevBuf samples[2];  // the sample stream, 16-byte items {sort key, lane 0, lane 1, lane 2}; two sets for the sort
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
   DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows;
   DevBuf tmp[6];
@@ -134,8 +134,8 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
   uint32_t* hist = as<uint32_t>(h->hist);
   uint32_t* gbase = hist + 8 * 256;
   KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
-  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 64 - 1) / (256 * 64), (uint64_t)h->sm_count * 2);
-  k_radix_hist<KeyT><<<hist_grid, 256, 0, h->stream>>>(keys[0], n_dev, (uint32_t)n, begin_bit, end_bit, hist);
+  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
+  k_radix_hist<KeyT><<<hist_grid, 256, 0, h->stream>>>(keys[0], 1u, n_dev, (uint32_t)n, begin_bit, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
   auto kern = k_onesweep_pass<KeyT, ValT, NV, ITEMS>;
@@ -162,6 +162,53 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
     a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
     a.err = &h->d_ctl->err;
     kern<<<grid, kSortThreads, smem, h->stream>>>(a);
+    cur ^= 1;
+  }
+  KS_CUDA(h, cudaGetLastError());
+  return cur;
+}
+
+// K2 driver for the 16-byte sample stream: sorts set 0/1 of h->samples on key bits [0, end_bit); returns the set that
+// holds the result.
+int radix_sort16(ks_handle* h, uint64_t n, int end_bit) {
+  constexpr int ITEMS = 8;
+  constexpr int TILE = kSortThreads * ITEMS;
+  if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
+  const int passes = (end_bit + 7) / 8;
+  if (passes <= 0 || n == 0) return 0;
+  const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
+  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  KS_ENSURE(h, h->lookback, lb_bytes);
+  KS_ENSURE(h, h->hist, 2 * 8 * 256 * sizeof(uint32_t));
+  uint32_t* hist = as<uint32_t>(h->hist);
+  uint32_t* gbase = hist + 8 * 256;
+  KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
+  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
+  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(as<uint32_t>(h->samples[0]), 4u, nullptr, (uint32_t)n, 0, end_bit, hist);
+  k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
+  h->launches += 2 + passes;
+  constexpr size_t smem = sort16_smem_bytes<ITEMS>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  int cur = 0;
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 5);
+  for (int p = 0; p < passes; ++p) {
+    KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+    SortPass16Args a{};
+    a.in = as<uint4>(h->samples[cur]);
+    a.out = as<uint4>(h->samples[cur ^ 1]);
+    a.n_dev = nullptr;
+    a.n = (uint32_t)n;
+    a.shift = 8 * p;
+    a.bits = std::min(8, end_bit - a.shift);
+    a.gbase = gbase + p * 256;
+    a.lookback = as<uint32_t>(h->lookback);
+    a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+    a.err = &h->d_ctl->err;
+    k_onesweep_pass16<ITEMS><<<grid, kSortThreads, smem, h->stream>>>(a);
     cur ^= 1;
   }
   KS_CUDA(h, cudaGetLastError());
@@ -261,19 +308,13 @@ int run_dict(ks_handle* h) {
 
 int ensure_samples(ks_handle* h, uint64_t cap) {
   for (int s = 0; s < 2; ++s) {
-    KS_ENSURE(h, h->skey[s], cap * 4);
-    for (int l = 0; l < kLanes; ++l) KS_ENSURE(h, h->lane[s][l], cap * 4);
+    KS_ENSURE(h, h->samples[s], cap * 16);
   }
   return 0;
 }
 
 uint64_t sample_capacity(ks_handle* h) {
-  uint64_t cap = h->skey[0].cap / 4;
-  for (int s = 0; s < 2; ++s) {
-    cap = std::min<uint64_t>(cap, h->skey[s].cap / 4);
-    for (int l = 0; l < kLanes; ++l) cap = std::min<uint64_t>(cap, h->lane[s][l].cap / 4);
-  }
-  return cap;
+  return std::min<uint64_t>(h->samples[0].cap, h->samples[1].cap) / 16;
 }
 
 int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b) {
@@ -283,10 +324,7 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
   j.tl_dm = as<unsigned long long>(h->tl_dm[tl]);
   j.kid_of_slot = h->kid_of_slot;
   j.n = n;
-  j.skey = as<uint32_t>(h->skey[0]);
-  j.lane0 = as<uint32_t>(h->lane[0][0]);
-  j.lane1 = as<uint32_t>(h->lane[0][1]);
-  j.lane2 = as<uint32_t>(h->lane[0][2]);
+  j.samples = as<uint4>(h->samples[0]);
   j.idx_a = idx_a;
   j.idx_b = idx_b;
   j.capacity = capacity;
@@ -306,7 +344,7 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
 }
 
 // K4 core: integer statistics of every row (three size classes, see ks_segstats.cuh)
-int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n_values, uint32_t max_rows) {
+int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], uint32_t stride, int n_lanes, uint64_t n_values, uint32_t max_rows) {
   const uint32_t max_large = (uint32_t)(n_values / kMidMax) + 1;
   const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
   KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
@@ -319,6 +357,7 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
   SegArgs s{};
   for (int l = 0; l < kLanes; ++l) s.lane[l] = lanes[l];
   s.n_lanes = n_lanes;
+  s.stride = stride;
   s.row_start = as<uint32_t>(h->row_start);
   s.n_rows_dev = &h->d_ctl->n_rows;
   s.max_rows = max_rows;
@@ -351,13 +390,14 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], int n_l
 }
 
 // rows + segment statistics over sorted samples (set `s`), n samples
-int run_rows_and_stats(ks_handle* h, const uint32_t* skey, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n, uint32_t max_rows) {
+int run_rows_and_stats(ks_handle* h, const uint32_t* skey, uint32_t stride, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n, uint32_t max_rows) {
   const uint32_t max_tiles = (uint32_t)((n + kRowsTile - 1) / kRowsTile);
   KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
   KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
   KS_ENSURE(h, h->row_key, ((size_t)max_rows + 2) * 4);
   RowsArgs r{};
   r.skey = skey;
+  r.key_stride = stride;
   r.n_dev = nullptr;
   r.n = (uint32_t)n;
   r.tile_cnt = as<uint32_t>(h->tile_cnt);
@@ -373,7 +413,7 @@ int run_rows_and_stats(ks_handle* h, const uint32_t* skey, const uint32_t* const
   k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
   h->launches += 3;
   KS_CUDA(h, cudaGetLastError());
-  return run_segment_stats(h, lanes, n_lanes, n, max_rows);
+  return run_segment_stats(h, lanes, stride, n_lanes, n, max_rows);
 }
 
 __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start, uint32_t n_rows, unsigned long long* out) {
@@ -476,10 +516,9 @@ void ks_destroy(ks_handle* h) {
   fr(h->dkeys); fr(h->dslot); fr(h->drank); fr(h->slot_of_kid); fr(h->row_of_kid); fr(h->keys_sorted); fr(h->solo_ns); fr(h->key_rows);
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
-                    &h->skey[0], &h->skey[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
+                    &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
                     &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
-  for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) fr(h->lane[s][l].p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
   delete h;
@@ -535,10 +574,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     SoloArgs s{};
     s.solo_stream = as<unsigned long long>(h->solo_stream);
     s.kid_of_slot = h->kid_of_slot;
-    s.skey = as<uint32_t>(h->skey[0]);
-    s.lane0 = as<uint32_t>(h->lane[0][0]);
-    s.lane1 = as<uint32_t>(h->lane[0][1]);
-    s.lane2 = as<uint32_t>(h->lane[0][2]);
+    s.samples = as<uint4>(h->samples[0]);
     s.capacity = cap;
     s.ctl = h->d_ctl;
     k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
@@ -561,18 +597,16 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   const uint64_t nk = h->h_ctl->n_keys, n_solo = h->h_ctl->n_solo;
 
   // K2: group the samples by sort key
-  uint32_t* keys[2] = {as<uint32_t>(h->skey[0]), as<uint32_t>(h->skey[1])};
-  uint32_t* vals[2][kLanes];
-  for (int s = 0; s < 2; ++s) for (int l = 0; l < kLanes; ++l) vals[s][l] = as<uint32_t>(h->lane[s][l]);
   const int end_bit = bit_length(nk + nk * nk);
-  const int cur = radix_sort<uint32_t, uint32_t, kLanes, 16>(h, keys, vals, n_samples, nullptr, 0, end_bit);
+  const int cur = radix_sort16(h, n_samples, end_bit);
   if (cur < 0) return cur;
   cudaEventRecord(ev[7], h->stream);
 
   // K4: rows, statistics, tables
   const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n_samples, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
-  const uint32_t* lanes[kLanes] = {vals[cur][0], vals[cur][1], vals[cur][2]};
-  { int r = run_rows_and_stats(h, keys[cur], lanes, kLanes, n_samples, max_rows); if (r) return r; }
+  const uint32_t* sorted = as<uint32_t>(h->samples[cur]);
+  const uint32_t* lanes[kLanes] = {sorted + 1, sorted + 2, sorted + 3};
+  { int r = run_rows_and_stats(h, sorted, 4, lanes, kLanes, n_samples, max_rows); if (r) return r; }
   cudaEventRecord(ev[8], h->stream);
   KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
   FinalArgs f{};
@@ -800,7 +834,7 @@ int64_t ks_segment_stats(ks_handle* h, const uint32_t* values, const uint64_t* o
   h->h_ctl->n_rows = rows;
   KS_CUDA(h, cudaMemcpyAsync(&h->d_ctl->n_rows, &h->h_ctl->n_rows, 4, cudaMemcpyHostToDevice, h->stream));
   const uint32_t* lanes1[kLanes] = {d_val, nullptr, nullptr};
-  { int r = run_segment_stats(h, lanes1, 1, n_values, rows); if (r) return r; }
+  { int r = run_segment_stats(h, lanes1, 1u, 1, n_values, rows); if (r) return r; }
   unsigned long long* d_out = dev ? reinterpret_cast<unsigned long long*>(out) : as<unsigned long long>(h->tmp[2]);
   k_stats_to_u64<<<(rows + 255) / 256, 256, 0, h->stream>>>(as<RowStats>(h->stats), as<uint32_t>(h->row_start), rows, d_out);
   KS_CUDA(h, cudaGetLastError());

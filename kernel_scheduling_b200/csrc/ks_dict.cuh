@@ -77,10 +77,7 @@ __global__ void __launch_bounds__(256) k_dict_place(const DictArgs a) {
 struct SoloArgs {
   const unsigned long long* solo_stream;
   const uint32_t* kid_of_slot;
-  uint32_t* skey;
-  uint32_t* lane0;
-  uint32_t* lane1;
-  uint32_t* lane2;
+  uint4* samples;  // {sort key, lane 0, lane 1, lane 2}
   uint64_t capacity;
   Control* ctl;
 };
@@ -89,10 +86,7 @@ __global__ void __launch_bounds__(256) k_solo_samples(const SoloArgs a) {
   if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->n_pairs = ns;  // pairs are appended behind the solo samples
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < ns && i < a.capacity; i += gridDim.x * blockDim.x) {
     const unsigned long long e = a.solo_stream[i];
-    a.skey[i] = a.kid_of_slot[(uint32_t)e & kMetaSlotMask];
-    a.lane0[i] = (uint32_t)(e >> 32);
-    a.lane1[i] = 0;
-    a.lane2[i] = 0;
+    a.samples[i] = make_uint4(a.kid_of_slot[(uint32_t)e & kMetaSlotMask], (uint32_t)(e >> 32), 0u, 0u);
   }
 }
 

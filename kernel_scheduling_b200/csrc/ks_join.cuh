@@ -33,10 +33,7 @@ struct JoinArgs {
   const unsigned long long* tl_dm;
   const uint32_t* kid_of_slot;
   uint64_t n;
-  uint32_t* skey;
-  uint32_t* lane0;
-  uint32_t* lane1;
-  uint32_t* lane2;
+  uint4* samples;   // {sort key, duration of a, duration of b, span}
   uint32_t* idx_a;  // stage API: positions instead of samples (may be null)
   uint32_t* idx_b;
   uint64_t capacity;  // entries the sample stream (or idx arrays) can hold
@@ -77,10 +74,8 @@ __device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long 
   } else {
     const uint32_t kid_i = ei.info & 0xFFFFu, kid_j = ej.info & 0xFFFFu;
     const uint32_t ka = i_is_a ? kid_i : kid_j, kb = i_is_a ? kid_j : kid_i;
-    a.skey[out] = nk + ka * nk + kb;
-    a.lane0[out] = i_is_a ? ei.dur : ej.dur;
-    a.lane1[out] = i_is_a ? ej.dur : ei.dur;
-    a.lane2[out] = (uint32_t)(max(ei.start + ei.dur, ej.start + ej.dur) - ei.start);
+    a.samples[out] = make_uint4(nk + ka * nk + kb, i_is_a ? ei.dur : ej.dur, i_is_a ? ej.dur : ei.dur,
+                                (uint32_t)(max(ei.start + ei.dur, ej.start + ej.dur) - ei.start));
   }
 }
 

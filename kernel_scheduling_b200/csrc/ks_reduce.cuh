@@ -15,7 +15,8 @@ namespace ks {
 
 constexpr int kRowsTile = 2048;  // samples per tile of the run-start compaction (256 threads x 8)
 struct RowsArgs {
-  const uint32_t* skey;      // sorted sort keys
+  const uint32_t* skey;      // sorted sort keys, one every key_stride words
+  uint32_t key_stride;
   const uint32_t* n_dev;     // number of samples in device memory, or nullptr to use n
   uint32_t n;
   uint32_t* tile_cnt;        // [tiles + 1]
@@ -27,7 +28,9 @@ struct RowsArgs {
   Control* ctl;
 };
 
-__device__ __forceinline__ bool run_starts_at(const uint32_t* skey, uint32_t i) { return i == 0 || skey[i] != skey[i - 1]; }
+__device__ __forceinline__ bool run_starts_at(const uint32_t* skey, uint32_t stride, uint32_t i) {
+  return i == 0 || skey[(size_t)i * stride] != skey[(size_t)(i - 1) * stride];
+}
 
 __global__ void __launch_bounds__(256) k_rows_count(const RowsArgs a) {
   __shared__ uint32_t warp_tot[8];
@@ -38,7 +41,7 @@ __global__ void __launch_bounds__(256) k_rows_count(const RowsArgs a) {
 #pragma unroll
     for (int k = 0; k < kRowsTile / 256; ++k) {
       const uint32_t i = tile * kRowsTile + k * 256 + threadIdx.x;
-      if (i < n) c += run_starts_at(a.skey, i);
+      if (i < n) c += run_starts_at(a.skey, a.key_stride, i);
     }
     c = warp_sum(c);
     __syncthreads();
@@ -82,40 +85,52 @@ __global__ void __launch_bounds__(1024) k_rows_scan(const RowsArgs a) {
 }
 
 __global__ void __launch_bounds__(256) k_rows_fill(const RowsArgs a) {
-  __shared__ uint32_t warp_tot[8];
+  __shared__ uint32_t word_base[kRowsTile / 32];  // run starts in front of each 32-sample word of the tile
   const uint32_t n = a.n_dev ? *a.n_dev : a.n;
   const uint32_t nk = a.ctl->n_keys;
   const uint32_t ntiles = min((n + kRowsTile - 1) / kRowsTile, a.max_tiles);
   if (a.ctl->n_rows > a.max_rows) return;
+  const uint32_t lane = lane_id(), warp = threadIdx.x >> 5;
   uint32_t solo_rows = 0;
   for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    // thread t owns 8 consecutive samples so that row order = sample order
-    const uint32_t i0 = tile * kRowsTile + threadIdx.x * (kRowsTile / 256);
-    uint32_t flags = 0, c = 0;
+    // consecutive lanes look at consecutive samples; a ballot per 32 samples marks the run starts
+    uint32_t key[kRowsTile / 256], ballot[kRowsTile / 256];
 #pragma unroll
     for (int k = 0; k < kRowsTile / 256; ++k) {
-      const uint32_t i = i0 + k;
-      if (i < n && run_starts_at(a.skey, i)) { flags |= 1u << k; ++c; }
+      const uint32_t i = tile * kRowsTile + k * 256 + threadIdx.x;
+      bool flag = false;
+      key[k] = 0;
+      if (i < n) {
+        key[k] = a.skey[(size_t)i * a.key_stride];
+        flag = i == 0 || key[k] != a.skey[(size_t)(i - 1) * a.key_stride];
+      }
+      ballot[k] = __ballot_sync(0xFFFFFFFFu, flag);
+      if (lane == 0) word_base[k * 8 + warp] = __popc(ballot[k]);
     }
-    const uint32_t inc = warp_incl_scan(c);
     __syncthreads();
-    if (lane_id() == 31) warp_tot[threadIdx.x >> 5] = inc;
+    if (warp == 0) {  // exclusive scan over the 64 words
+      const uint32_t c0 = word_base[lane], c1 = word_base[32 + lane];
+      const uint32_t i0 = warp_incl_scan(c0);
+      const uint32_t tot0 = __shfl_sync(0xFFFFFFFFu, i0, 31);
+      const uint32_t i1 = warp_incl_scan(c1);
+      word_base[lane] = i0 - c0;
+      word_base[32 + lane] = tot0 + i1 - c1;
+    }
     __syncthreads();
-    uint32_t row = a.tile_cnt[tile] + inc - c;
-    for (uint32_t w = 0; w < (threadIdx.x >> 5); ++w) row += warp_tot[w];
+    const uint32_t tile_row = a.tile_cnt[tile];
 #pragma unroll
     for (int k = 0; k < kRowsTile / 256; ++k) {
-      if (flags & (1u << k)) {
-        const uint32_t key = a.skey[i0 + k];
-        a.row_start[row] = i0 + k;
-        a.row_key[row] = key;
-        if (key < nk) { a.row_of_kid[key] = row; ++solo_rows; }
-        ++row;
+      if (ballot[k] & (1u << lane)) {
+        const uint32_t row = tile_row + word_base[k * 8 + warp] + __popc(ballot[k] & lanemask_lt());
+        a.row_start[row] = tile * kRowsTile + k * 256 + threadIdx.x;
+        a.row_key[row] = key[k];
+        if (key[k] < nk) { a.row_of_kid[key[k]] = row; ++solo_rows; }
       }
     }
+    __syncthreads();
   }
   solo_rows = warp_sum(solo_rows);
-  if (lane_id() == 0 && solo_rows) atomicAdd(&a.ctl->ticket2, solo_rows);  // ticket2 = number of solo rows
+  if (lane == 0 && solo_rows) atomicAdd(&a.ctl->ticket2, solo_rows);  // ticket2 = number of solo rows
 }
 
 // ---------------------------------------------------------------------------------------------------------

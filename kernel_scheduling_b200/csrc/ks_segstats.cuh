@@ -45,7 +45,8 @@ struct LargeRow {
 };
 
 struct SegArgs {
-  const uint32_t* lane[kLanes];
+  const uint32_t* lane[kLanes];  // value i of lane l is lane[l][i * stride]
+  uint32_t stride;
   int n_lanes;
   const uint32_t* row_start;
   const uint32_t* n_rows_dev;
@@ -134,8 +135,9 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
       for (int l = 0; l < a.n_lanes; ++l) { st->sum[l] = 0; st->mn[l] = 0; st->mx[l] = 0; st->lo[l] = 0; st->hi[l] = 0; }
     } else if (cnt <= 4) {
       for (int l = 0; l < a.n_lanes; ++l) {
-        const uint32_t* v = a.lane[l] + s;
-        uint32_t x0 = v[0], x1 = cnt > 1 ? v[1] : 0xFFFFFFFFu, x2 = cnt > 2 ? v[2] : 0xFFFFFFFFu, x3 = cnt > 3 ? v[3] : 0xFFFFFFFFu;
+        const uint32_t* v = a.lane[l] + (size_t)s * a.stride;
+        const uint32_t st1 = a.stride;
+        uint32_t x0 = v[0], x1 = cnt > 1 ? v[st1] : 0xFFFFFFFFu, x2 = cnt > 2 ? v[2 * st1] : 0xFFFFFFFFu, x3 = cnt > 3 ? v[3 * st1] : 0xFFFFFFFFu;
         const unsigned long long sum = (unsigned long long)x0 + (cnt > 1 ? x1 : 0u) + (cnt > 2 ? x2 : 0u) + (cnt > 3 ? x3 : 0u);
         uint32_t t;
 #define KS_CSWAP(p, q) t = min(p, q); q = max(p, q); p = t;
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
     RowStats* st = a.stats + row;
     for (int l = 0; l < a.n_lanes; ++l) {
       const bool have = lane < cnt;
-      const uint32_t v = have ? a.lane[l][s + lane] : 0u;
+      const uint32_t v = have ? a.lane[l][(size_t)(s + lane) * a.stride] : 0u;
       const unsigned long long sum = warp_sum64(v);
       const uint32_t mx = warp_max(v);
       const uint32_t sorted = bitonic_sort32(have ? v : 0xFFFFFFFFu);
@@ -195,11 +197,12 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
     const uint32_t row = a.mid_rows[t / a.n_lanes];
     const int l = (int)(t % a.n_lanes);
     const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
-    const uint32_t* vals = a.lane[l] + s;
+    const uint32_t* vals = a.lane[l] + (size_t)s * a.stride;
+    const uint32_t vs = a.stride;
     unsigned long long sum = 0;
     uint32_t mn = 0xFFFFFFFFu, mx = 0;
     for (uint32_t i = lane; i < cnt; i += 32) {
-      const uint32_t v = vals[i];
+      const uint32_t v = vals[(size_t)i * vs];
       sum += v;
       mn = min(mn, v);
       mx = max(mx, v);
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
         for (int i = 0; i < 8; ++i) hist[lane * 8 + i] = 0;
         __syncwarp();
         for (uint32_t i = lane; i < cnt; i += 32) {
-          const uint32_t u = vals[i] - mn;
+          const uint32_t u = vals[(size_t)i * vs] - mn;
           if (matches_prefix(u, prefix, hi_bit)) atomicAdd(&hist[(u >> shift) & ((1u << nb) - 1u)], 1u);
         }
         __syncwarp();
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
         // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
         uint32_t le = 0, next = 0xFFFFFFFFu;
         for (uint32_t i = lane; i < cnt; i += 32) {
-          const uint32_t v = vals[i];
+          const uint32_t v = vals[(size_t)i * vs];
           le += v <= lo;
           if (v > lo) next = min(next, v);
         }
@@ -261,12 +264,17 @@ __global__ void __launch_bounds__(256) k_segL_reduce(const SegArgs a) {
     LargeRow* L = a.large + a.chunk_row[c];
     const uint32_t off = a.chunk_idx[c] * kLargeChunk;
     const uint32_t m = min(kLargeChunk, L->cnt - off);
+    if (off == 0) {  // the row's first chunk clears the row's histograms for the selection rounds
+      uint32_t* gh = a.large_hist + (size_t)a.chunk_row[c] * 2 * kLanes * 256;
+      for (uint32_t i = threadIdx.x; i < 2 * kLanes * 256; i += blockDim.x) gh[i] = 0;
+    }
     for (int l = 0; l < a.n_lanes; ++l) {
-      const uint32_t* vals = a.lane[l] + L->start + off;
+      const uint32_t* vals = a.lane[l] + (size_t)(L->start + off) * a.stride;
+      const uint32_t vs = a.stride;
       unsigned long long sum = 0;
       uint32_t mn = 0xFFFFFFFFu, mx = 0;
       for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const uint32_t v = vals[i];
+        const uint32_t v = vals[(size_t)i * vs];
         sum += v;
         mn = min(mn, v);
         mx = max(mx, v);
@@ -294,8 +302,6 @@ __global__ void __launch_bounds__(256) k_segL_init(const SegArgs a) {
   if (t >= n_large * 2 * kLanes) return;
   LargeRow* L = a.large + t / (2 * kLanes);
   const int v = (int)(t % (2 * kLanes)), l = v >> 1, which = v & 1;
-  uint32_t* gh = a.large_hist + (size_t)t * 256;
-  for (int i = 0; i < 256; ++i) gh[i] = 0;
   if (l >= a.n_lanes) { L->hi_bit[v] = -1; L->prefix[v] = 0; L->k[v] = 0; return; }
   L->prefix[v] = 0;
   L->k[v] = which ? (L->cnt >> 1) : ((L->cnt - 1) >> 1);
@@ -324,9 +330,10 @@ __global__ void __launch_bounds__(256) k_segL_hist(const SegArgs a) {
       if (hb0 < 0 && hb1 < 0) continue;
       const uint32_t p0 = L->prefix[2 * l], p1 = L->prefix[2 * l + 1], mn = L->mn[l];
       const int nb0 = min(8, hb0 + 1), sh0 = hb0 + 1 - nb0, nb1 = min(8, hb1 + 1), sh1 = hb1 + 1 - nb1;
-      const uint32_t* vals = a.lane[l] + L->start + off;
+      const uint32_t* vals = a.lane[l] + (size_t)(L->start + off) * a.stride;
+      const uint32_t vs = a.stride;
       for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const uint32_t u = vals[i] - mn;
+        const uint32_t u = vals[(size_t)i * vs] - mn;
         if (hb0 >= 0 && matches_prefix(u, p0, hb0)) atomicAdd(&sh[2 * l][(u >> sh0) & ((1u << nb0) - 1u)], 1u);
         if (hb1 >= 0 && matches_prefix(u, p1, hb1)) atomicAdd(&sh[2 * l + 1][(u >> sh1) & ((1u << nb1) - 1u)], 1u);
       }

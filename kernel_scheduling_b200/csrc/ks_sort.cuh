@@ -1,7 +1,7 @@
 // ks_sort.cuh -- K2: stable least-significant-digit radix sort, one sweep over the data per 8-bit digit.
 //
 // Per pass every CTA takes tiles of 256 x ITEMS keys from a ticket counter (so a tile only ever waits for tiles
-// that already started), ranks the keys of a tile by digit with warp match operations and per-warp digit
+// that already started), ranks the keys of a tile by digit with warp ballots (one per digit bit) and per-warp digit
 // counters in shared memory, learns the number of equal digits in all earlier tiles by decoupled look-back over
 // a per-tile status array (aggregate / inclusive-prefix words with the flag in the top two bits), stages keys
 // and payload lanes in shared memory in digit order and writes them out in runs.  One histogram kernel in front
@@ -47,27 +47,52 @@ __device__ __forceinline__ uint32_t digit_of(KeyT k, int shift, uint32_t mask) {
   return (uint32_t)(k >> shift) & mask;
 }
 
+// Lanes of the warp whose digit equals this lane's digit, among the lanes of `valid_lanes`.  One ballot per digit
+// bit: the vote unit keeps up with the issue rate, the match instruction does not.
+template <int BITS = 8>
+__device__ __forceinline__ uint32_t match_digit(uint32_t d, uint32_t valid_lanes) {
+  uint32_t same = valid_lanes;
+#pragma unroll
+  for (int b = 0; b < BITS; ++b) {
+    const bool bit = (d >> b) & 1u;
+    const uint32_t vote = __ballot_sync(0xFFFFFFFFu, bit);
+    same &= bit ? vote : ~vote;
+  }
+  return same;
+}
+
 // ---- histogram of every pass's digits in one read of the keys
 template <typename KeyT>
-__global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ keys, const uint32_t* n_dev, uint32_t n, int begin_bit, int end_bit,
-                                                    uint32_t* __restrict__ hist /*[passes][256]*/) {
+__global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ keys, uint32_t stride, const uint32_t* n_dev, uint32_t n, int begin_bit,
+                                                    int end_bit, uint32_t* __restrict__ hist /*[passes][256]*/) {
   __shared__ uint32_t sh[8 * 256];
   if (n_dev) n = *n_dev;
   const int passes = (end_bit - begin_bit + 7) / 8;
   for (int i = threadIdx.x; i < passes * 256; i += blockDim.x) sh[i] = 0;
   __syncthreads();
-  const uint32_t stride = gridDim.x * blockDim.x;
+  const uint32_t gstride = gridDim.x * blockDim.x;
   // whole warps iterate together so that the match below always sees 32 lanes
   const uint32_t n_round = (n + 31u) & ~31u;
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
-    const bool valid = i < n;
-    const KeyT k = valid ? keys[i] : (KeyT)0;
-    for (int p = 0; p < passes; ++p) {
-      const int shift = begin_bit + 8 * p;
-      const int bits = min(8, end_bit - shift);
-      const uint32_t d = digit_of(k, shift, (1u << bits) - 1u);
-      const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? d : 0xFFFFu);
-      if (valid && (same & lanemask_lt()) == 0) atomicAdd(&sh[p * 256 + d], (uint32_t)__popc(same));
+  // four independent loads per thread and iteration: the loop is bound by load latency, not by arithmetic
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n_round; i0 += 4 * gstride) {
+    KeyT k[4];
+    bool valid[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t i = i0 + u * gstride;
+      valid[u] = i < n;
+      k[u] = valid[u] ? keys[(size_t)i * stride] : (KeyT)0;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u * gstride >= n_round) break;  // warp-uniform
+      for (int p = 0; p < passes; ++p) {
+        const int shift = begin_bit + 8 * p;
+        const int bits = min(8, end_bit - shift);
+        const uint32_t d = digit_of(k[u], shift, (1u << bits) - 1u);
+        const uint32_t same = match_digit(d, __ballot_sync(0xFFFFFFFFu, valid[u]));
+        if (valid[u] && (same & lanemask_lt()) == 0) atomicAdd(&sh[p * 256 + d], (uint32_t)__popc(same));
+      }
     }
   }
   __syncthreads();
@@ -132,7 +157,7 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
       const uint32_t li = wbase + i * 32 + lane;
       const bool valid = li < tile_n;
       const uint32_t d = digit_of(key[i], a.shift, dmask);
-      const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? d : 0xFFFFu);
+      const uint32_t same = match_digit(d, __ballot_sync(0xFFFFFFFFu, valid));
       const uint32_t before = __popc(same & lanemask_lt());
       uint32_t pre = 0;
       if (valid) pre = wh[d];
@@ -228,6 +253,133 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
       }
     }
   }
+}
+
+// ---- one pass over 16-byte items {key, three payload words}: the sample stream of the pair table.  Same scheme as
+// above; an item travels as one 128-bit load, one 128-bit shared-memory staging store and one 128-bit store, so even a
+// run of two equal digits fills a whole 32-byte sector.
+struct SortPass16Args {
+  const uint4* in;
+  uint4* out;
+  const uint32_t* n_dev;
+  uint32_t n;
+  int shift;
+  int bits;
+  const uint32_t* gbase;
+  uint32_t* lookback;
+  uint32_t* ticket;
+  uint32_t* err;
+};
+
+template <int ITEMS>
+__global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass16Args a) {
+  constexpr int TILE = kSortThreads * ITEMS;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* s_items = reinterpret_cast<uint4*>(smem_raw);                       // [TILE]
+  uint32_t* warp_hist = reinterpret_cast<uint32_t*>(s_items + TILE);          // [warps][256]
+  uint32_t* s_gpos = warp_hist + kSortWarps * 256;                            // [256]
+  uint32_t* s_misc = s_gpos + 256;                                            // [16]
+
+  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t ntiles = (n + TILE - 1) / TILE;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const uint32_t dmask = (1u << a.bits) - 1u;
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) s_misc[0] = atomicAdd(a.ticket, 1u);
+    for (int i = tid; i < kSortWarps * 256; i += kSortThreads) warp_hist[i] = 0;
+    __syncthreads();
+    const uint32_t tile = s_misc[0];
+    if (tile >= ntiles) break;
+    const uint32_t tile_base = tile * TILE;
+    const uint32_t tile_n = min((uint32_t)TILE, n - tile_base);
+
+    uint4 item[ITEMS];
+    uint32_t rank[ITEMS];
+    const uint32_t wbase = warp * 32 * ITEMS;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      item[i] = li < tile_n ? a.in[tile_base + li] : make_uint4(0, 0, 0, 0);
+    }
+    uint32_t* wh = warp_hist + warp * 256;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      const bool valid = li < tile_n;
+      const uint32_t d = (item[i].x >> a.shift) & dmask;
+      const uint32_t same = match_digit(d, __ballot_sync(0xFFFFFFFFu, valid));
+      const uint32_t before = __popc(same & lanemask_lt());
+      uint32_t pre = 0;
+      if (valid) pre = wh[d];
+      __syncwarp();
+      if (valid && before == 0) wh[d] = pre + __popc(same);
+      __syncwarp();
+      rank[i] = pre + before;
+    }
+    __syncthreads();
+    {
+      const uint32_t d = tid;
+      uint32_t acc = 0;
+#pragma unroll
+      for (int w = 0; w < kSortWarps; ++w) {
+        const uint32_t t = warp_hist[w * 256 + d];
+        warp_hist[w * 256 + d] = acc;
+        acc += t;
+      }
+      uint32_t excl = 0;
+      volatile uint32_t* lb = a.lookback + (size_t)tile * 256 + d;
+      if (tile == 0) {
+        *lb = acc | kFlagPrefix;
+      } else {
+        *lb = acc | kFlagAgg;
+        uint32_t t = tile - 1, spins = 0;
+        while (true) {
+          const uint32_t v = ld_volatile_u32(a.lookback + (size_t)t * 256 + d);
+          const uint32_t f = v & kFlagMask;
+          if (f == 0) {
+            if (++spins > kSpinLimit) { atomicOr(a.err, kErrWait); break; }
+            __nanosleep(20);
+            continue;
+          }
+          excl += v & kCountMask;
+          if (f == kFlagPrefix || t == 0) break;
+          --t;
+        }
+        *lb = ((excl + acc) & kCountMask) | kFlagPrefix;
+      }
+      const uint32_t inc = warp_incl_scan(acc);
+      if (lane == 31) s_misc[1 + warp] = inc;
+      __syncthreads();
+      uint32_t off = 0;
+      for (uint32_t w = 0; w < warp; ++w) off += s_misc[1 + w];
+      const uint32_t dstart = off + inc - acc;
+      s_gpos[d] = a.gbase[d] + excl - dstart;
+#pragma unroll
+      for (int w = 0; w < kSortWarps; ++w) warp_hist[w * 256 + d] += dstart;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t li = wbase + i * 32 + lane;
+      if (li < tile_n) s_items[rank[i] + wh[(item[i].x >> a.shift) & dmask]] = item[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t si = i * kSortThreads + tid;
+      if (si < tile_n) {
+        const uint4 it = s_items[si];
+        a.out[s_gpos[(it.x >> a.shift) & dmask] + si] = it;
+      }
+    }
+  }
+}
+
+template <int ITEMS>
+constexpr size_t sort16_smem_bytes() {
+  return (size_t)kSortThreads * ITEMS * sizeof(uint4) + (kSortWarps * 256 + 256 + 16) * sizeof(uint32_t);
 }
 
 template <typename KeyT, typename ValT, int ITEMS>
