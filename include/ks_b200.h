@@ -130,6 +130,20 @@ int64_t ks_hash_keys(ks_handle* h, const void* records, uint64_t n, uint32_t fla
 int64_t ks_sort_pairs_u64(ks_handle* h, uint64_t* keys, uint64_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags);
 int64_t ks_sort_pairs_u32(ks_handle* h, uint32_t* keys, uint32_t* vals, uint64_t n, int begin_bit, int end_bit, uint32_t flags);
 
+/* The same sort for callers that must not allocate device memory (no counterpart in the reference: its post-processing
+ * is host-side pandas).  Meant for code living inside another program's memory budget -- a plugin of a serving process
+ * whose caching allocator owns the device, a watchdog thread that may not wait on the allocator's lock.  keys and vals
+ * are DEVICE pointers on the current device (vals may be NULL), sorted in place on `stream`; no handle is needed.
+ * All scratch is a fixed device array inside the library (about 8.3 MB per GPU, held until the process exits), so:
+ *   - at most KS_NOALLOC_MAX_ITEMS items; more is refused with -KS_ERR_TOO_LARGE;
+ *   - the call never calls cudaMalloc / cudaFree or anything that allocates;
+ *   - every call on a device shares that array: two calls whose GPU work overlaps (different streams or threads) race;
+ *   - the first call on a device looks up the array's device address and sets kernel attributes; make that first call
+ *     before any stream capture starts.
+ * Returns n, or a negative status (text in ks_last_error(NULL)).  The call synchronises `stream` before returning. */
+#define KS_NOALLOC_MAX_ITEMS (1u << 20)
+int64_t ks_sort_pairs_u32_noalloc(void* stream, uint32_t* keys, uint32_t* vals, uint64_t n, int begin_bit, int end_bit);
+
 /* K1+K2: the launches grouped by key: (key, start_ns) of every record in (key, start_ns) order. */
 int64_t ks_sort_launches(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t* keys_out, uint64_t* start_out);
 

@@ -58,6 +58,7 @@ KS_API = [
     ("ks_hash_keys", [c_void_p, c_void_p, c_uint64, c_uint32, c_void_p], c_int64),
     ("ks_sort_pairs_u64", [c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int, c_uint32], c_int64),
     ("ks_sort_pairs_u32", [c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int, c_uint32], c_int64),
+    ("ks_sort_pairs_u32_noalloc", [c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int], c_int64),
     ("ks_sort_launches", [c_void_p, c_void_p, c_uint64, c_uint32, c_void_p, c_void_p], c_int64),
     ("ks_join_overlaps", [c_void_p, c_void_p, c_uint64, c_uint32, c_void_p, c_void_p, c_uint64], c_int64),
     ("ks_segment_stats", [c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p], c_int64),

@@ -927,3 +927,105 @@ int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Sorting without allocating.  Callers that run inside somebody else's memory budget -- a plugin of a serving process
+// whose allocator owns the whole device, a monitoring thread that must never take the device allocator's lock, code
+// that runs while the application has allocation frozen -- cannot let this library call cudaMalloc.  For them the
+// scratch of the radix sort (the second key/value buffer of the ping-pong, the per-tile look-back words, the digit
+// histograms and the error word) lives in one file-scope device array of fixed size.  Every GPU that loads the library
+// carries these ~8.3 MB until the process exits.
+constexpr uint32_t kNoAllocMaxItems = 1u << 20;
+constexpr int kNoAllocItems = 16;                                                   // keys per thread of the pass kernel
+constexpr uint32_t kNoAllocTile = kSortThreads * kNoAllocItems;
+constexpr uint32_t kNoAllocTiles = kNoAllocMaxItems / kNoAllocTile;
+constexpr uint32_t kNaAltKeys = 0;                                                  // word offsets inside the array
+constexpr uint32_t kNaAltVals = kNaAltKeys + kNoAllocMaxItems;
+constexpr uint32_t kNaLookback = kNaAltVals + kNoAllocMaxItems;                     // [tiles][256] + ticket (+ padding)
+constexpr uint32_t kNaHist = kNaLookback + kNoAllocTiles * 256 + 64;                // [8][256] counts, [8][256] offsets
+constexpr uint32_t kNaErr = kNaHist + 2 * 8 * 256;
+constexpr uint32_t kNaWords = kNaErr + 64;
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNaWords];
+
+namespace {
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a handle for the runtime, not
+// an address a kernel can use; the address comes from cudaGetSymbolAddress, asked once per device with it current.
+uint32_t* g_noalloc_ptr[64] = {};
+}  // namespace
+
+extern "C" int64_t ks_sort_pairs_u32_noalloc(void* stream, uint32_t* keys, uint32_t* vals, uint64_t n, int begin_bit, int end_bit) {
+  if ((!keys && n) || begin_bit < 0 || end_bit > 32 || begin_bit > end_bit) { g_null_error = "ks_sort_pairs_u32_noalloc: bad argument"; return -KS_ERR_ARG; }
+  if (n > kNoAllocMaxItems) {
+    g_null_error = "ks_sort_pairs_u32_noalloc: " + std::to_string(n) + " items, the fixed scratch holds at most " + std::to_string(kNoAllocMaxItems);
+    return -KS_ERR_TOO_LARGE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) { g_null_error = std::string("ks_sort_pairs_u32_noalloc: cudaGetDevice: ") + cudaGetErrorString(e); return -KS_ERR_CUDA; }
+  constexpr size_t smem = sort_smem_bytes<uint32_t, uint32_t, kNoAllocItems>();
+  if (!g_noalloc_ptr[dev]) {  // set-up, first call on this device
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) { g_null_error = std::string("ks_sort_pairs_u32_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e); return -KS_ERR_CUDA; }
+    e = cudaFuncSetAttribute(k_onesweep_pass<uint32_t, uint32_t, 1, kNoAllocItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_onesweep_pass<uint32_t, uint32_t, 0, kNoAllocItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { g_null_error = std::string("ks_sort_pairs_u32_noalloc: cudaFuncSetAttribute: ") + cudaGetErrorString(e); return -KS_ERR_CUDA; }
+    g_noalloc_ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  const int passes = (end_bit - begin_bit + 7) / 8;
+  if (n == 0 || passes == 0) return (int64_t)n;
+  uint32_t* base = g_noalloc_ptr[dev];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint32_t* kbuf[2] = {keys, base + kNaAltKeys};
+  uint32_t* vbuf[2] = {vals, base + kNaAltVals};
+  uint32_t* lookback = base + kNaLookback;
+  uint32_t* hist = base + kNaHist;
+  uint32_t* gbase = hist + 8 * 256;
+  uint32_t* err = base + kNaErr;
+  const uint32_t ntiles = (uint32_t)((n + kNoAllocTile - 1) / kNoAllocTile);
+  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+#define KS_NA(call)                                                                                                       \
+  do {                                                                                                                    \
+    cudaError_t e__ = (call);                                                                                             \
+    if (e__ != cudaSuccess) { g_null_error = std::string("ks_sort_pairs_u32_noalloc: " #call ": ") + cudaGetErrorString(e__); return -KS_ERR_CUDA; } \
+  } while (0)
+  // the array keeps whatever the last call left: counters and flags that must start at zero are cleared here
+  KS_NA(cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), st));
+  KS_NA(cudaMemsetAsync(err, 0, 64 * sizeof(uint32_t), st));
+  int sm_count = 148;
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)sm_count * 6);
+  k_radix_hist<uint32_t><<<hist_grid, 256, 0, st>>>(keys, 1u, nullptr, (uint32_t)n, begin_bit, end_bit, hist);
+  k_radix_scan_hist<<<1, 256, 0, st>>>(hist, gbase, passes);
+  int cur = 0;
+  for (int p = 0; p < passes; ++p) {
+    KS_NA(cudaMemsetAsync(lookback, 0, lb_bytes, st));
+    SortPassArgs<uint32_t, uint32_t, 1> a1{};
+    a1.kin = kbuf[cur]; a1.kout = kbuf[cur ^ 1];
+    a1.vin[0] = vbuf[cur]; a1.vout[0] = vbuf[cur ^ 1];
+    a1.n_dev = nullptr; a1.n = (uint32_t)n;
+    a1.shift = begin_bit + 8 * p; a1.bits = std::min(8, end_bit - a1.shift);
+    a1.gbase = gbase + p * 256; a1.lookback = lookback; a1.ticket = lookback + (size_t)ntiles * 256; a1.err = err;
+    const int grid = (int)std::min<uint32_t>(ntiles, (uint32_t)sm_count * 4);
+    if (vals) {
+      k_onesweep_pass<uint32_t, uint32_t, 1, kNoAllocItems><<<grid, kSortThreads, smem, st>>>(a1);
+    } else {
+      SortPassArgs<uint32_t, uint32_t, 0> a0{};
+      a0.kin = a1.kin; a0.kout = a1.kout; a0.n_dev = nullptr; a0.n = a1.n; a0.shift = a1.shift; a0.bits = a1.bits;
+      a0.gbase = a1.gbase; a0.lookback = a1.lookback; a0.ticket = a1.ticket; a0.err = a1.err;
+      k_onesweep_pass<uint32_t, uint32_t, 0, kNoAllocItems><<<grid, kSortThreads, smem, st>>>(a0);
+    }
+    cur ^= 1;
+  }
+  KS_NA(cudaGetLastError());
+  if (cur == 1) {  // an odd number of passes ends in the scratch: bring the result home
+    KS_NA(cudaMemcpyAsync(keys, kbuf[1], n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+    if (vals) KS_NA(cudaMemcpyAsync(vals, vbuf[1], n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+  }
+  uint32_t h_err = 0;
+  KS_NA(cudaMemcpyAsync(&h_err, err, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+  KS_NA(cudaStreamSynchronize(st));
+#undef KS_NA
+  if (h_err & kErrWait) { g_null_error = "ks_sort_pairs_u32_noalloc: a bounded device-side wait ran out"; return -KS_ERR_WAIT; }
+  return (int64_t)n;
+}
