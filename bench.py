@@ -155,13 +155,21 @@ def main():
 
     spec = trace.config(args.workload)
     n_rec = args.records or min(spec.n_records, args.max_records)
-    # weak scaling: every rank owns one time window of n_rec records (its own seed = its own stretch of the trace)
-    spec = trace.config(args.workload, n_rec, seed=spec.seed + 1000 * rank)
-    rec = trace.generate(spec)
+    # weak scaling: every rank owns one window of n_rec records of the same workload (same key tables, its own launches);
+    # the windows follow one another in time, so the job is ONE trace of world * n_rec records
+    spec = trace.config(args.workload, n_rec)
+    rec = trace.generate(spec, window=rank)
+    if world > 1:
+        span = torch.tensor([int(rec["start_ns"][-1] - rec["start_ns"][0]) + 1], dtype=torch.int64, device="cuda")
+        spans = [torch.zeros_like(span) for _ in range(world)]
+        dist.all_gather(spans, span)
+        shift = sum(int(x[0]) for x in spans[:rank])
+        rec["start_ns"] += np.uint64(shift)
+        rec["end_ns"] += np.uint64(shift)
     host = torch.from_numpy(rec.view(np.uint8).reshape(-1)).pin_memory()
     dev = host.cuda(non_blocking=False)
     stream = torch.cuda.Stream()
-    builder = PairTableBuilder(device=local_rank, stream=stream.cuda_stream, max_records=n_rec)
+    builder = PairTableBuilder(device=local_rank, stream=stream.cuda_stream, max_records=n_rec + 8192)
 
     def barrier():
         torch.cuda.synchronize()
@@ -169,8 +177,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    from kernel_scheduling_b200 import parallel
+
     def step_device():
-        return builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+        if world == 1:
+            return builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+        with torch.cuda.stream(stream):
+            keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev), rank, world, on_device=True))
+        builder.info = {"n_pairs": 0, "n_rows": table_t.numel() // 128, "n_keys": keys_t.numel() // 72}
+        return table_t.numel() // 128
 
     # ---- device-resident: warm-up, then K timed steps
     for _ in range(max(args.warmup, 3)):
@@ -188,25 +203,40 @@ def main():
         for _ in range(args.steps):
             step_device()
             for k in stage_names:
-                stage_ms[k] += builder.info[k]
+                stage_ms[k] += builder.info.get(k, 0.0)
         e1.record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    ms_dev = e0.elapsed_time(e1)
     launches = builder.launch_count - launches0
+    if world > 1:
+        # per-kernel times for the roofline: the same kernels over the local window alone, after the timed region
+        for _ in range(3):
+            builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+            for k in stage_names:
+                stage_ms[k] += builder.info[k] * args.steps / 3.0
+        torch.cuda.synchronize()
+    ms_dev = e0.elapsed_time(e1)
     info = dict(builder.info)
 
     # ---- end to end through the public API: host records in, host tables out
     e2e = None
     if not args.no_e2e:
         rec_pinned = host.numpy().view(RECORD_DTYPE)
+
+        def step_e2e():
+            if world == 1:
+                return builder.build(rec_pinned, time_ordered=True)
+            with torch.cuda.stream(stream):
+                d = host.to("cuda", non_blocking=True)
+                return parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, d), rank, world))
+
         for _ in range(2):
-            keys, pairs = builder.build(rec_pinned, time_ordered=True)
+            keys, pairs = step_e2e()
         barrier()
         t0 = time.perf_counter()
         e2e_steps = max(1, min(args.steps, 5))
         for _ in range(e2e_steps):
-            keys, pairs = builder.build(rec_pinned, time_ordered=True)
+            keys, pairs = step_e2e()
         torch.cuda.synchronize()
         ms_e2e = 1e3 * (time.perf_counter() - t0)
         e2e = {"ms": ms_e2e, "steps": e2e_steps, "h2d": rec.nbytes, "d2h": keys.nbytes + pairs.nbytes}
@@ -231,24 +261,30 @@ def main():
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured copy bandwidth (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s"
         per_stage = {k: v / args.steps for k, v in stage_ms.items()}
-        dom = max((k for k in per_stage if k != "ms_total"), key=lambda k: per_stage[k])
-        P, T, N = info["n_pairs"], info["n_rows"], n_rec
-        alg_bytes = {"ms_decode": 64.0 * N, "ms_join": 16.0 * N + 16.0 * P, "ms_sort": 16.0 * P * 2, "ms_reduce": 16.0 * P + 72.0 * T}
-        dom_bytes = alg_bytes.get(dom, 64.0 * N)
+        P, T, N = info.get("n_pairs", 0), info["n_rows"], n_rec
+        # the dominant KERNEL: decode and join are single launches; the sort and the statistics are several launches each
+        # (their per-launch times are smaller, see profiles/launch_list_*), so the choice is between the first two.
+        # algorithmic bytes per launch: decode reads 48 B and writes 16 B per record; the join reads the 16-byte timeline
+        # entry of every record and writes one 16-byte sample per overlapping pair.
+        # traffic: dram__bytes_read + dram__bytes_write of one ncu capture at 4 M records, scaled by the record count
+        # (both kernels stream the trace once, so traffic grows in proportion): 59.6 B/record and 16.9 B/record.
+        cand = {"ms_decode": ("k_decode_hash", 64.0 * N, 59.6 * N), "ms_join": ("k_join", 16.0 * N + 16.0 * P, 16.9 * N)}
+        dom = max(cand, key=lambda k: per_stage[k])
+        dom_name, dom_bytes, dom_traffic = cand[dom]
         achieved = dom_bytes / (per_stage[dom] * 1e-3) / 1e9
         path_bytes = 48.0 * N + 32.0 * P + 96.0 * T
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32/u64 integer, f64 tables",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {n_rec} records per GPU, {info['n_keys']} keys, {P} overlapping pairs, {T} table rows",
+            "config": {"workload": f"{args.workload}: {n_rec} records per GPU, {info['n_keys']} keys, {P} overlapping pairs per GPU, {T} table rows"
+                                   + ("" if world == 1 else f"; one trace of {total_records} records in {world} time windows, samples exchanged by all-to-all, whole table on every rank"),
                        "records_per_gpu": n_rec, "l2": "inputs (48 B x records) larger than L2; no flush needed", "input_order": "start_ns-ordered (verified on device)"},
             "clocks": clocks,
             "gpu_launches": int(launches),
             "stage_ms": per_stage,
-            "roofline": {"bound": "hbm", "kernel": {"ms_decode": "k_decode_hash", "ms_join": "k_join", "ms_sort": "k_onesweep_pass (+histogram)",
-                                                     "ms_reduce": "k_rows_* + k_seg_*"}.get(dom, dom),
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+            "roofline": {"bound": "hbm", "kernel": dom_name,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": dom_traffic, "peak_source": peak_src,
                          "path_algorithmic_bytes": path_bytes, "path_frac": path_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
         }
         if e2e:

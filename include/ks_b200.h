@@ -168,6 +168,26 @@ int64_t ks_count_batches(ks_handle* h, const uint64_t* start1, uint64_t n1, cons
 int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double* launches, const double* values, uint64_t rows, uint32_t cols,
                               uint32_t n_groups, uint32_t flags, double* out_total, double* out_means);
 
+/* ---- multi-GPU session: one process and one handle per GPU, each owning one window of the start-ordered trace.
+ * The reference has no multi-GPU path; these phases are what kernel_scheduling_b200/parallel.py runs between its
+ * collectives (all-gather of keys, sum of counts, all-to-all of samples, all-gather of solo times and table shards).
+ * All pointers are DEVICE pointers.  A pair of overlapping launches is reduced by the rank whose key range holds its
+ * (key_a, key_b); it is produced by the rank that owns its LATER launch. */
+#define KS_MG_HALO_MAX 4096    /* launches of the previous window that may still run when this one begins */
+#define KS_MG_HIST_BINS 4096   /* bins of the sample-key histogram the splitters are chosen from */
+int64_t ks_mg_begin(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags);      /* K1 over the window */
+int64_t ks_mg_tail(ks_handle* h, void* out_records, uint64_t capacity);                         /* launches reaching into the next window, start order */
+int64_t ks_mg_halo(ks_handle* h, const void* halo_records, uint64_t n_halo);                    /* the previous rank's tail */
+int64_t ks_mg_local_keys(ks_handle* h, uint64_t* keys_out, void* words_out, uint64_t capacity); /* distinct keys + 32 bytes of launch fields each */
+int64_t ks_mg_global_keys(ks_handle* h, const uint64_t* keys, const void* words, uint64_t n);   /* every rank's keys -> same dense ids everywhere; returns K */
+int64_t ks_mg_counts(ks_handle* h, uint64_t* launches, uint64_t* solo, int import);             /* per-key launch counts by dense id, out (0) or in (1) */
+int64_t ks_mg_samples(ks_handle* h);                                                            /* solo samples + K3; returns the local sample count */
+int64_t ks_mg_key_histogram(ks_handle* h, uint64_t* hist, uint32_t* shift_out);                 /* hist[KS_MG_HIST_BINS] of sort key >> shift */
+int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, void* send, uint64_t capacity, uint64_t* counts);
+int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n);                            /* K2 + K4 over the received samples */
+int64_t ks_mg_solo(ks_handle* h, double* solo, int import);                                     /* solo times by dense id, out (0) or in (1) */
+int64_t ks_mg_finalize(ks_handle* h);                                                           /* tables of this rank's key range; then ks_copy_*_rows */
+
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
  * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */
 int64_t ks_function_base(const char* symbol, char* out, uint64_t capacity);

@@ -64,6 +64,18 @@ KS_API = [
     ("ks_segment_stats", [c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p], c_int64),
     ("ks_count_batches", [c_void_p, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(c_uint64)], c_int64),
     ("ks_combine_duplicates", [c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p], c_int64),
+    ("ks_mg_begin", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
+    ("ks_mg_tail", [c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_halo", [c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_local_keys", [c_void_p, c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_global_keys", [c_void_p, c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_counts", [c_void_p, c_void_p, c_void_p, c_int], c_int64),
+    ("ks_mg_samples", [c_void_p], c_int64),
+    ("ks_mg_key_histogram", [c_void_p, c_void_p, POINTER(c_uint32)], c_int64),
+    ("ks_mg_partition", [c_void_p, POINTER(c_uint32), c_uint32, c_uint32, c_void_p, c_uint64, POINTER(c_uint64)], c_int64),
+    ("ks_mg_reduce", [c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_solo", [c_void_p, c_void_p, c_int], c_int64),
+    ("ks_mg_finalize", [c_void_p], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),
 ]
 

@@ -9,6 +9,7 @@
 #include "ks_decode.cuh"
 #include "ks_dict.cuh"
 #include "ks_join.cuh"
+#include "ks_mg.cuh"
 #include "ks_misc.cuh"
 #include "ks_reduce.cuh"
 #include "ks_sort.cuh"
@@ -55,6 +56,12 @@ struct ks_handle {
   // results of the last ks_build_table
   uint64_t n_pair_rows = 0, n_key_rows = 0;
   uint64_t launches = 0;  // kernels launched so far (cumulative)
+
+  // multi-GPU session state (ks_mg_*)
+  const unsigned char* mg_rec = nullptr;
+  uint64_t mg_n_owned = 0, mg_n_halo = 0, mg_nk = 0, mg_n_samples = 0;
+  uint32_t mg_flags = 0;
+  int mg_cur = 0;
   cudaEvent_t ev[12]{};
 };
 
@@ -245,10 +252,11 @@ int reset_run(ks_handle* h) {
 }
 
 // K1 over device records -> timeline set 0, solo stream, dictionary.  keys_out optional (device).
-int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, unsigned long long* keys_out) {
-  KS_ENSURE(h, h->tl_start[0], std::max<size_t>(n * 8, 16));
-  KS_ENSURE(h, h->tl_dm[0], std::max<size_t>(n * 8, 16));
-  KS_ENSURE(h, h->solo_stream, std::max<size_t>(n * 8, 16));
+int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, unsigned long long* keys_out, uint64_t out_offset = 0, uint64_t reserve = 0,
+               int halo = 0) {
+  KS_ENSURE(h, h->tl_start[0], std::max<size_t>((n + reserve) * 8, 16));
+  KS_ENSURE(h, h->tl_dm[0], std::max<size_t>((n + reserve) * 8, 16));
+  KS_ENSURE(h, h->solo_stream, std::max<size_t>((n + reserve) * 8, 16));
   if (n == 0) return 0;
   DecodeArgs a{};
   a.records = reinterpret_cast<const unsigned char*>(d_records);
@@ -258,8 +266,9 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
   a.dict_words = h->dict_words;
   a.dict_launches = h->dict_launches;
   a.dict_solo = h->dict_solo;
-  a.tl_start = as<unsigned long long>(h->tl_start[0]);
-  a.tl_dm = as<unsigned long long>(h->tl_dm[0]);
+  a.tl_start = as<unsigned long long>(h->tl_start[0]) + out_offset;
+  a.tl_dm = as<unsigned long long>(h->tl_dm[0]) + out_offset;
+  a.halo = halo;
   a.solo_stream = as<unsigned long long>(h->solo_stream);
   a.keys_out = keys_out;
   a.ctl = h->d_ctl;
@@ -317,11 +326,12 @@ uint64_t sample_capacity(ks_handle* h) {
   return std::min<uint64_t>(h->samples[0].cap, h->samples[1].cap) / 16;
 }
 
-int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b) {
+int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b, uint64_t tl_offset = 0, uint64_t n_halo = 0) {
   if (n == 0) return 0;
   JoinArgs j{};
-  j.tl_start = as<unsigned long long>(h->tl_start[tl]);
-  j.tl_dm = as<unsigned long long>(h->tl_dm[tl]);
+  j.tl_start = as<unsigned long long>(h->tl_start[tl]) + tl_offset;
+  j.tl_dm = as<unsigned long long>(h->tl_dm[tl]) + tl_offset;
+  j.n_halo = n_halo;
   j.kid_of_slot = h->kid_of_slot;
   j.n = n;
   j.samples = as<uint4>(h->samples[0]);
@@ -924,6 +934,295 @@ int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double*
   const int st = status_of_err(h->h_ctl->err, false);
   if (st) return fail(h, st, std::string("ks_combine_duplicates: ") + ks_status_string(st));
   return (int64_t)n_groups;
+}
+
+}  // extern "C"
+
+// =========================================================================================================
+// Multi-GPU session: one handle per rank, the caller (kernel_scheduling_b200/parallel.py) runs the collectives between
+// the phases.  All pointers are DEVICE pointers on the handle's device.
+namespace {
+
+int mg_zero_u32(ks_handle* h, uint32_t* field, size_t count = 1) {
+  KS_CUDA(h, cudaMemsetAsync(field, 0, count * sizeof(uint32_t), h->stream));
+  return 0;
+}
+
+int mg_status(ks_handle* h, const char* what) {
+  const int st = status_of_err(h->h_ctl->err, true);
+  if (st) return fail(h, st, std::string(what) + ": " + ks_status_string(st));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t ks_mg_begin(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags) {
+  if (!h || (!records && n_owned) || (flags & ~KS_KEY_TYPE)) return -KS_ERR_ARG;
+  if (n_owned + kHaloMax >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_begin: too many records for one rank");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n_owned && (reinterpret_cast<uintptr_t>(records) & 15u)) return fail(h, KS_ERR_ARG, "ks_mg_begin: records must be 16-byte aligned");
+  h->mg_rec = reinterpret_cast<const unsigned char*>(records);
+  h->mg_n_owned = n_owned;
+  h->mg_n_halo = 0;
+  h->mg_flags = flags;
+  h->n_pair_rows = h->n_key_rows = 0;
+  { int r = reset_run(h); if (r) return r; }
+  // sized once for window + halo so that the halo decode cannot trigger a (content-losing) regrowth
+  return run_decode(h, records, n_owned, flags, nullptr, kHaloMax, 2 * (uint64_t)kHaloMax, 0);
+}
+
+int64_t ks_mg_tail(ks_handle* h, void* out_records, uint64_t capacity) {
+  if (!h || (!out_records && capacity)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
+  uint32_t* idx = as<uint32_t>(h->tmp[0]);
+  uint32_t* count = idx + kHaloMax;
+  { int r = mg_zero_u32(h, count); if (r) return r; }
+  if (h->mg_n_owned) {
+    k_tail_select<<<1, 1024, 0, h->stream>>>(as<unsigned long long>(h->tl_start[0]) + kHaloMax, as<unsigned long long>(h->tl_dm[0]) + kHaloMax,
+                                             (uint32_t)h->mg_n_owned, idx, kHaloMax, count, h->d_ctl);
+    ++h->launches;
+  }
+  uint32_t n_tail = 0;
+  KS_CUDA(h, cudaMemcpyAsync(&n_tail, count, 4, cudaMemcpyDeviceToHost, h->stream));
+  { int r = read_ctl(h); if (r) return r; }
+  { int r = mg_status(h, "ks_mg_tail"); if (r) return r; }
+  if (n_tail > kHaloMax || n_tail > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_tail: more launches reach into the next window than the halo can hold");
+  if (n_tail) {
+    k_gather_records<<<(n_tail * 3 + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const uint4*>(h->mg_rec), idx, n_tail, reinterpret_cast<uint4*>(out_records));
+    ++h->launches;
+    KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  }
+  return (int64_t)n_tail;
+}
+
+int64_t ks_mg_halo(ks_handle* h, const void* halo_records, uint64_t n_halo) {
+  if (!h || (!halo_records && n_halo)) return -KS_ERR_ARG;
+  if (n_halo > kHaloMax) return fail(h, KS_ERR_CAPACITY, "ks_mg_halo: halo larger than the reserve");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  h->mg_n_halo = n_halo;
+  if (!n_halo) return 0;
+  // the halo records must be in start order themselves; the tail selection emits them unordered, so sort is the caller's job
+  return run_decode(h, halo_records, n_halo, h->mg_flags, nullptr, kHaloMax - n_halo, h->mg_n_owned + 2 * (uint64_t)kHaloMax - n_halo, 1);
+}
+
+int64_t ks_mg_local_keys(ks_handle* h, uint64_t* keys_out, void* words_out, uint64_t capacity) {
+  if (!h || !keys_out || !words_out) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+  DictArgs d{};
+  d.dict_keys = h->dict_keys; d.dkeys = h->dkeys; d.dslot = h->dslot; d.drank = h->drank; d.kid_of_slot = h->kid_of_slot;
+  d.slot_of_kid = h->slot_of_kid; d.keys_sorted = h->keys_sorted; d.ctl = h->d_ctl;
+  k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
+  ++h->launches;
+  { int r = read_ctl(h); if (r) return r; }
+  { int r = mg_status(h, "ks_mg_local_keys"); if (r) return r; }
+  const uint32_t nk = h->h_ctl->n_keys;
+  if (nk > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_local_keys: buffer too small");
+  if (nk) {
+    k_export_keys<<<(nk + 255) / 256, 256, 0, h->stream>>>(h->dkeys, h->dslot, h->dict_words, nk, reinterpret_cast<unsigned long long*>(keys_out),
+                                                           reinterpret_cast<uint4*>(words_out));
+    ++h->launches;
+    KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  }
+  return (int64_t)nk;
+}
+
+int64_t ks_mg_global_keys(ks_handle* h, const uint64_t* keys, const void* words, uint64_t n) {
+  if (!h || ((!keys || !words) && n)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n) {
+    k_dict_insert<<<(unsigned)((n + 255) / 256), 256, 0, h->stream>>>(reinterpret_cast<const unsigned long long*>(keys), reinterpret_cast<const uint4*>(words),
+                                                                      (uint32_t)n, h->dict_keys, h->dict_words, h->d_ctl);
+    ++h->launches;
+  }
+  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+  KS_CUDA(h, cudaMemsetAsync(h->drank, 0, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  { int r = run_dict(h); if (r) return r; }
+  { int r = read_ctl(h); if (r) return r; }
+  { int r = mg_status(h, "ks_mg_global_keys"); if (r) return r; }
+  h->mg_nk = h->h_ctl->n_keys;
+  return (int64_t)h->mg_nk;
+}
+
+int64_t ks_mg_counts(ks_handle* h, uint64_t* launches, uint64_t* solo, int import) {
+  if (!h || !launches || !solo) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (h->mg_nk) {
+    k_counts_by_kid<<<(unsigned)((h->mg_nk + 255) / 256), 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, (uint32_t)h->mg_nk,
+                                                                               reinterpret_cast<unsigned long long*>(launches), reinterpret_cast<unsigned long long*>(solo), import);
+    ++h->launches;
+  }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)h->mg_nk;
+}
+
+int64_t ks_mg_samples(ks_handle* h) {
+  if (!h) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const uint64_t n = h->mg_n_halo + h->mg_n_owned;
+  uint64_t cap = sample_capacity(h);
+  if (cap < std::max<uint64_t>(2 * n, 1u << 16)) { cap = std::max<uint64_t>(2 * n, 1u << 16); int r = ensure_samples(h, cap); if (r) return r; }
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    SoloArgs s{};
+    s.solo_stream = as<unsigned long long>(h->solo_stream);
+    s.kid_of_slot = h->kid_of_slot;
+    s.samples = as<uint4>(h->samples[0]);
+    s.capacity = cap;
+    s.ctl = h->d_ctl;
+    k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+    ++h->launches;
+    { int r = run_join(h, 0, n, cap, nullptr, nullptr, kHaloMax - h->mg_n_halo, h->mg_n_halo); if (r) return r; }
+    { int r = read_ctl(h); if (r) return r; }
+    { int r = mg_status(h, "ks_mg_samples"); if (r) return r; }
+    h->mg_n_samples = h->h_ctl->n_pairs;
+    if (h->mg_n_samples <= cap) break;
+    if (h->mg_n_samples >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_samples: 2^30 samples or more");
+    if (attempt == 1) return fail(h, KS_ERR_CAPACITY, "ks_mg_samples: sample stream still too small");
+    cap = h->mg_n_samples + h->mg_n_samples / 16;
+    int r = ensure_samples(h, cap);
+    if (r) return r;
+  }
+  return (int64_t)h->mg_n_samples;
+}
+
+int64_t ks_mg_key_histogram(ks_handle* h, uint64_t* hist, uint32_t* shift_out) {
+  if (!h || !hist || !shift_out) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const int bits = bit_length(h->mg_nk + h->mg_nk * h->mg_nk);
+  const uint32_t shift = bits > 12 ? (uint32_t)(bits - 12) : 0u;
+  *shift_out = shift;
+  KS_CUDA(h, cudaMemsetAsync(hist, 0, (size_t)kKeyHistBins * 8, h->stream));
+  if (h->mg_n_samples) {
+    k_key_hist<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), (uint32_t)h->mg_n_samples, shift, reinterpret_cast<unsigned long long*>(hist));
+    ++h->launches;
+  }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)kKeyHistBins;
+}
+
+// splitters[r-1] = first histogram bin of rank r (n_ranks - 1 ascending values).  Writes the samples grouped by destination
+// rank into send (capacity items); counts[r] = items for rank r.
+int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, void* send, uint64_t capacity, uint64_t* counts) {
+  if (!h || !counts || n_ranks == 0 || n_ranks > 16 || (n_ranks > 1 && !splitters) || (!send && capacity)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const uint64_t n = h->mg_n_samples;
+  if (n > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_partition: send buffer too small");
+  constexpr int ITEMS = 8;
+  constexpr int TILE = kSortThreads * ITEMS;
+  const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
+  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  KS_ENSURE(h, h->lookback, lb_bytes);
+  KS_ENSURE(h, h->hist, 2 * 8 * 256 * sizeof(uint32_t));
+  uint32_t* hist = as<uint32_t>(h->hist);
+  uint32_t* gbase = hist + 8 * 256;
+  KS_CUDA(h, cudaMemsetAsync(hist, 0, 256 * sizeof(uint32_t), h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+  SortPass16Args a{};
+  a.by_dest = 1;
+  a.n_split = n_ranks - 1;
+  a.split_shift = shift;
+  for (uint32_t i = 0; i + 1 < n_ranks; ++i) a.split[i] = splitters[i];
+  a.in = as<uint4>(h->samples[0]);
+  a.out = reinterpret_cast<uint4*>(send);
+  a.n = (uint32_t)n;
+  a.shift = 0;
+  a.bits = 8;
+  a.gbase = gbase;
+  a.lookback = as<uint32_t>(h->lookback);
+  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+  a.err = &h->d_ctl->err;
+  for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = 0;
+  if (n) {
+    constexpr size_t smem = sort16_smem_bytes<ITEMS>();
+    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_dest_hist<<<h->sm_count * 2, 256, 0, h->stream>>>(a, hist);
+    k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, 1);
+    k_onesweep_pass16<ITEMS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * 5), kSortThreads, smem, h->stream>>>(a);
+    h->launches += 3;
+    uint32_t hc[16];
+    KS_CUDA(h, cudaMemcpyAsync(hc, hist, sizeof(hc), cudaMemcpyDeviceToHost, h->stream));
+    { int r = read_ctl(h); if (r) return r; }
+    { int r = mg_status(h, "ks_mg_partition"); if (r) return r; }
+    for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = hc[r];
+  }
+  return (int64_t)n;
+}
+
+int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n) {
+  if (!h || (!samples && n)) return -KS_ERR_ARG;
+  if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_reduce: 2^30 samples or more");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = ensure_samples(h, std::max<uint64_t>(n, 16)); if (r) return r; }
+  if (n) KS_CUDA(h, cudaMemcpyAsync(h->samples[0].p, samples, n * 16, cudaMemcpyDeviceToDevice, h->stream));
+  // counters of the row / statistics kernels start from zero
+  { int r = mg_zero_u32(h, &h->d_ctl->n_rows, 2); if (r) return r; }
+  { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
+  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->scratch0, 0, 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  const uint64_t nk = h->mg_nk;
+  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk));
+  if (cur < 0) return cur;
+  h->mg_cur = cur;
+  h->mg_n_samples = n;
+  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
+  const uint32_t* sorted = as<uint32_t>(h->samples[cur]);
+  const uint32_t* lanes[kLanes] = {sorted + 1, sorted + 2, sorted + 3};
+  { int r = run_rows_and_stats(h, sorted, 4, lanes, kLanes, n, max_rows); if (r) return r; }
+  if (nk) {
+    k_solo_ns<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(as<RowStats>(h->stats), h->row_of_kid, (uint32_t)nk, h->solo_ns);
+    ++h->launches;
+  }
+  { int r = read_ctl(h); if (r) return r; }
+  { int r = mg_status(h, "ks_mg_reduce"); if (r) return r; }
+  return (int64_t)h->h_ctl->n_rows;
+}
+
+int64_t ks_mg_solo(ks_handle* h, double* solo, int import) {
+  if (!h || !solo) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (h->mg_nk) {
+    if (import) KS_CUDA(h, cudaMemcpyAsync(h->solo_ns, solo, h->mg_nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+    else KS_CUDA(h, cudaMemcpyAsync(solo, h->solo_ns, h->mg_nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+  }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)h->mg_nk;
+}
+
+int64_t ks_mg_finalize(ks_handle* h) {
+  if (!h) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const uint64_t nk = h->mg_nk, n = h->mg_n_samples;
+  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
+  KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
+  FinalArgs f{};
+  f.stats = as<RowStats>(h->stats);
+  f.row_start = as<uint32_t>(h->row_start);
+  f.row_key = as<uint32_t>(h->row_key);
+  f.row_of_kid = h->row_of_kid;
+  f.slot_of_kid = h->slot_of_kid;
+  f.keys_sorted = h->keys_sorted;
+  f.dict_words = h->dict_words;
+  f.dict_launches = h->dict_launches;
+  f.dict_solo = h->dict_solo;
+  f.solo_ns = h->solo_ns;
+  f.solo_given = 1;
+  f.key_rows = h->key_rows;
+  f.pair_rows = as<ks_pair_row>(h->pair_rows);
+  f.max_pair_rows = max_rows;
+  f.ctl = h->d_ctl;
+  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
+  k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
+  h->launches += nk ? 2 : 1;
+  KS_CUDA(h, cudaGetLastError());
+  { int r = read_ctl(h); if (r) return r; }
+  { int r = mg_status(h, "ks_mg_finalize"); if (r) return r; }
+  h->n_key_rows = h->h_ctl->n_keys;
+  h->n_pair_rows = h->h_ctl->n_rows - h->h_ctl->ticket2;
+  return (int64_t)h->n_pair_rows;
 }
 
 }  // extern "C"

@@ -37,6 +37,7 @@ struct DecodeArgs {
   unsigned long long* tl_dm;      // [n] duration | meta << 32
   unsigned long long* solo_stream;  // [n] slot | duration << 32, first Control::n_solo entries valid
   unsigned long long* keys_out;   // optional [n]: the key of every record
+  int halo;                       // 1: records of a neighbouring time window -- keyed and placed on the timeline, but not counted
   Control* ctl;
 };
 
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
     // one dictionary probe per distinct key of the warp
     const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? key : 0ull);
     const uint32_t leader = __ffs(same) - 1;
-    const uint32_t solo_ballot = __ballot_sync(0xFFFFFFFFu, valid && solo);
+    const uint32_t solo_ballot = __ballot_sync(0xFFFFFFFFu, valid && solo && !a.halo);
     uint32_t slot = 0;
     if (valid && lane == leader) {
       bool inserted;
@@ -165,10 +166,10 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
         a.dict_words[2 * (size_t)slot + 1] = k1;
       }
       // launch counts: CTA-local cache first, global atomics when the cache is crowded
-      const uint32_t c_all = __popc(same), c_solo = __popc(same & solo_ballot);
+      const uint32_t c_all = a.halo ? 0u : __popc(same), c_solo = __popc(same & solo_ballot);
       uint32_t h = (slot * 2654435761u) >> (32 - 10);
-      bool cached = false;
-      for (int probe = 0; probe < 8; ++probe) {
+      bool cached = c_all == 0;
+      for (int probe = 0; probe < 8 && !cached; ++probe) {
         const uint32_t old = atomicCAS(&cc_slot[h], 0u, slot + 1);
         if (old == 0u || old == slot + 1) {
           atomicAdd(&cc_cnt[h], c_all);
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
 
     if (valid) {
       if (end < start || end - start >= 0x80000000ull) err |= kErrRecord;
-      if (start < prev) err |= kErrUnordered;
+      if (start < prev && !(a.halo && r == 0)) err |= kErrUnordered;
       const uint32_t dur = (uint32_t)(end - start);
       const uint32_t meta = slot | (w1.w & (kMetaSoloBit | 0xFF000000u));
       a.tl_start[r] = start;

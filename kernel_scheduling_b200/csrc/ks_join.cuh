@@ -37,6 +37,8 @@ struct JoinArgs {
   uint32_t* idx_a;  // stage API: positions instead of samples (may be null)
   uint32_t* idx_b;
   uint64_t capacity;  // entries the sample stream (or idx arrays) can hold
+  uint64_t n_halo;    // the first n_halo timeline entries belong to the previous time window: a pair is emitted only if
+                      // its later member is at or behind this position (single owner across windows)
   Control* ctl;
 };
 
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
       while (run_off[li + 1] <= q) { ++li; ei = entry(li); }
       const uint32_t lj = li + 1 + (q - run_off[li]);
       const JoinEntry ej = entry(lj);
-      if (!join_pair_ok(ei, ej)) continue;
+      if (!join_pair_ok(ei, ej) || t0 + lj < a.n_halo) continue;
       if (pass == 0) ++n_valid;
       else { join_emit<kIndexOutput>(a, out, ei, ej, t0 + li, t0 + lj, nk); ++out; }
     }
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
         for (uint64_t j = t0 + wn; j < a.n; ++j) {
           const JoinEntry ej = join_entry(a, j);
           if (ej.start >= end_s) break;
-          if (!join_pair_ok(es, ej)) continue;
+          if (!join_pair_ok(es, ej) || j < a.n_halo) continue;
           if (pass == 1) join_emit<kIndexOutput>(a, s_base + spill_before + spill_cnt, es, ej, t0 + sl, j, nk);
           ++spill_cnt;
         }

@@ -145,6 +145,7 @@ struct FinalArgs {
   const uint32_t* dict_launches;
   const uint32_t* dict_solo;
   double* solo_ns;        // [kMaxKeys + 1]
+  int solo_given;         // 1: solo_ns already holds every key's solo time (multi-GPU: merged over the ranks)
   ks_key_row* key_rows;   // [kMaxKeys + 1]
   ks_pair_row* pair_rows; // [max_pair_rows]
   uint32_t max_pair_rows;
@@ -159,7 +160,8 @@ __global__ void __launch_bounds__(256) k_finalize_keys(const FinalArgs a) {
   const uint4 w0 = a.dict_words[2 * (size_t)slot], w1 = a.dict_words[2 * (size_t)slot + 1];
   const uint32_t row = a.row_of_kid[kid];
   double solo = __longlong_as_double(0x7FF8000000000000ll);
-  if (row != 0xFFFFFFFFu) solo = ((double)a.stats[row].lo[0] + (double)a.stats[row].hi[0]) * 0.5;
+  if (a.solo_given) solo = a.solo_ns[kid];
+  else if (row != 0xFFFFFFFFu) solo = ((double)a.stats[row].lo[0] + (double)a.stats[row].hi[0]) * 0.5;
   a.solo_ns[kid] = solo;
   ks_key_row r;
   r.key = a.keys_sorted[kid];

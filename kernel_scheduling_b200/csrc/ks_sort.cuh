@@ -259,6 +259,11 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
 // above; an item travels as one 128-bit load, one 128-bit shared-memory staging store and one 128-bit store, so even a
 // run of two equal digits fills a whole 32-byte sector.
 struct SortPass16Args {
+  // by_dest != 0: the "digit" is the destination rank of the item = number of splitters <= (key >> split_shift)
+  uint32_t by_dest;
+  uint32_t n_split;
+  uint32_t split_shift;
+  uint32_t split[15];
   const uint4* in;
   uint4* out;
   const uint32_t* n_dev;
@@ -270,6 +275,25 @@ struct SortPass16Args {
   uint32_t* ticket;
   uint32_t* err;
 };
+
+__device__ __forceinline__ uint32_t digit16(const SortPass16Args& a, uint32_t key, uint32_t dmask) {
+  if (!a.by_dest) return (key >> a.shift) & dmask;
+  const uint32_t b = key >> a.split_shift;
+  uint32_t d = 0;
+  for (uint32_t i = 0; i < a.n_split; ++i) d += a.split[i] <= b;
+  return d;
+}
+
+// histogram of the destination digit (multi-GPU partition): hist[256]
+__global__ void __launch_bounds__(256) k_dest_hist(const SortPass16Args a, uint32_t* __restrict__ hist) {
+  __shared__ uint32_t sh[16];
+  if (threadIdx.x < 16) sh[threadIdx.x] = 0;
+  __syncthreads();
+  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&sh[digit16(a, a.in[i].x, 0xFFu)], 1u);
+  __syncthreads();
+  if (threadIdx.x < 16 && sh[threadIdx.x]) atomicAdd(&hist[threadIdx.x], sh[threadIdx.x]);
+}
 
 template <int ITEMS>
 __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass16Args a) {
@@ -308,7 +332,7 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass
     for (int i = 0; i < ITEMS; ++i) {
       const uint32_t li = wbase + i * 32 + lane;
       const bool valid = li < tile_n;
-      const uint32_t d = (item[i].x >> a.shift) & dmask;
+      const uint32_t d = digit16(a, item[i].x, dmask);
       const uint32_t same = match_digit(d, __ballot_sync(0xFFFFFFFFu, valid));
       const uint32_t before = __popc(same & lanemask_lt());
       uint32_t pre = 0;
@@ -363,7 +387,7 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       const uint32_t li = wbase + i * 32 + lane;
-      if (li < tile_n) s_items[rank[i] + wh[(item[i].x >> a.shift) & dmask]] = item[i];
+      if (li < tile_n) s_items[rank[i] + wh[digit16(a, item[i].x, dmask)]] = item[i];
     }
     __syncthreads();
 #pragma unroll
@@ -371,7 +395,7 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass
       const uint32_t si = i * kSortThreads + tid;
       if (si < tile_n) {
         const uint4 it = s_items[si];
-        a.out[s_gpos[(it.x >> a.shift) & dmask] + si] = it;
+        a.out[s_gpos[digit16(a, it.x, dmask)] + si] = it;
       }
     }
   }

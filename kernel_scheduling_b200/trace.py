@@ -86,9 +86,14 @@ def _zipf_choice(rng, n_keys, s, size):
     return np.minimum(np.searchsorted(cdf, rng.random(size)), n_keys - 1)
 
 
-def generate(spec: TraceSpec, interleave_solo: bool = False) -> np.ndarray:
-    """-> records (RECORD_DTYPE), ordered by start_ns."""
-    rng = np.random.default_rng(spec.seed)
+def generate(spec: TraceSpec, interleave_solo: bool = False, window: int = 0) -> np.ndarray:
+    """-> records (RECORD_DTYPE), ordered by start_ns.
+
+    ``window`` selects an independent stretch of the same workload: the key tables (names, grids, typical durations)
+    depend on ``spec.seed`` only, the launches on (seed, window).  Multi-GPU runs give every rank its own window.
+    """
+    key_rng = np.random.default_rng(spec.seed)
+    rng = np.random.default_rng([spec.seed, 7919 + window])
     nt = len(spec.tenants)
     # launches per tenant: equal wall-clock span => count ~ utilisation / mean duration
     mean_dur = np.array([t.dur_median_ns * np.exp(0.5 * t.dur_sigma**2) for t in spec.tenants])
@@ -102,12 +107,12 @@ def generate(spec: TraceSpec, interleave_solo: bool = False) -> np.ndarray:
     for t, (ts, n) in enumerate(zip(spec.tenants, n_per)):
         n = int(n)
         k = ts.n_keys
-        key_name = name_base + rng.permutation(k).astype(np.uint32)
+        key_name = name_base + key_rng.permutation(k).astype(np.uint32)
         name_base += k
-        key_grid = np.stack([rng.integers(ts.grid_range[0], ts.grid_range[1] + 1, k), rng.integers(1, 3, k), np.ones(k, np.int64)], axis=1)
-        key_block = np.stack([rng.choice(ts.block_choices, k), np.ones(k, np.int64), np.ones(k, np.int64)], axis=1)
-        key_smem = rng.choice([0, 0, 0, 16384, 49152, 98304], k)
-        key_dur = ts.dur_median_ns * np.exp(ts.dur_sigma * rng.standard_normal(k))
+        key_grid = np.stack([key_rng.integers(ts.grid_range[0], ts.grid_range[1] + 1, k), key_rng.integers(1, 3, k), np.ones(k, np.int64)], axis=1)
+        key_block = np.stack([key_rng.choice(ts.block_choices, k), np.ones(k, np.int64), np.ones(k, np.int64)], axis=1)
+        key_smem = key_rng.choice([0, 0, 0, 16384, 49152, 98304], k)
+        key_dur = ts.dur_median_ns * np.exp(ts.dur_sigma * key_rng.standard_normal(k))
         kix = _zipf_choice(rng, k, ts.zipf_s, n)
         solo = rng.random(n) < spec.solo_fraction
         d = key_dur[kix] * np.exp(spec.launch_jitter_sigma * rng.standard_normal(n))

@@ -1,0 +1,79 @@
+"""GPU: the multi-rank path through the C ABI (ks_mg_*).  All ranks of a world run one after the other in this process
+on one GPU (no kernel ever waits for another rank, so this is safe), collectives are fulfilled in-process; with two or
+more GPUs present the same path also runs as real NCCL ranks."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from kernel_scheduling_b200 import parallel, trace
+from kernel_scheduling_b200.pair_table import PairTableBuilder
+from kernel_scheduling_b200.records import pack_records
+from oracle import pair_table_oracle as O
+from tests.helpers import assert_tables_match
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def sharded_gpu(rec, world, key_type=False):
+    wins = parallel.split_windows(len(rec), world)
+    builders = [PairTableBuilder(device=0) for _ in range(world)]
+    try:
+        stages = [parallel.GpuStages(b, torch.from_numpy(rec[lo:hi].view(np.uint8).reshape(-1).copy()).cuda()) for b, (lo, hi) in zip(builders, wins)]
+        return parallel.run_in_process([parallel.build_steps(s, r, world, key_type) for r, s in enumerate(stages)])
+    finally:
+        for b in builders:
+            b.close()
+
+
+@pytest.mark.parametrize("cfg,n,world", [("c1", 60_000, 1), ("c2", 300_000, 2), ("c3", 200_000, 4), ("c4", 150_000, 8)])
+def test_sharded_table_equals_oracle(cfg, n, world):
+    rec = trace.generate(trace.config(cfg, n))
+    okeys, opairs = O.build_pair_table(rec)
+    for keys, pairs in sharded_gpu(rec, world):
+        assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_sharded_equals_single_gpu_bit_for_bit(builder):
+    rec = trace.generate(trace.config("c3", 120_000), interleave_solo=True)
+    keys1, pairs1 = builder.build(rec, time_ordered=True)
+    for keys, pairs in sharded_gpu(rec, 3):
+        assert keys.tobytes() == keys1.tobytes()
+        for c in pairs1.dtype.names:
+            if c.startswith(("sum", "mean")):
+                assert np.allclose(pairs[c], pairs1[c], rtol=1e-6, atol=0, equal_nan=True)
+            else:
+                assert np.array_equal(pairs[c], pairs1[c], equal_nan=True), c
+
+
+def test_launch_spanning_windows_and_type_keys():
+    n = 4000
+    start = np.arange(n, dtype=np.uint64) * 100 + 1000
+    dur = np.full(n, 60, dtype=np.uint64)
+    tenant = 1 + (np.arange(n) % 2)
+    tenant[3], dur[3] = 0, 100 * n
+    rec = pack_records(tenant, np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, np.zeros(n, bool), start, start + dur)
+    okeys, opairs = O.build_pair_table(rec, key_mode=O.KEY_TYPE)
+    for keys, pairs in sharded_gpu(rec, 4, key_type=True):
+        assert_tables_match(keys, pairs, okeys, opairs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_nccl_ranks(tmp_path):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "nccl_rank.py"), str(r), "2", str(port), str(tmp_path)], cwd=ROOT, env=env) for r in range(2)]
+    assert [p.wait(timeout=300) for p in procs] == [0, 0]
+    rec = trace.generate(trace.config("c3", 400_000))
+    okeys, opairs = O.build_pair_table(rec)
+    for r in range(2):
+        d = np.load(tmp_path / f"rank{r}.npz")
+        assert_tables_match(d["keys"], d["pairs"], okeys, opairs)
