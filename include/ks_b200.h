@@ -185,6 +185,7 @@ int64_t ks_mg_samples(ks_handle* h);                                            
 int64_t ks_mg_key_histogram(ks_handle* h, uint64_t* hist, uint32_t* shift_out);                 /* hist[KS_MG_HIST_BINS] of sort key >> shift */
 int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, void* send, uint64_t capacity, uint64_t* counts);
 int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n);                            /* K2 + K4 over the received samples */
+int64_t ks_mg_row_count(ks_handle* h);                                                          /* pair rows of this rank's range (after ks_mg_reduce) */
 int64_t ks_mg_solo(ks_handle* h, double* solo, int import);                                     /* solo times by dense id, out (0) or in (1) */
 int64_t ks_mg_finalize(ks_handle* h);                                                           /* tables of this rank's key range; then ks_copy_*_rows */
 

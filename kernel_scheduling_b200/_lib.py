@@ -74,6 +74,7 @@ KS_API = [
     ("ks_mg_key_histogram", [c_void_p, c_void_p, POINTER(c_uint32)], c_int64),
     ("ks_mg_partition", [c_void_p, POINTER(c_uint32), c_uint32, c_uint32, c_void_p, c_uint64, POINTER(c_uint64)], c_int64),
     ("ks_mg_reduce", [c_void_p, c_void_p, c_uint64], c_int64),
+    ("ks_mg_row_count", [c_void_p], c_int64),
     ("ks_mg_solo", [c_void_p, c_void_p, c_int], c_int64),
     ("ks_mg_finalize", [c_void_p], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),

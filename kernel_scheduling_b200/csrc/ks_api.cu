@@ -1181,6 +1181,11 @@ int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n) {
   return (int64_t)h->h_ctl->n_rows;
 }
 
+int64_t ks_mg_row_count(ks_handle* h) {
+  if (!h) return -KS_ERR_ARG;
+  return (int64_t)h->h_ctl->n_rows - (int64_t)h->h_ctl->ticket2;  // as read back at the end of ks_mg_reduce
+}
+
 int64_t ks_mg_solo(ks_handle* h, double* solo, int import) {
   if (!h || !solo) return -KS_ERR_ARG;
   KS_CUDA(h, cudaSetDevice(h->device));

@@ -4,16 +4,16 @@ The start-ordered trace is cut into ``world`` windows by record position.  The s
 them (NCCL through ``torch.distributed`` on GPUs):
 
   1. K1 over the own window; pick the launches that are still running at the window's last start (``tail``)
-  2. all-gather of the tails  -> rank r decodes rank r-1's tail as its halo (a pair of overlapping launches is
-     PRODUCED by the rank that owns its later launch, so every pair is produced exactly once)
-  3. all-gather of the distinct keys -> every dictionary holds every key -> identical dense key ids on every rank
-  4. sum of the per-key launch counts
-  5. solo samples + K3 join; coarse histogram of the samples' sort keys; sum -> splitters that cut the key space
-     into ``world`` ranges of about equal sample count (a whole table row always lands on one rank)
-  6. partition by destination; all-to-all of the samples (samples travel, not partial tables: the median is exact)
-  7. K2 sort + K4 statistics of the received range; max-merge of the solo times (each key's solo row lives on
-     exactly one rank); tables
-  8. all-gather of the table shards: ranges are ordered, so their concatenation in rank order is the sorted table
+  2. all-gather of [tails | distinct keys]: every dictionary then holds every key -> identical dense key ids on
+     every rank; rank r decodes the earlier ranks' tails that reach into its window as its halo (a pair of
+     overlapping launches is PRODUCED by the rank that owns its later launch: exactly once)
+  3. solo samples + K3 join; all-gather of [coarse histogram of the samples' sort keys | per-key launch counts]
+     -> splitters that cut the key space into ``world`` ranges of about equal sample count (a whole table row
+     always lands on one rank), and how many samples every rank will send to every other
+  4. partition by destination; all-to-all of the samples (samples travel, not partial tables: the median is exact)
+  5. K2 sort + K4 statistics of the received range; all-gather of [solo times | shard sizes] (each key's solo row
+     lives on exactly one rank); tables
+  6. all-gather of the table shards: ranges are ordered, so their concatenation in rank order is the sorted table
 
 ``build_steps`` is a generator: it yields one request per collective and is driven either by ``run_distributed``
 (torch.distributed, one process per rank) or by ``run_in_process`` (all ranks in one process, one after the other;
@@ -51,67 +51,87 @@ def choose_splitters(hist: np.ndarray, world: int) -> list[int]:
     return out
 
 
+_key_capacity = 4096  # keys per rank that fit the first exchange; grown (on every rank alike) when a rank has more
+
+
+def _u64_bytes(dev, *vals):
+    return torch.frombuffer(bytearray(b"".join(int(v).to_bytes(8, "little") for v in vals)), dtype=torch.uint8).to(dev)
+
+
+def _u64_at(buf_cpu: np.ndarray, i: int) -> int:
+    return int.from_bytes(buf_cpu[8 * i: 8 * i + 8].tobytes(), "little")
+
+
 def build_steps(stages, rank: int, world: int, key_type: bool = False, on_device: bool = False):
-    """Generator over the collectives of one rank; returns (key_rows, pair_rows) of the WHOLE table as numpy arrays
-    (``on_device``: as uint8 tensors on the stages' device, no copy to the host)."""
+    """Generator over the collectives of one rank (five per table); returns (key_rows, pair_rows) of the WHOLE table as
+    numpy arrays (``on_device``: as uint8 tensors on the stages' device, no copy to the host)."""
+    global _key_capacity
     stages.begin(key_type)
-    # -- halo
-    tail = stages.tail()  # uint8 tensor, 48 bytes per record, start order
-    padded = stages.zeros((HALO_MAX * 48 + 8,), torch.uint8)
-    padded[: tail.numel()] = tail
-    padded[HALO_MAX * 48:] = torch.tensor(list(int(tail.numel() // 48).to_bytes(8, "little")), dtype=torch.uint8, device=padded.device)
-    tails = yield ("all_gather", padded)
+    # -- collective 1: [n_tail, n_keys | tail records | distinct keys | their launch fields] of every rank
+    tail = stages.tail()               # uint8, 48 bytes per record, start order
+    keys, words = stages.local_keys()  # int64 [k], uint8 [k * 32]  (own window; halo keys arrive from their owners)
+    while True:
+        cap = _key_capacity
+        buf = stages.zeros((16 + HALO_MAX * 48 + cap * 40,), torch.uint8)
+        buf[:16] = _u64_bytes(buf.device, tail.numel() // 48, keys.numel())
+        buf[16: 16 + tail.numel()] = tail
+        k_fit = min(keys.numel(), cap)
+        if k_fit:
+            buf[16 + HALO_MAX * 48: 16 + HALO_MAX * 48 + k_fit * 8] = keys[:k_fit].contiguous().view(torch.uint8)
+        buf[16 + HALO_MAX * 48 + cap * 8: 16 + HALO_MAX * 48 + cap * 8 + k_fit * 32] = words[: k_fit * 32]
+        bufs = yield ("all_gather", buf)
+        heads = [b[:16].cpu().numpy() for b in bufs]
+        need = max(_u64_at(h, 1) for h in heads)
+        if need <= cap:
+            break
+        _key_capacity = 1 << int(need - 1).bit_length()  # every rank sees the same headers and grows alike
+    k0 = 16 + HALO_MAX * 48
+    all_k = torch.cat([b[k0: k0 + _u64_at(h, 1) * 8] for b, h in zip(bufs, heads)]).contiguous().view(torch.int64)
+    all_w = torch.cat([b[k0 + cap * 8: k0 + cap * 8 + _u64_at(h, 1) * 32] for b, h in zip(bufs, heads)])
+    n_keys = stages.global_keys(all_k, all_w)
     # the halo of rank r: launches of ANY earlier window that are still running when window r begins (a launch can span
-    # several windows); every rank holds every tail after the all-gather, the filter runs on the host (a few KB)
+    # several windows); the filter runs on the host over a few KB
     first = stages.first_start()
     parts = []
     for q in range(rank):
-        t = tails[q].cpu().numpy()
-        n_q = int.from_bytes(t[HALO_MAX * 48:].tobytes(), "little")
-        recs = np.frombuffer(t[: n_q * 48].tobytes(), dtype=RECORD_DTYPE)
-        if first is not None:
+        n_q = _u64_at(heads[q], 0)
+        if n_q and first is not None:
+            recs = np.frombuffer(bufs[q][16: 16 + n_q * 48].cpu().numpy().tobytes(), dtype=RECORD_DTYPE)
             parts.append(recs[recs["end_ns"] > np.uint64(first)])
     halo = np.concatenate(parts) if parts else np.zeros(0, dtype=RECORD_DTYPE)
     if len(halo) > HALO_MAX:
         raise _lib.KsError(_lib.ERR_CAPACITY, f"{len(halo)} launches of earlier windows reach into window {rank}; the halo holds {HALO_MAX}")
     stages.halo(stages.from_bytes(halo.tobytes()))
-    # -- global keys
-    keys, words = stages.local_keys()  # int64 [k], uint8 [k * 32]
-    counts = yield ("all_gather", stages.tensor([keys.numel()], torch.int64))
-    kmax = max(int(c[0]) for c in counts)
-    kp = stages.zeros((kmax,), torch.int64)
-    wp = stages.zeros((kmax * 32,), torch.uint8)
-    kp[: keys.numel()] = keys
-    wp[: words.numel()] = words
-    all_k = yield ("all_gather", kp)
-    all_w = yield ("all_gather", wp)
-    n_keys = stages.global_keys(torch.cat(all_k), torch.cat(all_w))  # zero keys (padding) are skipped by the insert
+    # -- samples; collective 2: [sample-key histogram | per-key launch counts] of every rank
     launches, solo = stages.counts_export()
-    launches = yield ("all_reduce_sum", launches)
-    solo = yield ("all_reduce_sum", solo)
-    stages.counts_import(launches, solo)
-    # -- samples, splitters, exchange
     stages.samples()
     hist, shift = stages.key_histogram()
-    hist = yield ("all_reduce_sum", hist)
-    splitters = choose_splitters(hist.cpu().numpy(), world)
+    gathered = yield ("all_gather", torch.cat([hist, launches, solo]))
+    hists = [g[:HIST_BINS].cpu().numpy() for g in gathered]
+    total = torch.stack(gathered).sum(dim=0)
+    stages.counts_import(total[HIST_BINS: HIST_BINS + n_keys].contiguous(), total[HIST_BINS + n_keys:].contiguous())
+    splitters = choose_splitters(np.sum(hists, axis=0), world)
+    edges = [0] + [min(x, HIST_BINS) for x in splitters] + [HIST_BINS]
+    recv_counts = [int(h[edges[rank]: edges[rank + 1]].sum()) for h in hists]  # what each rank holds for my range
+    # -- collective 3: the samples travel to the rank that owns their key range
     send, send_counts = stages.partition(splitters, shift, world)  # int32 [n, 4] grouped by destination
-    recv = yield ("all_to_all", send, send_counts)
+    recv = yield ("all_to_all", send, send_counts, recv_counts)
     stages.reduce(recv)
-    # -- solo times: each key's solo row was reduced by exactly one rank
+    # -- collective 4: [solo times | size of the table shard]; each key's solo row was reduced by exactly one rank
     solo_ns = stages.solo_export()
-    neg = torch.where(torch.isnan(solo_ns), torch.full_like(solo_ns, float("-inf")), solo_ns)
-    neg = yield ("all_reduce_max", neg)
-    stages.solo_import(torch.where(torch.isinf(neg) & (neg < 0), torch.full_like(neg, float("nan")), neg))
+    n_rows = stages.row_count()
+    got = yield ("all_gather", torch.cat([solo_ns, stages.tensor([float(n_rows)], torch.float64)]))
+    stacked = torch.stack([g[:n_keys] for g in got])
+    merged = torch.where(torch.isnan(stacked), torch.full_like(stacked, float("-inf")), stacked).max(dim=0).values
+    stages.solo_import(torch.where(torch.isinf(merged) & (merged < 0), torch.full_like(merged, float("nan")), merged))
+    sizes = [int(g[n_keys].item()) * PAIR_ROW_DTYPE.itemsize for g in got]
     stages.finalize()
     key_rows, pair_rows = stages.tables()  # uint8 tensors: this rank's key range
-    # -- the whole table on every rank
-    sizes = yield ("all_gather", stages.tensor([pair_rows.numel()], torch.int64))
-    pmax = max(int(s[0]) for s in sizes)
-    pp = stages.zeros((pmax,), torch.uint8)
+    # -- collective 5: the whole table on every rank (ranges are ordered: concatenation in rank order is the sorted table)
+    pp = stages.zeros((max(sizes),), torch.uint8)
     pp[: pair_rows.numel()] = pair_rows
     shards = yield ("all_gather", pp)
-    table = torch.cat([sh[: int(sz[0])] for sh, sz in zip(shards, sizes)])
+    table = torch.cat([sh[:sz] for sh, sz in zip(shards, sizes)])
     if on_device:
         return key_rows, table
     return (np.frombuffer(key_rows.cpu().numpy().tobytes(), dtype=KEY_ROW_DTYPE)[:n_keys].copy(),
@@ -139,11 +159,7 @@ def run_distributed(gen, group=None):
                 res = req[1].clone()
                 dist.all_reduce(res, op=dist.ReduceOp.MAX, group=group)
             elif kind == "all_to_all":
-                send, counts = req[1], [int(c) for c in req[2]]
-                ct = torch.tensor(counts, dtype=torch.int64, device=send.device)
-                rc = torch.empty_like(ct)
-                dist.all_to_all_single(rc, ct, group=group)
-                rcounts = [int(c) for c in rc.cpu().tolist()]
+                send, counts, rcounts = req[1], [int(c) for c in req[2]], [int(c) for c in req[3]]
                 res = torch.empty((sum(rcounts), send.shape[1]), dtype=send.dtype, device=send.device)
                 dist.all_to_all_single(res, send.contiguous(), output_split_sizes=rcounts, input_split_sizes=counts, group=group)
             else:
@@ -177,6 +193,7 @@ def run_in_process(gens):
             offs = [np.concatenate([[0], np.cumsum([int(c) for c in q[2]])]) for q in reqs]
             for dst in range(world):
                 res.append(torch.cat([reqs[src][1][int(offs[src][dst]): int(offs[src][dst + 1])] for src in range(world)]))
+                assert [int(c) for c in reqs[dst][3]] == [int(offs[src][dst + 1] - offs[src][dst]) for src in range(world)], "receive counts"
         else:
             raise ValueError(kind)
         for r, g in enumerate(gens):
@@ -193,6 +210,10 @@ class GpuStages:
     """One rank's compute through the C ABI (ks_mg_*).  ``records`` is a uint8 CUDA tensor of 48-byte records."""
 
     def __init__(self, builder, records: torch.Tensor):
+        if records.is_cuda and builder.stream != torch.cuda.current_stream(records.device).cuda_stream:
+            # the collectives run on torch's current stream; the library must launch on the same one, or a collective
+            # could still be writing a buffer the next phase reads
+            raise ValueError("create the PairTableBuilder with stream=torch.cuda.current_stream().cuda_stream (and keep that stream current)")
         self.b = builder
         self.lib = builder._lib
         self.h = builder._h
@@ -275,11 +296,6 @@ class GpuStages:
         self._ck(self.lib.ks_mg_partition(self.h, sp, shift, world, ctypes.c_void_p(send.data_ptr()), send.shape[0], counts), "ks_mg_partition")
         return send[: self.n_samples], [int(c) for c in counts]
 
-    def reduce(self, recv):
-        recv = recv.contiguous()
-        self._keep.append(recv)
-        self._ck(self.lib.ks_mg_reduce(self.h, self._p(recv), recv.shape[0]), "ks_mg_reduce")
-
     def solo_export(self):
         t = self.zeros((self.n_keys,), torch.float64)
         if self.n_keys:
@@ -290,6 +306,15 @@ class GpuStages:
         t = t.contiguous()
         if self.n_keys:
             self._ck(self.lib.ks_mg_solo(self.h, ctypes.c_void_p(t.data_ptr()), 1), "ks_mg_solo")
+
+    def reduce(self, recv):
+        recv = recv.contiguous()
+        self._keep.append(recv)
+        self._rows_total = self._ck(self.lib.ks_mg_reduce(self.h, self._p(recv), recv.shape[0]), "ks_mg_reduce")
+
+    def row_count(self):
+        """Pair rows of this rank's key range (known after reduce: rows minus solo rows)."""
+        return self._ck(self.lib.ks_mg_row_count(self.h), "ks_mg_row_count")
 
     def finalize(self):
         self.n_rows = self._ck(self.lib.ks_mg_finalize(self.h), "ks_mg_finalize")

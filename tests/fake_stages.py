@@ -134,6 +134,9 @@ class FakeStages:
                 v = np.sort(self.rs[st: st + c, 1].astype(np.float64))
                 self.solo_ns[k] = (v[(c - 1) // 2] + v[c // 2]) * 0.5
 
+    def row_count(self):
+        return int(sum(1 for st in self.seg if int(self.rs[st, 0]) >= self.n_keys))
+
     def solo_export(self):
         return torch.from_numpy(self.solo_ns.copy())
 

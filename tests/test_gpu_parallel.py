@@ -22,13 +22,16 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def sharded_gpu(rec, world, key_type=False):
     wins = parallel.split_windows(len(rec), world)
-    builders = [PairTableBuilder(device=0) for _ in range(world)]
-    try:
-        stages = [parallel.GpuStages(b, torch.from_numpy(rec[lo:hi].view(np.uint8).reshape(-1).copy()).cuda()) for b, (lo, hi) in zip(builders, wins)]
-        return parallel.run_in_process([parallel.build_steps(s, r, world, key_type) for r, s in enumerate(stages)])
-    finally:
-        for b in builders:
-            b.close()
+    stream = torch.cuda.Stream()  # the library and torch must share one stream (see parallel.GpuStages)
+    with torch.cuda.stream(stream):
+        builders = [PairTableBuilder(device=0, stream=stream.cuda_stream) for _ in range(world)]
+        try:
+            stages = [parallel.GpuStages(b, torch.from_numpy(rec[lo:hi].view(np.uint8).reshape(-1).copy()).cuda()) for b, (lo, hi) in zip(builders, wins)]
+            return parallel.run_in_process([parallel.build_steps(s, r, world, key_type) for r, s in enumerate(stages)])
+        finally:
+            torch.cuda.synchronize()
+            for b in builders:
+                b.close()
 
 
 @pytest.mark.parametrize("cfg,n,world", [("c1", 60_000, 1), ("c2", 300_000, 2), ("c3", 200_000, 4), ("c4", 150_000, 8)])
