@@ -354,7 +354,7 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
 }
 
 // K4 core: integer statistics of every row (three size classes, see ks_segstats.cuh)
-int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], uint32_t stride, int n_lanes, uint64_t n_values, uint32_t max_rows) {
+int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, uint64_t n_values, uint32_t max_rows) {
   const uint32_t max_large = (uint32_t)(n_values / kMidMax) + 1;
   const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
   KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
@@ -365,9 +365,9 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], uint32_
   KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->large_hist, (size_t)max_large * 2 * kLanes * 256 * 4);
   SegArgs s{};
-  for (int l = 0; l < kLanes; ++l) s.lane[l] = lanes[l];
-  s.n_lanes = n_lanes;
-  s.stride = stride;
+  s.items = items;
+  s.plain = plain;
+  s.n_lanes = items ? kLanes : 1;
   s.row_start = as<uint32_t>(h->row_start);
   s.n_rows_dev = &h->d_ctl->n_rows;
   s.max_rows = max_rows;
@@ -400,14 +400,14 @@ int run_segment_stats(ks_handle* h, const uint32_t* const lanes[kLanes], uint32_
 }
 
 // rows + segment statistics over sorted samples (set `s`), n samples
-int run_rows_and_stats(ks_handle* h, const uint32_t* skey, uint32_t stride, const uint32_t* const lanes[kLanes], int n_lanes, uint64_t n, uint32_t max_rows) {
+int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t max_rows) {
   const uint32_t max_tiles = (uint32_t)((n + kRowsTile - 1) / kRowsTile);
   KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
   KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
   KS_ENSURE(h, h->row_key, ((size_t)max_rows + 2) * 4);
   RowsArgs r{};
-  r.skey = skey;
-  r.key_stride = stride;
+  r.skey = reinterpret_cast<const uint32_t*>(items);
+  r.key_stride = 4;
   r.n_dev = nullptr;
   r.n = (uint32_t)n;
   r.tile_cnt = as<uint32_t>(h->tile_cnt);
@@ -423,7 +423,7 @@ int run_rows_and_stats(ks_handle* h, const uint32_t* skey, uint32_t stride, cons
   k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
   h->launches += 3;
   KS_CUDA(h, cudaGetLastError());
-  return run_segment_stats(h, lanes, stride, n_lanes, n, max_rows);
+  return run_segment_stats(h, items, nullptr, n, max_rows);
 }
 
 __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start, uint32_t n_rows, unsigned long long* out) {
@@ -614,9 +614,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
 
   // K4: rows, statistics, tables
   const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n_samples, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
-  const uint32_t* sorted = as<uint32_t>(h->samples[cur]);
-  const uint32_t* lanes[kLanes] = {sorted + 1, sorted + 2, sorted + 3};
-  { int r = run_rows_and_stats(h, sorted, 4, lanes, kLanes, n_samples, max_rows); if (r) return r; }
+  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n_samples, max_rows); if (r) return r; }
   cudaEventRecord(ev[8], h->stream);
   KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
   FinalArgs f{};
@@ -843,8 +841,7 @@ int64_t ks_segment_stats(ks_handle* h, const uint32_t* values, const uint64_t* o
   k_offsets_to_u32<<<(rows + 1 + 255) / 256, 256, 0, h->stream>>>(d_off, rows + 1, as<uint32_t>(h->row_start));
   h->h_ctl->n_rows = rows;
   KS_CUDA(h, cudaMemcpyAsync(&h->d_ctl->n_rows, &h->h_ctl->n_rows, 4, cudaMemcpyHostToDevice, h->stream));
-  const uint32_t* lanes1[kLanes] = {d_val, nullptr, nullptr};
-  { int r = run_segment_stats(h, lanes1, 1u, 1, n_values, rows); if (r) return r; }
+  { int r = run_segment_stats(h, nullptr, d_val, n_values, rows); if (r) return r; }
   unsigned long long* d_out = dev ? reinterpret_cast<unsigned long long*>(out) : as<unsigned long long>(h->tmp[2]);
   k_stats_to_u64<<<(rows + 255) / 256, 256, 0, h->stream>>>(as<RowStats>(h->stats), as<uint32_t>(h->row_start), rows, d_out);
   KS_CUDA(h, cudaGetLastError());
@@ -1169,9 +1166,7 @@ int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n) {
   h->mg_cur = cur;
   h->mg_n_samples = n;
   const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
-  const uint32_t* sorted = as<uint32_t>(h->samples[cur]);
-  const uint32_t* lanes[kLanes] = {sorted + 1, sorted + 2, sorted + 3};
-  { int r = run_rows_and_stats(h, sorted, 4, lanes, kLanes, n, max_rows); if (r) return r; }
+  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n, max_rows); if (r) return r; }
   if (nk) {
     k_solo_ns<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(as<RowStats>(h->stats), h->row_of_kid, (uint32_t)nk, h->solo_ns);
     ++h->launches;

@@ -1,15 +1,18 @@
 // ks_segstats.cuh -- K4 core: per row (segment of the sorted sample stream) and per value lane, the exact integer
 // statistics  sum, min, max and the two middle order statistics  lo = x[(n-1)/2], hi = x[n/2].
 //
+// A sample is a 16-byte item {sort key, lane 0, lane 1, lane 2}; every kernel loads an item once (one 128-bit load) and
+// feeds all three lanes from it.  The stage entry point ks_segment_stats hands in a plain u32 array instead (one lane).
+//
 // Rows differ in size by six orders of magnitude (most key pairs meet a few times, the hottest pair owns percent of
-// all samples), so three size classes share the work:
+// all samples), so four size classes share the work:
 //
 //   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
 //                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
 //   small  (n <= 32)      k_seg_small: one warp per row, shuffle reductions and a 32-wide bitonic network.
-//   mid    (n <= 2048)    k_seg_mid: one warp per (row, lane).  Reductions, then a radix select over (value - min):
-//                         only the bits in which the row's values can differ are walked, 8 per round, with a
-//                         256-bin histogram in the warp's own shared memory -- no block-wide barrier anywhere.
+//   mid    (n <= 2048)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
+//                         only the bits in which the row's values can differ are walked, 8 per round, with 256-bin
+//                         histograms in the warp's own shared memory -- no block-wide barrier anywhere.
 //   large  (n > 2048)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
 //                         chunk's sum/min/max into the row's accumulators, then up to four rounds of
 //                         k_segL_hist (chunk histograms of the current digit into the row's global histogram) and
@@ -25,7 +28,7 @@
 namespace ks {
 
 constexpr int kLanes = 3;
-constexpr uint32_t kMidMax = 2048;     // largest row the warp-per-(row, lane) kernel takes
+constexpr uint32_t kMidMax = 2048;     // largest row the warp-per-row kernel takes
 constexpr uint32_t kLargeChunk = 4096; // samples per work item of a large row
 constexpr int kLargeRounds = 4;        // 8 bits per round: any 32-bit range
 
@@ -45,9 +48,9 @@ struct LargeRow {
 };
 
 struct SegArgs {
-  const uint32_t* lane[kLanes];  // value i of lane l is lane[l][i * stride]
-  uint32_t stride;
-  int n_lanes;
+  const uint4* items;      // 16-byte samples (lanes = .y .z .w), or nullptr:
+  const uint32_t* plain;   // one lane of plain u32 values
+  int n_lanes;             // 3 with items, 1 with plain
   const uint32_t* row_start;
   const uint32_t* n_rows_dev;
   uint32_t max_rows;
@@ -60,8 +63,24 @@ struct SegArgs {
   uint32_t* large_hist;    // [max_large][2 * kLanes][256]
   uint32_t max_large, max_chunks;
   int round;
-  Control* ctl;            // n_big = mid rows, ticket = large rows, scratch0 = chunks, pad[0..3] = unresolved states per round
+  Control* ctl;            // n_small / n_big = small / mid rows, ticket = large rows, scratch0 = chunks,
+                           // pad[0..3] = unresolved selection states per round
 };
+
+struct Val3 {
+  uint32_t v[kLanes];
+};
+
+__device__ __forceinline__ Val3 seg_fetch(const SegArgs& a, size_t i) {
+  Val3 r;
+  if (a.items) {
+    const uint4 it = a.items[i];
+    r.v[0] = it.y; r.v[1] = it.z; r.v[2] = it.w;
+  } else {
+    r.v[0] = a.plain[i]; r.v[1] = 0; r.v[2] = 0;
+  }
+  return r;
+}
 
 __device__ __forceinline__ uint32_t bitonic_sort32(uint32_t v) {
   const uint32_t lane = lane_id();
@@ -109,8 +128,8 @@ __device__ __forceinline__ void warp_pick_bin(const uint32_t* bins, uint32_t k, 
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// One thread per row.  Rows of up to four samples (most rows of a Zipf-distributed trace) are finished right here with
-// a five-comparator sorting network in registers; the others go to the work list of their size class.
+// One thread per row.  Rows of up to four samples are finished right here with a five-comparator sorting network in
+// registers; the others go to the work list of their size class.
 __device__ __forceinline__ void push_row(uint32_t* list, uint32_t* counter, bool mine, uint32_t row) {
   const uint32_t ballot = __ballot_sync(__activemask(), mine);
   if (!mine) return;
@@ -134,21 +153,28 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
     if (cnt == 0) {  // only the stage API can hand in an empty segment
       for (int l = 0; l < a.n_lanes; ++l) { st->sum[l] = 0; st->mn[l] = 0; st->mx[l] = 0; st->lo[l] = 0; st->hi[l] = 0; }
     } else if (cnt <= 4) {
-      for (int l = 0; l < a.n_lanes; ++l) {
-        const uint32_t* v = a.lane[l] + (size_t)s * a.stride;
-        const uint32_t st1 = a.stride;
-        uint32_t x0 = v[0], x1 = cnt > 1 ? v[st1] : 0xFFFFFFFFu, x2 = cnt > 2 ? v[2 * st1] : 0xFFFFFFFFu, x3 = cnt > 3 ? v[3 * st1] : 0xFFFFFFFFu;
+      Val3 x[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if ((uint32_t)i < cnt) x[i] = seg_fetch(a, (size_t)s + i);
+        else { x[i].v[0] = x[i].v[1] = x[i].v[2] = 0xFFFFFFFFu; }
+      }
+      const uint32_t i_max = cnt - 1, i_lo = (cnt - 1) >> 1, i_hi = cnt >> 1;
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        if (l >= a.n_lanes) break;
+        uint32_t x0 = x[0].v[l], x1 = x[1].v[l], x2 = x[2].v[l], x3 = x[3].v[l];
         const unsigned long long sum = (unsigned long long)x0 + (cnt > 1 ? x1 : 0u) + (cnt > 2 ? x2 : 0u) + (cnt > 3 ? x3 : 0u);
         uint32_t t;
 #define KS_CSWAP(p, q) t = min(p, q); q = max(p, q); p = t;
         KS_CSWAP(x0, x1) KS_CSWAP(x2, x3) KS_CSWAP(x0, x2) KS_CSWAP(x1, x3) KS_CSWAP(x1, x2)
 #undef KS_CSWAP
-        const uint32_t srt[4] = {x0, x1, x2, x3};
+        auto pick = [&](uint32_t i) { return i == 0 ? x0 : i == 1 ? x1 : i == 2 ? x2 : x3; };
         st->sum[l] = sum;
         st->mn[l] = x0;
-        st->mx[l] = srt[cnt - 1];
-        st->lo[l] = srt[(cnt - 1) >> 1];
-        st->hi[l] = srt[cnt >> 1];
+        st->mx[l] = pick(i_max);
+        st->lo[l] = pick(i_lo);
+        st->hi[l] = pick(i_hi);
       }
     } else if (cnt > kMidMax) {
       const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
@@ -172,13 +198,18 @@ __global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
     const uint32_t row = a.small_rows[t];
     const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
     RowStats* st = a.stats + row;
-    for (int l = 0; l < a.n_lanes; ++l) {
-      const bool have = lane < cnt;
-      const uint32_t v = have ? a.lane[l][(size_t)(s + lane) * a.stride] : 0u;
+    const bool have = lane < cnt;
+    Val3 x;
+    if (have) x = seg_fetch(a, (size_t)s + lane);
+    else { x.v[0] = x.v[1] = x.v[2] = 0; }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      if (l >= a.n_lanes) break;
+      const uint32_t v = x.v[l];
       const unsigned long long sum = warp_sum64(v);
-      const uint32_t mx = warp_max(v);
       const uint32_t sorted = bitonic_sort32(have ? v : 0xFFFFFFFFu);
       const uint32_t mn = __shfl_sync(0xFFFFFFFFu, sorted, 0);
+      const uint32_t mx = __shfl_sync(0xFFFFFFFFu, sorted, cnt - 1);
       const uint32_t lo = __shfl_sync(0xFFFFFFFFu, sorted, (cnt - 1) >> 1);
       const uint32_t hi = __shfl_sync(0xFFFFFFFFu, sorted, cnt >> 1);
       if (lane == 0) { st->sum[l] = sum; st->mn[l] = mn; st->mx[l] = mx; st->lo[l] = lo; st->hi[l] = hi; }
@@ -187,69 +218,94 @@ __global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// one warp per row of 33..2048 samples; the three lanes are selected together, every sample is loaded once per round
 __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
-  __shared__ uint32_t hist_all[8][256];
-  uint32_t* hist = hist_all[threadIdx.x >> 5];
+  __shared__ uint32_t hist_all[8][kLanes][256];
+  uint32_t (*hist)[256] = hist_all[threadIdx.x >> 5];
   const uint32_t lane = lane_id();
-  const uint32_t n_tasks = min(a.ctl->n_big, a.max_rows) * (uint32_t)a.n_lanes;
+  const uint32_t n_mid = min(a.ctl->n_big, a.max_rows);
   const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-  for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_tasks; t += warps) {
-    const uint32_t row = a.mid_rows[t / a.n_lanes];
-    const int l = (int)(t % a.n_lanes);
+  const int nl = a.n_lanes;
+  for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_mid; t += warps) {
+    const uint32_t row = a.mid_rows[t];
     const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
-    const uint32_t* vals = a.lane[l] + (size_t)s * a.stride;
-    const uint32_t vs = a.stride;
-    unsigned long long sum = 0;
-    uint32_t mn = 0xFFFFFFFFu, mx = 0;
+    unsigned long long sum[kLanes] = {0, 0, 0};
+    uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
     for (uint32_t i = lane; i < cnt; i += 32) {
-      const uint32_t v = vals[(size_t)i * vs];
-      sum += v;
-      mn = min(mn, v);
-      mx = max(mx, v);
-    }
-    sum = warp_sum64(sum);
-    mn = warp_min(mn);
-    mx = warp_max(mx);
-    uint32_t lo = mn, hi = mn;
-    if (mn != mx) {
-      const uint32_t k_lo = (cnt - 1) >> 1, k_hi = cnt >> 1;
-      uint32_t prefix = 0, k = k_lo;
-      int hi_bit = bit_length32(mx - mn) - 1;
-      while (hi_bit >= 0) {
-        const int nb = min(8, hi_bit + 1), shift = hi_bit + 1 - nb;
+      const Val3 x = seg_fetch(a, (size_t)s + i);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) hist[lane * 8 + i] = 0;
-        __syncwarp();
-        for (uint32_t i = lane; i < cnt; i += 32) {
-          const uint32_t u = vals[(size_t)i * vs] - mn;
-          if (matches_prefix(u, prefix, hi_bit)) atomicAdd(&hist[(u >> shift) & ((1u << nb) - 1u)], 1u);
+      for (int l = 0; l < kLanes; ++l) { sum[l] += x.v[l]; mn[l] = min(mn[l], x.v[l]); mx[l] = max(mx[l], x.v[l]); }
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) { sum[l] = warp_sum64(sum[l]); mn[l] = warp_min(mn[l]); mx[l] = warp_max(mx[l]); }
+
+    const uint32_t k_lo = (cnt - 1) >> 1, k_hi = cnt >> 1;
+    uint32_t prefix[kLanes] = {0, 0, 0}, k[kLanes] = {k_lo, k_lo, k_lo};
+    int hi_bit[kLanes];
+    bool open = false;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      hi_bit[l] = (l < nl && mn[l] != mx[l]) ? bit_length32(mx[l] - mn[l]) - 1 : -1;
+      open = open || hi_bit[l] >= 0;
+    }
+    while (open) {
+      int nb[kLanes], shift[kLanes];
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        nb[l] = min(8, hi_bit[l] + 1);
+        shift[l] = hi_bit[l] + 1 - nb[l];
+        if (hi_bit[l] >= 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) hist[l][lane * 8 + i] = 0;
         }
-        __syncwarp();
-        uint32_t d, below;
-        warp_pick_bin(hist, k, &d, &below);
-        __syncwarp();
-        prefix |= d << shift;
-        k -= below;
-        hi_bit = shift - 1;
       }
-      lo = mn + prefix;
-      hi = lo;
-      if (k_hi != k_lo) {
-        // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
-        uint32_t le = 0, next = 0xFFFFFFFFu;
-        for (uint32_t i = lane; i < cnt; i += 32) {
-          const uint32_t v = vals[(size_t)i * vs];
-          le += v <= lo;
-          if (v > lo) next = min(next, v);
+      __syncwarp();
+      for (uint32_t i = lane; i < cnt; i += 32) {
+        const Val3 x = seg_fetch(a, (size_t)s + i);
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) {
+          if (hi_bit[l] < 0) continue;
+          const uint32_t u = x.v[l] - mn[l];
+          if (matches_prefix(u, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(u >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
         }
-        le = warp_sum(le);
-        next = warp_min(next);
-        hi = (le > k_hi) ? lo : next;
+      }
+      __syncwarp();
+      open = false;
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        if (hi_bit[l] < 0) continue;
+        uint32_t d, below;
+        warp_pick_bin(hist[l], k[l], &d, &below);
+        prefix[l] |= d << shift[l];
+        k[l] -= below;
+        hi_bit[l] = shift[l] - 1;
+        open = open || hi_bit[l] >= 0;
+      }
+      __syncwarp();
+    }
+    uint32_t lo[kLanes], hi[kLanes];
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) { lo[l] = mn[l] + prefix[l]; hi[l] = lo[l]; }
+    if (k_hi != k_lo) {
+      // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
+      uint32_t le[kLanes] = {0, 0, 0}, next[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
+      for (uint32_t i = lane; i < cnt; i += 32) {
+        const Val3 x = seg_fetch(a, (size_t)s + i);
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) {
+          le[l] += x.v[l] <= lo[l];
+          if (x.v[l] > lo[l]) next[l] = min(next[l], x.v[l]);
+        }
+      }
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        const uint32_t le_t = warp_sum(le[l]), nx = warp_min(next[l]);
+        hi[l] = (le_t > k_hi) ? lo[l] : nx;
       }
     }
     if (lane == 0) {
       RowStats* st = a.stats + row;
-      st->sum[l] = sum; st->mn[l] = mn; st->mx[l] = mx; st->lo[l] = lo; st->hi[l] = hi;
+      for (int l = 0; l < nl; ++l) { st->sum[l] = sum[l]; st->mn[l] = mn[l]; st->mx[l] = mx[l]; st->lo[l] = lo[l]; st->hi[l] = hi[l]; }
     }
   }
 }
@@ -257,8 +313,8 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
 // ---------------------------------------------------------------------------------------------------------
 // large rows: chunk work items
 __global__ void __launch_bounds__(256) k_segL_reduce(const SegArgs a) {
-  __shared__ unsigned long long sh_sum[8];
-  __shared__ uint32_t sh_mn[8], sh_mx[8];
+  __shared__ unsigned long long sh_sum[8][kLanes];
+  __shared__ uint32_t sh_mn[8][kLanes], sh_mx[8][kLanes];
   const uint32_t n_chunks = (uint32_t)min(a.ctl->scratch0, (unsigned long long)a.max_chunks);
   for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
     LargeRow* L = a.large + a.chunk_row[c];
@@ -268,29 +324,30 @@ __global__ void __launch_bounds__(256) k_segL_reduce(const SegArgs a) {
       uint32_t* gh = a.large_hist + (size_t)a.chunk_row[c] * 2 * kLanes * 256;
       for (uint32_t i = threadIdx.x; i < 2 * kLanes * 256; i += blockDim.x) gh[i] = 0;
     }
-    for (int l = 0; l < a.n_lanes; ++l) {
-      const uint32_t* vals = a.lane[l] + (size_t)(L->start + off) * a.stride;
-      const uint32_t vs = a.stride;
-      unsigned long long sum = 0;
-      uint32_t mn = 0xFFFFFFFFu, mx = 0;
-      for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const uint32_t v = vals[(size_t)i * vs];
-        sum += v;
-        mn = min(mn, v);
-        mx = max(mx, v);
-      }
-      sum = warp_sum64(sum);
-      mn = warp_min(mn);
-      mx = warp_max(mx);
-      __syncthreads();
-      if (lane_id() == 0) { sh_sum[threadIdx.x >> 5] = sum; sh_mn[threadIdx.x >> 5] = mn; sh_mx[threadIdx.x >> 5] = mx; }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w) { sum += sh_sum[w]; mn = min(mn, sh_mn[w]); mx = max(mx, sh_mx[w]); }
-        atomicAdd(&L->sum[l], sum);
-        atomicMin(&L->mn[l], mn);
-        atomicMax(&L->mx[l], mx);
-      }
+    const size_t base = (size_t)L->start + off;
+    unsigned long long sum[kLanes] = {0, 0, 0};
+    uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
+    for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
+      const Val3 x = seg_fetch(a, base + i);
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) { sum[l] += x.v[l]; mn[l] = min(mn[l], x.v[l]); mx[l] = max(mx[l], x.v[l]); }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      const unsigned long long s2 = warp_sum64(sum[l]);
+      const uint32_t n2 = warp_min(mn[l]), x2 = warp_max(mx[l]);
+      if (lane_id() == 0) { sh_sum[threadIdx.x >> 5][l] = s2; sh_mn[threadIdx.x >> 5][l] = n2; sh_mx[threadIdx.x >> 5][l] = x2; }
+    }
+    __syncthreads();
+    if (threadIdx.x < (uint32_t)a.n_lanes) {
+      const int l = threadIdx.x;
+      unsigned long long s2 = 0;
+      uint32_t n2 = 0xFFFFFFFFu, x2 = 0;
+      for (int w = 0; w < 8; ++w) { s2 += sh_sum[w][l]; n2 = min(n2, sh_mn[w][l]); x2 = max(x2, sh_mx[w][l]); }
+      atomicAdd(&L->sum[l], s2);
+      atomicMin(&L->mn[l], n2);
+      atomicMax(&L->mx[l], x2);
     }
   }
 }
@@ -317,25 +374,33 @@ __global__ void __launch_bounds__(256) k_segL_hist(const SegArgs a) {
   for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
     const uint32_t li = a.chunk_row[c];
     const LargeRow* L = a.large + li;
+    int hb[2 * kLanes], nb[2 * kLanes], shf[2 * kLanes];
+    uint32_t pre[2 * kLanes], mn[kLanes];
     bool any = false;
-    for (int v = 0; v < 2 * a.n_lanes; ++v) any = any || L->hi_bit[v] >= 0;
+#pragma unroll
+    for (int v = 0; v < 2 * kLanes; ++v) {
+      hb[v] = L->hi_bit[v];
+      pre[v] = L->prefix[v];
+      nb[v] = min(8, hb[v] + 1);
+      shf[v] = hb[v] + 1 - nb[v];
+      any = any || hb[v] >= 0;
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) mn[l] = L->mn[l];
     if (!any) continue;
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < 2 * kLanes * 256; i += blockDim.x) (&sh[0][0])[i] = 0;
     __syncthreads();
     const uint32_t off = a.chunk_idx[c] * kLargeChunk;
     const uint32_t m = min(kLargeChunk, L->cnt - off);
-    for (int l = 0; l < a.n_lanes; ++l) {
-      const int hb0 = L->hi_bit[2 * l], hb1 = L->hi_bit[2 * l + 1];
-      if (hb0 < 0 && hb1 < 0) continue;
-      const uint32_t p0 = L->prefix[2 * l], p1 = L->prefix[2 * l + 1], mn = L->mn[l];
-      const int nb0 = min(8, hb0 + 1), sh0 = hb0 + 1 - nb0, nb1 = min(8, hb1 + 1), sh1 = hb1 + 1 - nb1;
-      const uint32_t* vals = a.lane[l] + (size_t)(L->start + off) * a.stride;
-      const uint32_t vs = a.stride;
-      for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const uint32_t u = vals[(size_t)i * vs] - mn;
-        if (hb0 >= 0 && matches_prefix(u, p0, hb0)) atomicAdd(&sh[2 * l][(u >> sh0) & ((1u << nb0) - 1u)], 1u);
-        if (hb1 >= 0 && matches_prefix(u, p1, hb1)) atomicAdd(&sh[2 * l + 1][(u >> sh1) & ((1u << nb1) - 1u)], 1u);
+    const size_t base = (size_t)L->start + off;
+    for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
+      const Val3 x = seg_fetch(a, base + i);
+#pragma unroll
+      for (int v = 0; v < 2 * kLanes; ++v) {
+        if (hb[v] < 0) continue;
+        const uint32_t u = x.v[v >> 1] - mn[v >> 1];
+        if (matches_prefix(u, pre[v], hb[v])) atomicAdd(&sh[v][(u >> shf[v]) & ((1u << nb[v]) - 1u)], 1u);
       }
     }
     __syncthreads();

@@ -71,10 +71,9 @@ __global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ key
   for (int i = threadIdx.x; i < passes * 256; i += blockDim.x) sh[i] = 0;
   __syncthreads();
   const uint32_t gstride = gridDim.x * blockDim.x;
-  // whole warps iterate together so that the match below always sees 32 lanes
-  const uint32_t n_round = (n + 31u) & ~31u;
-  // four independent loads per thread and iteration: the loop is bound by load latency, not by arithmetic
-  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n_round; i0 += 4 * gstride) {
+  // four independent loads per thread and iteration (the loop is bound by load latency); plain shared-memory atomics:
+  // they cost a few cycles per distinct digit of a warp, less than grouping the lanes by digit first
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += 4 * gstride) {
     KeyT k[4];
     bool valid[4];
 #pragma unroll
@@ -85,13 +84,11 @@ __global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ key
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      if (i0 + u * gstride >= n_round) break;  // warp-uniform
+      if (!valid[u]) continue;
       for (int p = 0; p < passes; ++p) {
         const int shift = begin_bit + 8 * p;
         const int bits = min(8, end_bit - shift);
-        const uint32_t d = digit_of(k[u], shift, (1u << bits) - 1u);
-        const uint32_t same = match_digit(d, __ballot_sync(0xFFFFFFFFu, valid[u]));
-        if (valid[u] && (same & lanemask_lt()) == 0) atomicAdd(&sh[p * 256 + d], (uint32_t)__popc(same));
+        atomicAdd(&sh[p * 256 + digit_of(k[u], shift, (1u << bits) - 1u)], 1u);
       }
     }
   }
