@@ -5,8 +5,7 @@
 // lines although a record is 48 bytes; each thread then takes its record from shared memory as three 128-bit
 // loads (a 48-byte stride is conflict-free for 128-bit shared loads).  Per record it
 //   * computes the 64-bit kernel key (ks_common.cuh kernel_key),
-//   * finds the key's slot in the open-addressing dictionary -- one probe per distinct key of the warp
-//     (__match_any_sync groups equal keys, the group's first lane probes and shares the slot by shuffle),
+//   * finds the key's slot in the open-addressing dictionary (2^18 slots, 2 MB: the probes are L2 hits),
 //   * writes the compact timeline entry  start_ns (u64) | duration (u32) | meta (u32: slot, solo, tenant),
 //   * appends solo launches to the solo stream (slot | duration << 32) with one warp-aggregated counter update,
 //   * checks the record (end >= start, duration < 2^31 ns so that a pair's span fits 32 bits) and whether start_ns is non-decreasing.
@@ -149,12 +148,11 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
     const bool solo = (w1.w & kMetaSoloBit) != 0;
     const uint64_t key = kernel_key(w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, a.type_mode != 0);
 
-    // one dictionary probe per distinct key of the warp
-    const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? key : 0ull);
-    const uint32_t leader = __ffs(same) - 1;
+    // every lane looks its key up itself: the keys of a warp are mostly distinct (a Zipf law over a thousand keys), so
+    // grouping equal keys first costs more than the few duplicate probes it saves; the probes hit L2
     const uint32_t solo_ballot = __ballot_sync(0xFFFFFFFFu, valid && solo && !a.halo);
     uint32_t slot = 0;
-    if (valid && lane == leader) {
+    if (valid) {
       bool inserted;
       slot = dict_find_or_insert(a.dict_keys, key, &inserted);
       if (slot >= kDictSlots) { err |= kErrTooManyKeys; slot = 0; inserted = false; }
@@ -165,26 +163,28 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
         a.dict_words[2 * (size_t)slot] = k0;
         a.dict_words[2 * (size_t)slot + 1] = k1;
       }
-      // launch counts: CTA-local cache first, global atomics when the cache is crowded
-      const uint32_t c_all = a.halo ? 0u : __popc(same), c_solo = __popc(same & solo_ballot);
-      uint32_t h = (slot * 2654435761u) >> (32 - 10);
-      bool cached = c_all == 0;
-      for (int probe = 0; probe < 8 && !cached; ++probe) {
-        const uint32_t old = atomicCAS(&cc_slot[h], 0u, slot + 1);
-        if (old == 0u || old == slot + 1) {
-          atomicAdd(&cc_cnt[h], c_all);
-          if (c_solo) atomicAdd(&cc_solo[h], c_solo);
-          cached = true;
-          break;
+      if (!a.halo) {
+        // launch counts: CTA-local cache first (a plain load finds the key's entry once it exists), global atomics when
+        // the cache is crowded
+        uint32_t h = (slot * 2654435761u) >> (32 - 10);
+        bool cached = false;
+        for (int probe = 0; probe < 8; ++probe) {
+          uint32_t cur = cc_slot[h];
+          if (cur == 0u) cur = atomicCAS(&cc_slot[h], 0u, slot + 1);
+          if (cur == 0u || cur == slot + 1) {
+            atomicAdd(&cc_cnt[h], 1u);
+            if (solo) atomicAdd(&cc_solo[h], 1u);
+            cached = true;
+            break;
+          }
+          h = (h + 1) & (kCtaCountSlots - 1);
         }
-        h = (h + 1) & (kCtaCountSlots - 1);
-      }
-      if (!cached) {
-        atomicAdd(&a.dict_launches[slot], c_all);
-        if (c_solo) atomicAdd(&a.dict_solo[slot], c_solo);
+        if (!cached) {
+          atomicAdd(&a.dict_launches[slot], 1u);
+          if (solo) atomicAdd(&a.dict_solo[slot], 1u);
+        }
       }
     }
-    slot = __shfl_sync(0xFFFFFFFFu, slot, leader);
 
     if (valid) {
       if (end < start || end - start >= 0x80000000ull) err |= kErrRecord;

@@ -10,10 +10,10 @@
 //   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
 //                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
 //   small  (n <= 32)      k_seg_small: one warp per row, shuffle reductions and a 32-wide bitonic network.
-//   mid    (n <= 2048)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
+//   mid    (n <= 1024)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
 //                         only the bits in which the row's values can differ are walked, 8 per round, with 256-bin
 //                         histograms in the warp's own shared memory -- no block-wide barrier anywhere.
-//   large  (n > 2048)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
+//   large  (n > 1024)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
 //                         chunk's sum/min/max into the row's accumulators, then up to four rounds of
 //                         k_segL_hist (chunk histograms of the current digit into the row's global histogram) and
 //                         k_segL_resolve (pick the digit that holds the wanted rank) narrow lo and hi separately.
@@ -28,7 +28,7 @@
 namespace ks {
 
 constexpr int kLanes = 3;
-constexpr uint32_t kMidMax = 2048;     // largest row the warp-per-row kernel takes
+constexpr uint32_t kMidMax = 1024;     // largest row the warp-per-row kernel takes
 constexpr uint32_t kLargeChunk = 4096; // samples per work item of a large row
 constexpr int kLargeRounds = 4;        // 8 bits per round: any 32-bit range
 
@@ -231,10 +231,17 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
     const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
     unsigned long long sum[kLanes] = {0, 0, 0};
     uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
-    for (uint32_t i = lane; i < cnt; i += 32) {
-      const Val3 x = seg_fetch(a, (size_t)s + i);
+    for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
+      Val3 xs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+      if (i0 + 32 * u >= cnt) break;
+      const Val3 x = xs[u];
 #pragma unroll
       for (int l = 0; l < kLanes; ++l) { sum[l] += x.v[l]; mn[l] = min(mn[l], x.v[l]); mx[l] = max(mx[l], x.v[l]); }
+      }
     }
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) { sum[l] = warp_sum64(sum[l]); mn[l] = warp_min(mn[l]); mx[l] = warp_max(mx[l]); }
@@ -260,13 +267,20 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
         }
       }
       __syncwarp();
-      for (uint32_t i = lane; i < cnt; i += 32) {
-        const Val3 x = seg_fetch(a, (size_t)s + i);
+      for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
+        Val3 xs[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+        if (i0 + 32 * u >= cnt) break;
+        const Val3 x = xs[u];
 #pragma unroll
         for (int l = 0; l < kLanes; ++l) {
           if (hi_bit[l] < 0) continue;
           const uint32_t u = x.v[l] - mn[l];
           if (matches_prefix(u, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(u >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
+        }
         }
       }
       __syncwarp();
@@ -289,12 +303,19 @@ __global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
     if (k_hi != k_lo) {
       // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
       uint32_t le[kLanes] = {0, 0, 0}, next[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-      for (uint32_t i = lane; i < cnt; i += 32) {
-        const Val3 x = seg_fetch(a, (size_t)s + i);
+      for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
+        Val3 xs[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+        if (i0 + 32 * u >= cnt) break;
+        const Val3 x = xs[u];
 #pragma unroll
         for (int l = 0; l < kLanes; ++l) {
           le[l] += x.v[l] <= lo[l];
           if (x.v[l] > lo[l]) next[l] = min(next[l], x.v[l]);
+        }
         }
       }
 #pragma unroll
