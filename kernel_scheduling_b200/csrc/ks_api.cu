@@ -63,6 +63,9 @@ struct ks_handle {
   uint32_t mg_flags = 0;
   int mg_cur = 0;
   cudaEvent_t ev[12]{};
+  // the three size classes of K4 are independent of one another: they run side by side on two helper streams
+  cudaStream_t aux[2]{};
+  cudaEvent_t fork_ev{}, join_ev[2]{};
 };
 
 namespace {
@@ -383,9 +386,15 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   s.ctl = h->d_ctl;
   const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 255) / 256, (uint32_t)h->sm_count * 8));
   k_seg_classify<<<cgrid, 256, 0, h->stream>>>(s);
-  k_seg_small<<<h->sm_count * 8, 256, 0, h->stream>>>(s);
-  k_seg_mid<<<h->sm_count * 8, 256, 0, h->stream>>>(s);
-  const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 8));
+  // fork: small rows on aux[0], mid rows on aux[1], the large-row rounds stay on the main stream
+  KS_CUDA(h, cudaEventRecord(h->fork_ev, h->stream));
+  KS_CUDA(h, cudaStreamWaitEvent(h->aux[0], h->fork_ev, 0));
+  KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->fork_ev, 0));
+  k_seg_small<<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
+  k_seg_mid<<<h->sm_count * 4, 256, 0, h->aux[1]>>>(s);
+  KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
+  KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
+  const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 4));
   k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
   k_segL_init<<<(max_large * 2 * kLanes + 255) / 256, 256, 0, h->stream>>>(s);
   for (int r = 0; r < kLargeRounds; ++r) {
@@ -394,6 +403,8 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
     k_segL_resolve<<<(int)std::min<uint32_t>(max_large, (uint32_t)h->sm_count * 8), 2 * kLanes * 32, 0, h->stream>>>(s);
   }
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
+  KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
+  KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[1], 0));
   h->launches += 6 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
@@ -504,6 +515,9 @@ ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
   alloc(&h->solo_ns, (size_t)(kMaxKeys + 1) * 8);
   alloc(&h->key_rows, (size_t)(kMaxKeys + 1) * sizeof(ks_key_row));
   for (auto& e : h->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+  for (auto& st : h->aux) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->fork_ev, cudaEventDisableTiming) == cudaSuccess;
+  for (auto& e : h->join_ev) ok = ok && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess;
   if (ok && h->cfg.max_records) {
     const size_t n = h->cfg.max_records;
     ok = ok && !ensure(h, h->tl_start[0], n * 8) && !ensure(h, h->tl_dm[0], n * 8) && !ensure(h, h->solo_stream, n * 8);
@@ -530,6 +544,9 @@ void ks_destroy(ks_handle* h) {
                     &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
+  for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+  if (h->fork_ev) cudaEventDestroy(h->fork_ev);
+  for (auto& e : h->join_ev) if (e) cudaEventDestroy(e);
   if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
   delete h;
 }
