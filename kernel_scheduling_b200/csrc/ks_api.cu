@@ -204,7 +204,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit) {
     attr_set = true;
   }
   int cur = 0;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 5);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
   for (int p = 0; p < passes; ++p) {
     KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
     SortPass16Args a{};
@@ -281,7 +281,7 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
     attr_set = true;
   }
   const uint64_t ntiles = (n + kDecodeThreads - 1) / kDecodeThreads;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 5);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
   k_decode_hash<<<grid, kDecodeThreads, decode_smem_bytes(), h->stream>>>(a);
   ++h->launches;
   KS_CUDA(h, cudaGetLastError());

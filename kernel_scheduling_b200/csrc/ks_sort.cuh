@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(256) k_dest_hist(const SortPass16Args a, uint3
 }
 
 template <int ITEMS>
-__global__ void __launch_bounds__(kSortThreads) k_onesweep_pass16(const SortPass16Args a) {
+__global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortPass16Args a) {
   constexpr int TILE = kSortThreads * ITEMS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* s_items = reinterpret_cast<uint4*>(smem_raw);                       // [TILE]
