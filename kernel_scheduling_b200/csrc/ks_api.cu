@@ -1069,7 +1069,6 @@ int64_t ks_mg_counts(ks_handle* h, uint64_t* launches, uint64_t* solo, int impor
                                                                                reinterpret_cast<unsigned long long*>(launches), reinterpret_cast<unsigned long long*>(solo), import);
     ++h->launches;
   }
-  KS_CUDA(h, cudaStreamSynchronize(h->stream));
   return (int64_t)h->mg_nk;
 }
 
@@ -1113,14 +1112,13 @@ int64_t ks_mg_key_histogram(ks_handle* h, uint64_t* hist, uint32_t* shift_out) {
     k_key_hist<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), (uint32_t)h->mg_n_samples, shift, reinterpret_cast<unsigned long long*>(hist));
     ++h->launches;
   }
-  KS_CUDA(h, cudaStreamSynchronize(h->stream));
   return (int64_t)kKeyHistBins;
 }
 
 // splitters[r-1] = first histogram bin of rank r (n_ranks - 1 ascending values).  Writes the samples grouped by destination
 // rank into send (capacity items); counts[r] = items for rank r.
 int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, void* send, uint64_t capacity, uint64_t* counts) {
-  if (!h || !counts || n_ranks == 0 || n_ranks > 16 || (n_ranks > 1 && !splitters) || (!send && capacity)) return -KS_ERR_ARG;
+  if (!h || n_ranks == 0 || n_ranks > 16 || (n_ranks > 1 && !splitters) || (!send && capacity)) return -KS_ERR_ARG;
   KS_CUDA(h, cudaSetDevice(h->device));
   const uint64_t n = h->mg_n_samples;
   if (n > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_partition: send buffer too small");
@@ -1148,7 +1146,7 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   a.lookback = as<uint32_t>(h->lookback);
   a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
   a.err = &h->d_ctl->err;
-  for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = 0;
+  if (counts) for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = 0;
   if (n) {
     constexpr size_t smem = sort16_smem_bytes<ITEMS>();
     KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1156,11 +1154,13 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
     k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, 1);
     k_onesweep_pass16<ITEMS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * 5), kSortThreads, smem, h->stream>>>(a);
     h->launches += 3;
-    uint32_t hc[16];
-    KS_CUDA(h, cudaMemcpyAsync(hc, hist, sizeof(hc), cudaMemcpyDeviceToHost, h->stream));
-    { int r = read_ctl(h); if (r) return r; }
-    { int r = mg_status(h, "ks_mg_partition"); if (r) return r; }
-    for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = hc[r];
+    if (counts) {
+      uint32_t hc[16];
+      KS_CUDA(h, cudaMemcpyAsync(hc, hist, sizeof(hc), cudaMemcpyDeviceToHost, h->stream));
+      { int r = read_ctl(h); if (r) return r; }
+      { int r = mg_status(h, "ks_mg_partition"); if (r) return r; }
+      for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = hc[r];
+    }
   }
   return (int64_t)n;
 }
@@ -1205,7 +1205,6 @@ int64_t ks_mg_solo(ks_handle* h, double* solo, int import) {
     if (import) KS_CUDA(h, cudaMemcpyAsync(h->solo_ns, solo, h->mg_nk * 8, cudaMemcpyDeviceToDevice, h->stream));
     else KS_CUDA(h, cudaMemcpyAsync(solo, h->solo_ns, h->mg_nk * 8, cudaMemcpyDeviceToDevice, h->stream));
   }
-  KS_CUDA(h, cudaStreamSynchronize(h->stream));
   return (int64_t)h->mg_nk;
 }
 

@@ -6,7 +6,8 @@
 // earlier member.
 //
 // A CTA stages a tile of the timeline plus a look-ahead window in shared memory as separate start / duration / info
-// arrays (dictionary slots already translated to dense key ids).  Consecutive lanes take consecutive launches and
+// arrays; start times are stored relative to the window's first entry in 32 bits whenever the window spans less than
+// 2^31 ns (always, for a busy trace), so the searches and comparisons are 32-bit.  Consecutive lanes take consecutive launches and
 // find where their run of candidates ends by a galloping search (most runs are empty or a few entries long).  An
 // exclusive scan of the run lengths numbers the CANDIDATES of the tile; every thread then takes an equal, contiguous
 // share of the candidates (merge-path style: one binary search for the owner of its first candidate, then a walk),
@@ -42,15 +43,18 @@ struct JoinArgs {
   Control* ctl;
 };
 
-struct JoinEntry {
-  unsigned long long start;
+// A window entry.  TimeT = uint32_t when the window's start times fit 31 bits relative to its first entry (then every
+// comparison and the staging traffic are 32-bit), unsigned long long otherwise.
+template <typename TimeT>
+struct JoinEntryT {
+  TimeT start;
   uint32_t dur;
   uint32_t info;  // dictionary slot | solo << 23 | tenant << 24
 };
+using JoinEntry = JoinEntryT<unsigned long long>;
 
-// window entries keep the timeline's meta word (dictionary slot | solo << 23 | tenant << 24); slots are translated to
-// dense key ids only for the pairs that are emitted (about one lookup per two launches instead of three per two)
-__device__ __forceinline__ uint32_t join_info(const JoinArgs& a, uint32_t meta) { return meta; }
+// window entries keep the timeline's meta word; slots are translated to dense key ids only for the pairs that are
+// emitted (about one lookup per two launches instead of three per two)
 __device__ __forceinline__ bool info_solo(uint32_t info) { return (info & kMetaSoloBit) != 0; }
 __device__ __forceinline__ uint32_t info_tenant(uint32_t info) { return info >> 24; }
 
@@ -59,17 +63,18 @@ __device__ __forceinline__ JoinEntry join_entry(const JoinArgs& a, uint64_t j) {
   e.start = a.tl_start[j];
   const unsigned long long dm = a.tl_dm[j];
   e.dur = (uint32_t)dm;
-  e.info = join_info(a, (uint32_t)(dm >> 32));
+  e.info = (uint32_t)(dm >> 32);
   return e;
 }
 
-__device__ __forceinline__ bool join_pair_ok(const JoinEntry& ei, const JoinEntry& ej) {
+template <typename TimeT>
+__device__ __forceinline__ bool join_pair_ok(const JoinEntryT<TimeT>& ei, const JoinEntryT<TimeT>& ej) {
   return !info_solo(ej.info) && ((ei.info ^ ej.info) >> 24) != 0 && ei.start < ej.start + ej.dur;
 }
 
-template <bool kIndexOutput>
-__device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long out, const JoinEntry& ei, const JoinEntry& ej, uint64_t gi, uint64_t gj,
-                                          uint32_t nk) {
+template <bool kIndexOutput, typename TimeT>
+__device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long out, const JoinEntryT<TimeT>& ei, const JoinEntryT<TimeT>& ej, uint64_t gi,
+                                          uint64_t gj, uint32_t nk) {
   if (out >= a.capacity) return;
   const bool i_is_a = info_tenant(ei.info) < info_tenant(ej.info);
   if constexpr (kIndexOutput) {
@@ -83,32 +88,26 @@ __device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long 
   }
 }
 
-template <bool kIndexOutput>
-__global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
-  __shared__ unsigned long long s_start[kJoinWindow];
-  __shared__ uint32_t s_dur[kJoinWindow];
-  __shared__ uint32_t s_info[kJoinWindow];
-  __shared__ __align__(16) uint32_t run_off[kJoinTile + 4];  // run lengths, then their exclusive scan
-  __shared__ uint32_t warp_tot[kJoinThreads / 32];
-  __shared__ uint32_t warp_tot2[kJoinThreads / 32];
-  __shared__ unsigned long long s_base;
-  __shared__ uint32_t s_spill;
+struct JoinShared {
+  unsigned long long start_raw[kJoinWindow];  // TimeT view: the first sizeof(TimeT) * kJoinWindow bytes
+  uint32_t dur[kJoinWindow];
+  uint32_t info[kJoinWindow];
+  __align__(16) uint32_t run_off[kJoinTile + 4];  // run lengths, then their exclusive scan
+  uint32_t warp_tot[kJoinThreads / 32];
+  uint32_t warp_tot2[kJoinThreads / 32];
+  unsigned long long base_out;
+  uint32_t spill;
+  uint32_t wide;
+};
 
+// The tile's work once the window is staged.  base = start_ns the TimeT values are relative to (0 for 64-bit).
+template <bool kIndexOutput, typename TimeT>
+__device__ __forceinline__ void join_tile(const JoinArgs& a, JoinShared& sh, uint64_t t0, uint32_t tn, uint32_t wn, unsigned long long base) {
+  using Entry = JoinEntryT<TimeT>;
+  const TimeT* s_start = reinterpret_cast<const TimeT*>(sh.start_raw);
   const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-  const uint64_t t0 = (uint64_t)blockIdx.x * kJoinTile;
-  if (t0 >= a.n) return;
-  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, a.n - t0);    // launches of this tile
-  const uint32_t wn = (uint32_t)min((uint64_t)kJoinWindow, a.n - t0);  // staged entries
-  for (uint32_t i = tid; i < wn; i += kJoinThreads) {
-    s_start[i] = a.tl_start[t0 + i];
-    const unsigned long long dm = a.tl_dm[t0 + i];
-    s_dur[i] = (uint32_t)dm;
-    s_info[i] = join_info(a, (uint32_t)(dm >> 32));
-  }
-  if (tid == 0) s_spill = 0;
-  __syncthreads();
   const uint32_t nk = a.ctl->n_keys;
-  auto entry = [&](uint32_t i) -> JoinEntry { JoinEntry e; e.start = s_start[i]; e.dur = s_dur[i]; e.info = s_info[i]; return e; };
+  auto entry = [&](uint32_t i) -> Entry { Entry e; e.start = s_start[i]; e.dur = sh.dur[i]; e.info = sh.info[i]; return e; };
 
   // ---- run length of every launch of the tile inside the window (consecutive lanes, consecutive launches)
   bool spills = false;
@@ -116,8 +115,8 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
   for (int k = 0; k < kJoinPerThread; ++k) {
     const uint32_t li = k * kJoinThreads + tid;
     uint32_t len = 0;
-    if (li < tn && !info_solo(s_info[li]) && s_dur[li]) {
-      const unsigned long long end_i = s_start[li] + s_dur[li];
+    if (li < tn && !info_solo(sh.info[li]) && sh.dur[li]) {
+      const TimeT end_i = s_start[li] + sh.dur[li];
       // gallop: [lo, hi) brackets the first staged entry with start >= end_i
       uint32_t lo = li + 1, step = 1, hi = lo;
       while (hi < wn && s_start[hi] < end_i) { lo = hi + 1; hi += step; step <<= 1; }
@@ -129,33 +128,33 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
       len = lo - (li + 1);
       if (lo == wn && t0 + wn < a.n) spills = true;  // the run may go on behind the window
     }
-    run_off[li] = len;
+    sh.run_off[li] = len;
   }
-  if (spills) atomicOr(&s_spill, 1u);
+  if (spills) atomicOr(&sh.spill, 1u);
   __syncthreads();
   // ---- exclusive scan of the run lengths (thread t scans launches 4t .. 4t+3)
   uint32_t len4[kJoinPerThread], mine = 0;
   {
-    const uint4 v = *reinterpret_cast<const uint4*>(run_off + tid * kJoinPerThread);
+    const uint4 v = *reinterpret_cast<const uint4*>(sh.run_off + tid * kJoinPerThread);
     len4[0] = v.x; len4[1] = v.y; len4[2] = v.z; len4[3] = v.w;
     mine = v.x + v.y + v.z + v.w;
   }
   const uint32_t inc = warp_incl_scan(mine);
-  if (lane == 31) warp_tot[warp] = inc;
+  if (lane == 31) sh.warp_tot[warp] = inc;
   __syncthreads();
   uint32_t off = inc - mine, total = 0;
   for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
-    if (w < warp) off += warp_tot[w];
-    total += warp_tot[w];
+    if (w < warp) off += sh.warp_tot[w];
+    total += sh.warp_tot[w];
   }
   {
     uint4 o;
     o.x = off; o.y = off + len4[0]; o.z = o.y + len4[1]; o.w = o.z + len4[2];
-    *reinterpret_cast<uint4*>(run_off + tid * kJoinPerThread) = o;
+    *reinterpret_cast<uint4*>(sh.run_off + tid * kJoinPerThread) = o;
   }
-  if (tid == 0) run_off[kJoinTile] = total;
+  if (tid == 0) sh.run_off[kJoinTile] = total;
   __syncthreads();
-  const bool any_spill = s_spill != 0;
+  const bool any_spill = sh.spill != 0;
 
   // ---- this thread's share of the candidates: [c0, c1)
   const uint32_t per = (total + kJoinThreads - 1) / kJoinThreads;
@@ -165,7 +164,7 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
     uint32_t lo = 0, hi = kJoinTile;
     while (lo + 1 < hi) {
       const uint32_t mid = (lo + hi) >> 1;
-      if (run_off[mid] <= c0) lo = mid; else hi = mid;
+      if (sh.run_off[mid] <= c0) lo = mid; else hi = mid;
     }
     owner0 = lo;
   }
@@ -174,30 +173,33 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
   unsigned long long out = 0;
   for (int pass = 0; pass < 2; ++pass) {
     uint32_t li = owner0;
-    JoinEntry ei = entry(li);
+    Entry ei = entry(li);
     for (uint32_t q = c0; q < c1; ++q) {
-      while (run_off[li + 1] <= q) { ++li; ei = entry(li); }
-      const uint32_t lj = li + 1 + (q - run_off[li]);
-      const JoinEntry ej = entry(lj);
+      while (sh.run_off[li + 1] <= q) { ++li; ei = entry(li); }
+      const uint32_t lj = li + 1 + (q - sh.run_off[li]);
+      const Entry ej = entry(lj);
       if (!join_pair_ok(ei, ej) || t0 + lj < a.n_halo) continue;
       if (pass == 0) ++n_valid;
       else { join_emit<kIndexOutput>(a, out, ei, ej, t0 + li, t0 + lj, nk); ++out; }
     }
-    // runs that continue behind the window: their owner walks the rest from global memory
+    // runs that continue behind the window: their owner walks the rest from global memory (64-bit times)
     uint32_t spill_cnt = 0;
     if (any_spill) {
 #pragma unroll 1
       for (int k = 0; k < kJoinPerThread; ++k) {
         const uint32_t sl = tid * kJoinPerThread + k;
         if (!(sl < tn && sl + 1 + len4[k] == wn)) continue;  // only runs that reached the end of the window
-        const JoinEntry es = entry(sl);
+        JoinEntry es;
+        es.start = base + s_start[sl];
+        es.dur = sh.dur[sl];
+        es.info = sh.info[sl];
         if (info_solo(es.info) || !es.dur) continue;
         const unsigned long long end_s = es.start + es.dur;
         for (uint64_t j = t0 + wn; j < a.n; ++j) {
           const JoinEntry ej = join_entry(a, j);
           if (ej.start >= end_s) break;
           if (!join_pair_ok(es, ej) || j < a.n_halo) continue;
-          if (pass == 1) join_emit<kIndexOutput>(a, s_base + spill_before + spill_cnt, es, ej, t0 + sl, j, nk);
+          if (pass == 1) join_emit<kIndexOutput>(a, sh.base_out + spill_before + spill_cnt, es, ej, t0 + sl, j, nk);
           ++spill_cnt;
         }
       }
@@ -206,21 +208,55 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
       // one scan over (window pairs, spilled pairs) per thread; window pairs first, spilled pairs behind all of them
       const uint32_t vinc = warp_incl_scan(n_valid), sinc = warp_incl_scan(spill_cnt);
       __syncthreads();
-      if (lane == 31) { warp_tot[warp] = vinc; warp_tot2[warp] = sinc; }
+      if (lane == 31) { sh.warp_tot[warp] = vinc; sh.warp_tot2[warp] = sinc; }
       __syncthreads();
       uint32_t vbefore = vinc - n_valid, sbefore = sinc - spill_cnt, vtotal = 0, stotal = 0;
       for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
-        if (w < warp) { vbefore += warp_tot[w]; sbefore += warp_tot2[w]; }
-        vtotal += warp_tot[w];
-        stotal += warp_tot2[w];
+        if (w < warp) { vbefore += sh.warp_tot[w]; sbefore += sh.warp_tot2[w]; }
+        vtotal += sh.warp_tot[w];
+        stotal += sh.warp_tot2[w];
       }
       __syncthreads();
-      if (tid == 0) s_base = (vtotal + stotal) ? atomicAdd(&a.ctl->n_pairs, (unsigned long long)(vtotal + stotal)) : 0ull;
+      if (tid == 0) sh.base_out = (vtotal + stotal) ? atomicAdd(&a.ctl->n_pairs, (unsigned long long)(vtotal + stotal)) : 0ull;
       __syncthreads();
       if (vtotal + stotal == 0) return;
-      out = s_base + vbefore;
+      out = sh.base_out + vbefore;
       spill_before = vtotal + sbefore;
     }
+  }
+}
+
+template <bool kIndexOutput>
+__global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
+  __shared__ JoinShared sh;
+  const uint32_t tid = threadIdx.x;
+  const uint64_t t0 = (uint64_t)blockIdx.x * kJoinTile;
+  if (t0 >= a.n) return;
+  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, a.n - t0);    // launches of this tile
+  const uint32_t wn = (uint32_t)min((uint64_t)kJoinWindow, a.n - t0);  // staged entries
+  // the window is in start order: it fits 31 bits relative to its first entry iff its last entry does
+  const unsigned long long base = a.tl_start[t0];
+  const bool wide = a.tl_start[t0 + wn - 1] - base >= 0x80000000ull;
+  if (tid == 0) sh.spill = 0;
+  if (!wide) {
+    uint32_t* s32 = reinterpret_cast<uint32_t*>(sh.start_raw);
+    for (uint32_t i = tid; i < wn; i += kJoinThreads) {
+      s32[i] = (uint32_t)(a.tl_start[t0 + i] - base);
+      const unsigned long long dm = a.tl_dm[t0 + i];
+      sh.dur[i] = (uint32_t)dm;
+      sh.info[i] = (uint32_t)(dm >> 32);
+    }
+    __syncthreads();
+    join_tile<kIndexOutput, uint32_t>(a, sh, t0, tn, wn, base);
+  } else {
+    for (uint32_t i = tid; i < wn; i += kJoinThreads) {
+      sh.start_raw[i] = a.tl_start[t0 + i];
+      const unsigned long long dm = a.tl_dm[t0 + i];
+      sh.dur[i] = (uint32_t)dm;
+      sh.info[i] = (uint32_t)(dm >> 32);
+    }
+    __syncthreads();
+    join_tile<kIndexOutput, unsigned long long>(a, sh, t0, tn, wn, 0ull);
   }
 }
 

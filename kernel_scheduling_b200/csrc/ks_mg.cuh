@@ -51,10 +51,12 @@ __global__ void __launch_bounds__(1024) k_tail_select(const unsigned long long* 
   const uint32_t found = s_count;
   if (threadIdx.x == 0) *count = found;
   if (found > kHaloMax || found > capacity) return;  // the host reports the overflow
-  // bitonic sort of the (padded) list in shared memory
-  for (uint32_t k = 2; k <= kHaloMax; k <<= 1) {
+  // bitonic sort of the list (padded with 0xFFFFFFFF to a power of two) in shared memory
+  uint32_t width = 2;
+  while (width < found) width <<= 1;
+  for (uint32_t k = 2; k <= width; k <<= 1) {
     for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-      for (uint32_t t = threadIdx.x; t < kHaloMax; t += blockDim.x) {
+      for (uint32_t t = threadIdx.x; t < width; t += blockDim.x) {
         const uint32_t o = t ^ j;
         if (o > t) {
           const uint32_t x = list[t], y = list[o];

@@ -114,7 +114,8 @@ def build_steps(stages, rank: int, world: int, key_type: bool = False, on_device
     edges = [0] + [min(x, HIST_BINS) for x in splitters] + [HIST_BINS]
     recv_counts = [int(h[edges[rank]: edges[rank + 1]].sum()) for h in hists]  # what each rank holds for my range
     # -- collective 3: the samples travel to the rank that owns their key range
-    send, send_counts = stages.partition(splitters, shift, world)  # int32 [n, 4] grouped by destination
+    send_counts = [int(hists[rank][edges[d]: edges[d + 1]].sum()) for d in range(world)]  # what I hold for every range
+    send = stages.partition(splitters, shift, world)  # int32 [n, 4] grouped by destination
     recv = yield ("all_to_all", send, send_counts, recv_counts)
     stages.reduce(recv)
     # -- collective 4: [solo times | size of the table shard]; each key's solo row was reduced by exactly one rank
@@ -292,9 +293,8 @@ class GpuStages:
     def partition(self, splitters, shift, world):
         send = torch.empty((max(self.n_samples, 1), 4), dtype=torch.int32, device=self.device)
         sp = (ctypes.c_uint32 * max(len(splitters), 1))(*splitters)
-        counts = (ctypes.c_uint64 * world)()
-        self._ck(self.lib.ks_mg_partition(self.h, sp, shift, world, ctypes.c_void_p(send.data_ptr()), send.shape[0], counts), "ks_mg_partition")
-        return send[: self.n_samples], [int(c) for c in counts]
+        self._ck(self.lib.ks_mg_partition(self.h, sp, shift, world, ctypes.c_void_p(send.data_ptr()), send.shape[0], None), "ks_mg_partition")
+        return send[: self.n_samples]
 
     def solo_export(self):
         t = self.zeros((self.n_keys,), torch.float64)

@@ -118,7 +118,7 @@ class FakeStages:
         for sp in splitters:
             dest += sp <= b
         order = np.argsort(dest, kind="stable")
-        return torch.from_numpy(self.smp[order].view(np.int32).copy()), np.bincount(dest, minlength=world).tolist()
+        return torch.from_numpy(self.smp[order].view(np.int32).copy())
 
     def reduce(self, recv):
         smp = recv.numpy().view(np.uint32).reshape(-1, 4)

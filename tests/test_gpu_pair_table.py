@@ -102,3 +102,15 @@ def test_error_statuses(builder):
     keys, pairs = builder.build(rec, time_ordered=True)
     okeys, opairs = O.build_pair_table(rec)
     assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_sparse_trace_uses_64_bit_windows(builder):
+    # bursts of launches separated by idle gaps of 5 s: a join window then spans more than 2^31 ns
+    rec = trace.generate(trace.config("c3", 40_000), interleave_solo=True)
+    gap = (np.arange(len(rec), dtype=np.uint64) // np.uint64(64)) * np.uint64(5_000_000_000)
+    rec["start_ns"] += gap
+    rec["end_ns"] += gap
+    keys, pairs = builder.build(rec, time_ordered=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert opairs["count"].sum() > 10_000
+    assert_tables_match(keys, pairs, okeys, opairs)
