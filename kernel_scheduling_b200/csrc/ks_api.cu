@@ -50,7 +50,7 @@ struct ks_handle {
   DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
   DevBuf samples[2];  // the sample stream, 16-byte items {sort key, lane 0, lane 1, lane 2}; two sets for the sort
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
-  DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows;
+  DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows;
   DevBuf tmp[6];
 
   // results of the last ks_build_table
@@ -360,9 +360,10 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
 int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, uint64_t n_values, uint32_t max_rows) {
   const uint32_t max_large = (uint32_t)(n_values / kMidMax) + 1;
   const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
-  KS_ENSURE(h, h->stats, ((size_t)max_rows + 1) * sizeof(RowStats));
+  KS_ENSURE(h, h->stats, ((size_t)max_rows + 257) * sizeof(RowStats));
   KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
   KS_ENSURE(h, h->small_rows, ((size_t)max_rows + 1) * 4);
+  KS_ENSURE(h, h->small8_rows, ((size_t)max_rows + 1) * 4);
   KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
   KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
@@ -377,6 +378,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   s.stats = as<RowStats>(h->stats);
   s.mid_rows = as<uint32_t>(h->big_rows);
   s.small_rows = as<uint32_t>(h->small_rows);
+  s.small8_rows = as<uint32_t>(h->small8_rows);
   s.large = as<LargeRow>(h->large_rows);
   s.chunk_row = as<uint32_t>(h->chunk_row);
   s.chunk_idx = as<uint32_t>(h->chunk_idx);
@@ -390,7 +392,8 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   KS_CUDA(h, cudaEventRecord(h->fork_ev, h->stream));
   KS_CUDA(h, cudaStreamWaitEvent(h->aux[0], h->fork_ev, 0));
   KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->fork_ev, 0));
-  k_seg_small<<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
+  k_seg_small<8><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
+  k_seg_small<32><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
   k_seg_mid<<<h->sm_count * 4, 256, 0, h->aux[1]>>>(s);
   KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
   KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
@@ -405,7 +408,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[1], 0));
-  h->launches += 6 + 2 * kLargeRounds;
+  h->launches += 7 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -541,7 +544,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }

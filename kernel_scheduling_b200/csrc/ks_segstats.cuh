@@ -9,7 +9,7 @@
 //
 //   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
 //                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
-//   small  (n <= 32)      k_seg_small: one warp per row, shuffle reductions and a 32-wide bitonic network.
+//   small  (n <= 32)      k_seg_small<W>: W = 8 or 32 lanes per row, shuffle reductions and a W-wide bitonic network.
 //   mid    (n <= 1024)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
 //                         only the bits in which the row's values can differ are walked, 8 per round, with 256-bin
 //                         histograms in the warp's own shared memory -- no block-wide barrier anywhere.
@@ -55,7 +55,8 @@ struct SegArgs {
   const uint32_t* n_rows_dev;
   uint32_t max_rows;
   RowStats* stats;
-  uint32_t* small_rows;    // [max_rows]
+  uint32_t* small_rows;    // [max_rows] rows of 9..32 samples
+  uint32_t* small8_rows;   // [max_rows] rows of 5..8 samples
   uint32_t* mid_rows;      // [max_rows]
   LargeRow* large;         // [max_large]
   uint32_t* chunk_row;     // [max_chunks] index into large[]
@@ -63,7 +64,7 @@ struct SegArgs {
   uint32_t* large_hist;    // [max_large][2 * kLanes][256]
   uint32_t max_large, max_chunks;
   int round;
-  Control* ctl;            // n_small / n_big = small / mid rows, ticket = large rows, scratch0 = chunks,
+  Control* ctl;            // pad32 / n_small / n_big = rows of 5..8 / 9..32 / mid rows, ticket = large rows, scratch0 = chunks,
                            // pad[0..3] = unresolved selection states per round
 };
 
@@ -141,18 +142,23 @@ __device__ __forceinline__ void push_row(uint32_t* list, uint32_t* counter, bool
 }
 
 __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
+  // the statistics of 256 consecutive rows are 18 KB of consecutive memory: staged here, written with coalesced stores
+  constexpr int kWords = sizeof(RowStats) / 4;
+  __shared__ uint32_t stage[256 * kWords];
   const uint32_t n_rows = min(*a.n_rows_dev, a.max_rows);
-  const uint32_t n_round = (n_rows + 31u) & ~31u;  // whole warps take part in the list pushes
-  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n_round; row += gridDim.x * blockDim.x) {
+  const uint32_t n_round = (n_rows + 255u) & ~255u;  // whole CTAs take part in the staging and the list pushes
+  for (uint32_t row0 = blockIdx.x * blockDim.x; row0 < n_round; row0 += gridDim.x * blockDim.x) {
+    const uint32_t row = row0 + threadIdx.x;
     const bool valid = row < n_rows;
     const uint32_t s = valid ? a.row_start[row] : 0, cnt = valid ? a.row_start[row + 1] - s : 0;
-    push_row(a.small_rows, &a.ctl->n_small, valid && cnt > 4 && cnt <= kSmallSegment, row);
+    push_row(a.small8_rows, &a.ctl->pad32, valid && cnt > 4 && cnt <= 8, row);
+    push_row(a.small_rows, &a.ctl->n_small, valid && cnt > 8 && cnt <= kSmallSegment, row);
     push_row(a.mid_rows, &a.ctl->n_big, valid && cnt > kSmallSegment && cnt <= kMidMax, row);
-    if (!valid) continue;
-    RowStats* st = a.stats + row;
-    if (cnt == 0) {  // only the stage API can hand in an empty segment
-      for (int l = 0; l < a.n_lanes; ++l) { st->sum[l] = 0; st->mn[l] = 0; st->mx[l] = 0; st->lo[l] = 0; st->hi[l] = 0; }
-    } else if (cnt <= 4) {
+    RowStats st;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) { st.sum[l] = 0; st.mn[l] = 0; st.mx[l] = 0; st.lo[l] = 0; st.hi[l] = 0; }
+    // empty rows (stage API only) and tiny rows are finished here
+    if (valid && cnt > 0 && cnt <= 4) {
       Val3 x[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -162,7 +168,6 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
       const uint32_t i_max = cnt - 1, i_lo = (cnt - 1) >> 1, i_hi = cnt >> 1;
 #pragma unroll
       for (int l = 0; l < kLanes; ++l) {
-        if (l >= a.n_lanes) break;
         uint32_t x0 = x[0].v[l], x1 = x[1].v[l], x2 = x[2].v[l], x3 = x[3].v[l];
         const unsigned long long sum = (unsigned long long)x0 + (cnt > 1 ? x1 : 0u) + (cnt > 2 ? x2 : 0u) + (cnt > 3 ? x3 : 0u);
         uint32_t t;
@@ -170,56 +175,93 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
         KS_CSWAP(x0, x1) KS_CSWAP(x2, x3) KS_CSWAP(x0, x2) KS_CSWAP(x1, x3) KS_CSWAP(x1, x2)
 #undef KS_CSWAP
         auto pick = [&](uint32_t i) { return i == 0 ? x0 : i == 1 ? x1 : i == 2 ? x2 : x3; };
-        st->sum[l] = sum;
-        st->mn[l] = x0;
-        st->mx[l] = pick(i_max);
-        st->lo[l] = pick(i_lo);
-        st->hi[l] = pick(i_hi);
+        st.sum[l] = sum;
+        st.mn[l] = x0;
+        st.mx[l] = pick(i_max);
+        st.lo[l] = pick(i_lo);
+        st.hi[l] = pick(i_hi);
       }
-    } else if (cnt > kMidMax) {
+    } else if (valid && cnt > kMidMax) {
       const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
       const uint32_t l = atomicAdd(&a.ctl->ticket, 1u);
       const uint32_t cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
-      if (l >= a.max_large || cbase + nch > a.max_chunks) { atomicOr(&a.ctl->err, kErrTooLarge); continue; }
-      LargeRow* L = a.large + l;
-      L->row = row; L->start = s; L->cnt = cnt;
-      for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
-      for (uint32_t c = 0; c < nch; ++c) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
+      if (l >= a.max_large || cbase + nch > a.max_chunks) {
+        atomicOr(&a.ctl->err, kErrTooLarge);
+      } else {
+        LargeRow* L = a.large + l;
+        L->row = row; L->start = s; L->cnt = cnt;
+        for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
+        for (uint32_t c = 0; c < nch; ++c) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
+      }
     }
+    // rows of the other classes get zeros now and their statistics from the class kernels, which run after this one
+    __syncthreads();
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&st);
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) stage[threadIdx.x * kWords + i] = w[i];
+    __syncthreads();
+    const uint32_t rows_here = min(256u, n_rows > row0 ? n_rows - row0 : 0u);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(a.stats + row0);
+    for (uint32_t i = threadIdx.x; i < rows_here * kWords; i += blockDim.x) dst[i] = stage[i];
   }
 }
 
-// one warp per row of 5..32 samples: shuffle reductions and a 32-wide bitonic network
+// W lanes per row (W = 8 for rows of 5..8 samples, 32 for 9..32): a warp takes 32 / W rows at a time; shuffle
+// reductions and a W-wide bitonic network inside each group
+template <int W>
+__device__ __forceinline__ uint32_t bitonic_sort_group(uint32_t v) {
+  const uint32_t sub = lane_id() & (W - 1);
+#pragma unroll
+  for (int k = 2; k <= W; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const uint32_t o = __shfl_xor_sync(0xFFFFFFFFu, v, j);
+      const bool up = (sub & k) == 0;
+      const bool lower = (sub & j) == 0;
+      v = (lower == up) ? min(v, o) : max(v, o);
+    }
+  }
+  return v;
+}
+
+template <int W>
 __global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
-  const uint32_t n_small = min(a.ctl->n_small, a.max_rows);
-  const uint32_t lane = lane_id();
+  constexpr uint32_t G = 32 / W;
+  const uint32_t* list = W == 8 ? a.small8_rows : a.small_rows;
+  const uint32_t n_list = min(W == 8 ? a.ctl->pad32 : a.ctl->n_small, a.max_rows);
+  const uint32_t lane = lane_id(), sub = lane & (W - 1), gbase = lane & ~(uint32_t)(W - 1);
   const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-  for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_small; t += warps) {
-    const uint32_t row = a.small_rows[t];
-    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
-    RowStats* st = a.stats + row;
-    const bool have = lane < cnt;
+  const uint32_t n_round = (n_list + G - 1) / G * G;
+  for (uint32_t t0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G; t0 < n_round; t0 += warps * G) {
+    const uint32_t t = t0 + lane / W;
+    const bool valid = t < n_list;
+    const uint32_t row = valid ? list[t] : 0;
+    const uint32_t s = valid ? a.row_start[row] : 0, cnt = valid ? a.row_start[row + 1] - s : 1;
+    const bool have = valid && sub < cnt;
     Val3 x;
-    if (have) x = seg_fetch(a, (size_t)s + lane);
+    if (have) x = seg_fetch(a, (size_t)s + sub);
     else { x.v[0] = x.v[1] = x.v[2] = 0; }
+    RowStats* st = a.stats + row;
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) {
       if (l >= a.n_lanes) break;
       const uint32_t v = x.v[l];
-      const unsigned long long sum = warp_sum64(v);
-      const uint32_t sorted = bitonic_sort32(have ? v : 0xFFFFFFFFu);
-      const uint32_t mn = __shfl_sync(0xFFFFFFFFu, sorted, 0);
-      const uint32_t mx = __shfl_sync(0xFFFFFFFFu, sorted, cnt - 1);
-      const uint32_t lo = __shfl_sync(0xFFFFFFFFu, sorted, (cnt - 1) >> 1);
-      const uint32_t hi = __shfl_sync(0xFFFFFFFFu, sorted, cnt >> 1);
-      if (lane == 0) { st->sum[l] = sum; st->mn[l] = mn; st->mx[l] = mx; st->lo[l] = lo; st->hi[l] = hi; }
+      unsigned long long sum = v;
+#pragma unroll
+      for (int o = W / 2; o; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+      const uint32_t sorted = bitonic_sort_group<W>(have ? v : 0xFFFFFFFFu);
+      const uint32_t mn = __shfl_sync(0xFFFFFFFFu, sorted, gbase);
+      const uint32_t mx = __shfl_sync(0xFFFFFFFFu, sorted, gbase + cnt - 1);
+      const uint32_t lo = __shfl_sync(0xFFFFFFFFu, sorted, gbase + ((cnt - 1) >> 1));
+      const uint32_t hi = __shfl_sync(0xFFFFFFFFu, sorted, gbase + (cnt >> 1));
+      if (valid && sub == 0) { st->sum[l] = sum; st->mn[l] = mn; st->mx[l] = mx; st->lo[l] = lo; st->hi[l] = hi; }
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------
 // one warp per row of 33..2048 samples; the three lanes are selected together, every sample is loaded once per round
-__global__ void __launch_bounds__(256) k_seg_mid(const SegArgs a) {
+__global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
   __shared__ uint32_t hist_all[8][kLanes][256];
   uint32_t (*hist)[256] = hist_all[threadIdx.x >> 5];
   const uint32_t lane = lane_id();
