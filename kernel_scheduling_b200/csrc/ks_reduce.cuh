@@ -178,45 +178,72 @@ __global__ void __launch_bounds__(256) k_finalize_keys(const FinalArgs a) {
 }
 
 __global__ void __launch_bounds__(256) k_finalize_pairs(const FinalArgs a) {
+  // 256 consecutive rows per CTA and iteration: their statistics (18 KB) come in and their table rows (32 KB) go out as
+  // consecutive memory, staged through shared memory so that every global access is coalesced
+  constexpr int kInWords = sizeof(RowStats) / 4, kOutWords = sizeof(ks_pair_row) / 4;
+  constexpr int kRowVec = kOutWords / 4 + 1;  // 16-byte vectors per staged row, one of padding: conflict-free 128-bit stores
+  __shared__ __align__(16) uint32_t stage[256 * kRowVec * 4];
   const uint32_t n_rows = a.ctl->n_rows, first = a.ctl->ticket2;  // rows [0, first) are the solo rows
   const uint32_t nk = a.ctl->n_keys;
   const double nan = __longlong_as_double(0x7FF8000000000000ll);
-  for (uint32_t r = first + blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += gridDim.x * blockDim.x) {
-    const uint32_t out = r - first;
-    if (out >= a.max_pair_rows) { atomicOr(&a.ctl->err, kErrPairTableFull); return; }
-    const uint32_t pid = a.row_key[r] - nk;
-    const uint32_t ka = pid / nk, kb = pid % nk;
-    const RowStats st = a.stats[r];
-    const uint32_t cnt = a.row_start[r + 1] - a.row_start[r];
-    const double sa = a.solo_ns[ka], sb = a.solo_ns[kb];
-    const bool va = sa > 0.0, vb = sb > 0.0;  // false for NaN
+  const uint32_t n_out = n_rows > first ? n_rows - first : 0;
+  for (uint32_t out0 = blockIdx.x * 256u; out0 < n_out; out0 += gridDim.x * 256u) {
+    const uint32_t here = min(256u, n_out - out0);
+    if (out0 + here > a.max_pair_rows) { if (threadIdx.x == 0) atomicOr(&a.ctl->err, kErrPairTableFull); return; }
+    __syncthreads();
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.stats + first + out0);
+    for (uint32_t i = threadIdx.x; i < here * kInWords; i += 256) stage[i] = src[i];
+    __syncthreads();
     ks_pair_row p;
-    p.key_a = a.keys_sorted[ka];
-    p.key_b = a.keys_sorted[kb];
-    p.count = cnt;
-    p.flags = (va ? 1ull : 0ull) | (vb ? 2ull : 0ull);
-    if (va) {
-      p.sum_a = (double)st.sum[0] / sa;
-      p.mean_a = p.sum_a / (double)cnt;
-      p.min_a = (double)st.mn[0] / sa;
-      p.max_a = (double)st.mx[0] / sa;
-      p.median_a = ((double)st.lo[0] / sa + (double)st.hi[0] / sa) * 0.5;
-    } else {
-      p.sum_a = p.mean_a = p.min_a = p.max_a = p.median_a = nan;
+    const bool mine = threadIdx.x < here;
+    if (mine) {
+      const uint32_t r = first + out0 + threadIdx.x;
+      RowStats st;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&st);
+#pragma unroll
+      for (int i = 0; i < kInWords; ++i) w[i] = stage[threadIdx.x * kInWords + i];
+      const uint32_t pid = a.row_key[r] - nk;
+      const uint32_t ka = pid / nk, kb = pid % nk;
+      const uint32_t cnt = a.row_start[r + 1] - a.row_start[r];
+      const double sa = a.solo_ns[ka], sb = a.solo_ns[kb];
+      const bool va = sa > 0.0, vb = sb > 0.0;  // false for NaN
+      p.key_a = a.keys_sorted[ka];
+      p.key_b = a.keys_sorted[kb];
+      p.count = cnt;
+      p.flags = (va ? 1ull : 0ull) | (vb ? 2ull : 0ull);
+      if (va) {
+        p.sum_a = (double)st.sum[0] / sa;
+        p.mean_a = p.sum_a / (double)cnt;
+        p.min_a = (double)st.mn[0] / sa;
+        p.max_a = (double)st.mx[0] / sa;
+        p.median_a = ((double)st.lo[0] / sa + (double)st.hi[0] / sa) * 0.5;
+      } else {
+        p.sum_a = p.mean_a = p.min_a = p.max_a = p.median_a = nan;
+      }
+      if (vb) {
+        p.sum_b = (double)st.sum[1] / sb;
+        p.mean_b = p.sum_b / (double)cnt;
+        p.min_b = (double)st.mn[1] / sb;
+        p.max_b = (double)st.mx[1] / sb;
+        p.median_b = ((double)st.lo[1] / sb + (double)st.hi[1] / sb) * 0.5;
+      } else {
+        p.sum_b = p.mean_b = p.min_b = p.max_b = p.median_b = nan;
+      }
+      // efficiency falls as the span grows, so its two middle values come from the span's two middle values
+      p.efficiency = (va && vb) ? ((sa + sb) / (double)st.lo[2] + (sa + sb) / (double)st.hi[2]) * 0.5 : nan;
+      p.span_sum_ns = st.sum[2];
     }
-    if (vb) {
-      p.sum_b = (double)st.sum[1] / sb;
-      p.mean_b = p.sum_b / (double)cnt;
-      p.min_b = (double)st.mn[1] / sb;
-      p.max_b = (double)st.mx[1] / sb;
-      p.median_b = ((double)st.lo[1] / sb + (double)st.hi[1] / sb) * 0.5;
-    } else {
-      p.sum_b = p.mean_b = p.min_b = p.max_b = p.median_b = nan;
+    __syncthreads();
+    if (mine) {
+      const uint4* q = reinterpret_cast<const uint4*>(&p);
+      uint4* d = reinterpret_cast<uint4*>(stage) + threadIdx.x * kRowVec;
+#pragma unroll
+      for (int i = 0; i < kOutWords / 4; ++i) d[i] = q[i];
     }
-    // efficiency falls as the span grows, so its two middle values come from the span's two middle values
-    p.efficiency = (va && vb) ? ((sa + sb) / (double)st.lo[2] + (sa + sb) / (double)st.hi[2]) * 0.5 : nan;
-    p.span_sum_ns = st.sum[2];
-    a.pair_rows[out] = p;
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(a.pair_rows + out0);
+    const uint4* sv = reinterpret_cast<const uint4*>(stage);
+    for (uint32_t i = threadIdx.x; i < here * (kOutWords / 4); i += 256) dst[i] = sv[(i / (kOutWords / 4)) * kRowVec + i % (kOutWords / 4)];
   }
 }
 
