@@ -62,6 +62,10 @@ struct ks_handle {
   uint64_t mg_n_owned = 0, mg_n_halo = 0, mg_nk = 0, mg_n_samples = 0;
   uint32_t mg_flags = 0;
   int mg_cur = 0;
+
+  // what the last ks_build_table saw: lets the next call queue every stage without reading counts back in between
+  bool hint_valid = false;
+  uint64_t hint_samples = 0, hint_nk = 0, hint_rows = 0;
   cudaEvent_t ev[12]{};
   // the three size classes of K4 are independent of one another: they run side by side on two helper streams
   cudaStream_t aux[2]{};
@@ -180,7 +184,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 
 // K2 driver for the 16-byte sample stream: sorts set 0/1 of h->samples on key bits [0, end_bit); returns the set that
 // holds the result.
-int radix_sort16(ks_handle* h, uint64_t n, int end_bit) {
+int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr) {
   constexpr int ITEMS = 8;
   constexpr int TILE = kSortThreads * ITEMS;
   if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
@@ -194,7 +198,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit) {
   uint32_t* gbase = hist + 8 * 256;
   KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
   const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
-  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(as<uint32_t>(h->samples[0]), 4u, nullptr, (uint32_t)n, 0, end_bit, hist);
+  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(as<uint32_t>(h->samples[0]), 4u, n_dev, (uint32_t)n, 0, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
   constexpr size_t smem = sort16_smem_bytes<ITEMS>();
@@ -210,7 +214,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit) {
     SortPass16Args a{};
     a.in = as<uint4>(h->samples[cur]);
     a.out = as<uint4>(h->samples[cur ^ 1]);
-    a.n_dev = nullptr;
+    a.n_dev = n_dev;
     a.n = (uint32_t)n;
     a.shift = 8 * p;
     a.bits = std::min(8, end_bit - a.shift);
@@ -414,7 +418,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
 }
 
 // rows + segment statistics over sorted samples (set `s`), n samples
-int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t max_rows) {
+int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t max_rows, const uint32_t* n_dev = nullptr) {
   const uint32_t max_tiles = (uint32_t)((n + kRowsTile - 1) / kRowsTile);
   KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
   KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
@@ -422,7 +426,7 @@ int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t ma
   RowsArgs r{};
   r.skey = reinterpret_cast<const uint32_t*>(items);
   r.key_stride = 4;
-  r.n_dev = nullptr;
+  r.n_dev = n_dev;
   r.n = (uint32_t)n;
   r.tile_cnt = as<uint32_t>(h->tile_cnt);
   r.row_start = as<uint32_t>(h->row_start);
@@ -565,6 +569,10 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_build_table: 2^30 records or more in one call");
   KS_CUDA(h, cudaSetDevice(h->device));
   const bool assume_ordered = (flags & KS_ASSUME_TIME_ORDERED) != 0;
+  // With the caller vouching for the order and the previous call's counts as a guide, every stage is queued without a
+  // host round trip; the kernels take the actual counts from device memory, clamped to the bounds the buffers were
+  // sized for, and the bounds are checked at the end (a violated guess reruns the call the slow way).
+  const bool hinted = assume_ordered && h->hint_valid;
   h->n_pair_rows = h->n_key_rows = 0;
   cudaEvent_t* ev = h->ev;
 
@@ -612,6 +620,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     if (attempt == 0) cudaEventRecord(ev[5], h->stream);
     { int r = run_join(h, tl, n, cap, nullptr, nullptr); if (r) return r; }
     cudaEventRecord(ev[6], h->stream);
+    if (hinted) { n_samples = std::min<uint64_t>(cap, h->hint_samples + h->hint_samples / 4 + 4096); break; }  // a bound, not the count
     { int r = read_ctl(h); if (r) return r; }
     const int st = status_of_err(h->h_ctl->err, assume_ordered);
     if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
@@ -624,17 +633,19 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     if (r) return r;
   }
   cudaEventRecord(ev[10], h->stream);
-  const uint64_t nk = h->h_ctl->n_keys, n_solo = h->h_ctl->n_solo;
+  const uint64_t nk = hinted ? h->hint_nk : h->h_ctl->n_keys;
+  const uint32_t* n_dev = hinted ? reinterpret_cast<const uint32_t*>(&h->d_ctl->n_pairs) : nullptr;
 
-  // K2: group the samples by sort key
-  const int end_bit = bit_length(nk + nk * nk);
-  const int cur = radix_sort16(h, n_samples, end_bit);
+  // K2: group the samples by sort key (whole bytes of the key when the key count is only a guess)
+  const int end_bit = hinted ? 8 * ((bit_length(nk + nk * nk) + 7) / 8) : bit_length(nk + nk * nk);
+  const int cur = radix_sort16(h, n_samples, end_bit, n_dev);
   if (cur < 0) return cur;
   cudaEventRecord(ev[7], h->stream);
 
   // K4: rows, statistics, tables
-  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n_samples, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
-  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n_samples, max_rows); if (r) return r; }
+  uint32_t max_rows = (uint32_t)std::min<uint64_t>(n_samples, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
+  if (hinted) max_rows = (uint32_t)std::min<uint64_t>(max_rows, h->hint_rows + h->hint_rows / 4 + 4096);
+  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n_samples, max_rows, n_dev); if (r) return r; }
   cudaEventRecord(ev[8], h->stream);
   KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
   FinalArgs f{};
@@ -652,14 +663,30 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   f.pair_rows = as<ks_pair_row>(h->pair_rows);
   f.max_pair_rows = max_rows;
   f.ctl = h->d_ctl;
-  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
+  const uint64_t nk_launch = hinted ? kMaxKeys : nk;  // the kernel clamps to the key count in device memory
+  if (nk_launch) k_finalize_keys<<<(unsigned)((nk_launch + 255) / 256), 256, 0, h->stream>>>(f);
   k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
-  h->launches += nk ? 2 : 1;
+  h->launches += nk_launch ? 2 : 1;
   KS_CUDA(h, cudaGetLastError());
   cudaEventRecord(ev[9], h->stream);
   { int r = read_ctl(h); if (r) return r; }
+  if (hinted) {
+    const Control& g = *h->h_ctl;
+    const bool guess_held = g.n_pairs <= n_samples && bit_length((uint64_t)g.n_keys + (uint64_t)g.n_keys * g.n_keys) <= end_bit && g.n_rows <= max_rows &&
+                            !(g.err & (kErrTooLarge | kErrPairTableFull));
+    if (!guess_held) {  // the trace changed shape: do it again, reading the counts back between the stages
+      h->hint_valid = false;
+      return ks_build_table(h, records, n, flags, info);
+    }
+  }
   const int st = status_of_err(h->h_ctl->err, assume_ordered);
-  if (st) return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st));
+  if (st) { h->hint_valid = false; return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st)); }
+  h->hint_valid = true;
+  h->hint_samples = h->h_ctl->n_pairs;
+  h->hint_nk = h->h_ctl->n_keys;
+  h->hint_rows = h->h_ctl->n_rows;
+  const uint64_t n_solo = h->h_ctl->n_solo;
+  n_samples = h->h_ctl->n_pairs;
 
   const Control& c = *h->h_ctl;
   h->n_key_rows = c.n_keys;

@@ -34,7 +34,7 @@ __device__ __forceinline__ bool run_starts_at(const uint32_t* skey, uint32_t str
 
 __global__ void __launch_bounds__(256) k_rows_count(const RowsArgs a) {
   __shared__ uint32_t warp_tot[8];
-  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t n = a.n_dev ? min(*a.n_dev, a.n) : a.n;
   const uint32_t ntiles = (n + kRowsTile - 1) / kRowsTile;
   for (uint32_t tile = blockIdx.x; tile < ntiles && tile < a.max_tiles; tile += gridDim.x) {
     uint32_t c = 0;
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) k_rows_count(const RowsArgs a) {
 __global__ void __launch_bounds__(1024) k_rows_scan(const RowsArgs a) {
   __shared__ uint32_t warp_tot[32];
   __shared__ uint32_t carry;
-  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t n = a.n_dev ? min(*a.n_dev, a.n) : a.n;
   const uint32_t ntiles = min((n + kRowsTile - 1) / kRowsTile, a.max_tiles);
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
@@ -78,18 +78,24 @@ __global__ void __launch_bounds__(1024) k_rows_scan(const RowsArgs a) {
   }
   if (threadIdx.x == 0) {
     const uint32_t rows = carry;
-    a.ctl->n_rows = rows;
-    if (rows > a.max_rows) atomicOr(&a.ctl->err, kErrTooLarge);
-    else a.row_start[rows] = n;
+    if (rows > a.max_rows) {
+      // more rows than the arrays hold: report it and leave NO rows, so that no later kernel walks stale row offsets
+      atomicOr(&a.ctl->err, kErrTooLarge);
+      a.ctl->n_rows = 0;
+      a.row_start[0] = 0;
+    } else {
+      a.ctl->n_rows = rows;
+      a.row_start[rows] = n;
+    }
   }
 }
 
 __global__ void __launch_bounds__(256) k_rows_fill(const RowsArgs a) {
   __shared__ uint32_t word_base[kRowsTile / 32];  // run starts in front of each 32-sample word of the tile
-  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t n = a.n_dev ? min(*a.n_dev, a.n) : a.n;
   const uint32_t nk = a.ctl->n_keys;
   const uint32_t ntiles = min((n + kRowsTile - 1) / kRowsTile, a.max_tiles);
-  if (a.ctl->n_rows > a.max_rows) return;
+  if (a.ctl->err & kErrTooLarge) return;  // the scan found more rows than the arrays hold
   const uint32_t lane = lane_id(), warp = threadIdx.x >> 5;
   uint32_t solo_rows = 0;
   for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {

@@ -66,7 +66,7 @@ template <typename KeyT>
 __global__ void __launch_bounds__(256) k_radix_hist(const KeyT* __restrict__ keys, uint32_t stride, const uint32_t* n_dev, uint32_t n, int begin_bit,
                                                     int end_bit, uint32_t* __restrict__ hist /*[passes][256]*/) {
   __shared__ uint32_t sh[8 * 256];
-  if (n_dev) n = *n_dev;
+  if (n_dev) n = min(*n_dev, n);  // n is then the bound the buffers were sized for
   const int passes = (end_bit - begin_bit + 7) / 8;
   for (int i = threadIdx.x; i < passes * 256; i += blockDim.x) sh[i] = 0;
   __syncthreads();
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
   uint32_t* s_gpos = warp_hist + kSortWarps * 256;                            // [256]
   uint32_t* s_misc = s_gpos + 256;                                            // [16]
 
-  const uint32_t n = a.n_dev ? *a.n_dev : a.n;
+  const uint32_t n = a.n_dev ? min(*a.n_dev, a.n) : a.n;  // with n_dev, a.n is the bound the buffers were sized for
   const uint32_t ntiles = (n + TILE - 1) / TILE;
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const uint32_t dmask = (1u << a.bits) - 1u;

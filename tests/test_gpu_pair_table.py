@@ -114,3 +114,29 @@ def test_sparse_trace_uses_64_bit_windows(builder):
     okeys, opairs = O.build_pair_table(rec)
     assert opairs["count"].sum() > 10_000
     assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_shape_changes_between_calls(builder):
+    # with time-ordered input a call sizes its launches from what the previous call saw and verifies the guess at the
+    # end; a trace that is larger, has more keys or fewer rows than the last one must give the same table as ever
+    for cfg, n in (("c1", 20_000), ("c2", 300_000), ("c1", 5_000), ("c3", 150_000), ("c3", 150_000)):
+        rec = trace.generate(trace.config(cfg, n))
+        keys, pairs = builder.build(rec, time_ordered=True)
+        okeys, opairs = O.build_pair_table(rec)
+        assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_row_capacity_is_an_error_not_a_fault():
+    from kernel_scheduling_b200 import _lib
+    from kernel_scheduling_b200.pair_table import PairTableBuilder
+
+    rec = trace.generate(trace.config("c1", 20_000))
+    with PairTableBuilder(device=0, max_pair_rows=16) as small:
+        for _ in range(2):  # the second call takes the path that trusts the previous call's counts
+            with pytest.raises(_lib.KsError) as e:
+                small.build(rec, time_ordered=True)
+            assert e.value.status in (_lib.ERR_TOO_LARGE, _lib.ERR_TABLE_FULL)
+        tiny = rec[:40]
+        keys, pairs = small.build(tiny, time_ordered=True)
+        okeys, opairs = O.build_pair_table(tiny)
+        assert_tables_match(keys, pairs, okeys, opairs)
