@@ -225,7 +225,7 @@ def main():
 
         def step_e2e():
             if world == 1:
-                return builder.build(rec_pinned, time_ordered=True)
+                return builder.build(rec_pinned, time_ordered=True, pinned=True)
             with torch.cuda.stream(stream):
                 d = host.to("cuda", non_blocking=True)
                 return parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, d), rank, world))

@@ -111,6 +111,9 @@ const char* ks_last_error(ks_handle* h);
 void* ks_stream(ks_handle* h);
 /* kernels of this library launched through the handle so far (cumulative) */
 uint64_t ks_launch_count(ks_handle* h);
+/* page-locked host buffers for records and tables that cross PCIe on every call */
+void* ks_pinned_alloc(uint64_t bytes);
+void ks_pinned_free(void* p);
 
 /* ---- the whole path.  Stands where the reference runs its offline post-processing over the agents' logs
  * (scheduler/postprocess.py:8-41 and the absent make_pair_eff.py named at scheduler_daemon.cpp:5,193,848).

@@ -52,6 +52,8 @@ KS_API = [
     ("ks_last_error", [c_void_p], c_char_p),
     ("ks_stream", [c_void_p], c_void_p),
     ("ks_launch_count", [c_void_p], c_uint64),
+    ("ks_pinned_alloc", [c_uint64], c_void_p),
+    ("ks_pinned_free", [c_void_p], None),
     ("ks_build_table", [c_void_p, c_void_p, c_uint64, c_uint32, POINTER(KsTableInfo)], c_int64),
     ("ks_copy_pair_rows", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_copy_key_rows", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),

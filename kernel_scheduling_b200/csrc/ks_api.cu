@@ -562,6 +562,14 @@ const char* ks_last_error(ks_handle* h) { return h ? h->last_error.c_str() : g_n
 void* ks_stream(ks_handle* h) { return h ? reinterpret_cast<void*>(h->stream) : nullptr; }
 uint64_t ks_launch_count(ks_handle* h) { return h ? h->launches : 0; }
 
+// page-locked host memory for inputs and outputs that cross PCIe every call (pageable memory halves the copy rate)
+void* ks_pinned_alloc(uint64_t bytes) {
+  void* p = nullptr;
+  if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) { g_null_error = "ks_pinned_alloc: cudaMallocHost failed"; return nullptr; }
+  return p;
+}
+void ks_pinned_free(void* p) { if (p) cudaFreeHost(p); }
+
 // ---------------------------------------------------------------------------------------------------------
 int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info) {
   if (!h) return -KS_ERR_ARG;

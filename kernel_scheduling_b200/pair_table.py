@@ -24,10 +24,14 @@ class PairTableBuilder:
         if not self._h:
             raise _lib.KsError(_lib.ERR_CUDA, self._lib.ks_last_error(None).decode() or "ks_create failed (no CUDA device?)")
         self.info = None
+        self._pinned_bufs = {}
 
     # -- plumbing
     def close(self):
         if getattr(self, "_h", None):
+            for p, _ in self._pinned_bufs.values():
+                self._lib.ks_pinned_free(p)
+            self._pinned_bufs = {}
             self._lib.ks_destroy(self._h)
             self._h = None
 
@@ -71,17 +75,43 @@ class PairTableBuilder:
         self.info = info.as_dict()
         return rows
 
-    def fetch(self):
-        """-> (key_rows, pair_rows) of the last build as structured numpy arrays."""
-        pair = np.zeros(int(self.info["n_rows"]), dtype=PAIR_ROW_DTYPE)
-        keys = np.zeros(int(self.info["n_keys"]), dtype=KEY_ROW_DTYPE)
+    def _pinned(self, slot: str, n: int, dtype) -> np.ndarray:
+        """A page-locked array owned by the builder (grown on demand, reused by later calls)."""
+        need = max(n, 1) * dtype.itemsize
+        cur = self._pinned_bufs.get(slot)
+        if cur is None or cur[1] < need:
+            if cur is not None:
+                self._lib.ks_pinned_free(cur[0])
+            size = need + need // 4
+            p = self._lib.ks_pinned_alloc(size)
+            if not p:
+                raise _lib.KsError(_lib.ERR_CUDA, "ks_pinned_alloc failed")
+            cur = self._pinned_bufs[slot] = (p, size)
+        raw = (ctypes.c_uint8 * (n * dtype.itemsize)).from_address(cur[0])
+        return np.frombuffer(raw, dtype=dtype, count=n)
+
+    def fetch(self, pinned: bool = False):
+        """-> (key_rows, pair_rows) of the last build as structured numpy arrays.
+
+        ``pinned=True`` returns views of page-locked buffers owned by the builder (no allocation, full PCIe rate); they
+        are overwritten by the next ``fetch(pinned=True)`` and die with the builder.
+        """
+        n_rows, n_keys = int(self.info["n_rows"]), int(self.info["n_keys"])
+        if pinned:
+            pair, keys = self._pinned("pairs", n_rows, PAIR_ROW_DTYPE), self._pinned("keys", n_keys, KEY_ROW_DTYPE)
+        else:
+            pair, keys = np.zeros(n_rows, dtype=PAIR_ROW_DTYPE), np.zeros(n_keys, dtype=KEY_ROW_DTYPE)
         self._check(self._lib.ks_copy_pair_rows(self._h, _lib.ptr(pair), len(pair), 0), "ks_copy_pair_rows")
         self._check(self._lib.ks_copy_key_rows(self._h, _lib.ptr(keys), len(keys), 0), "ks_copy_key_rows")
         return keys, pair
 
-    def build(self, records, n=None, time_ordered: bool = False, key_type: bool = False):
+    def build(self, records, n=None, time_ordered: bool = False, key_type: bool = False, pinned: bool = False):
         self.build_device(records, n, time_ordered, key_type)
-        return self.fetch()
+        return self.fetch(pinned)
+
+    def pinned_records(self, n: int) -> np.ndarray:
+        """A page-locked record array owned by the builder: fill it and pass it to ``build`` for full-rate host-to-device copies."""
+        return self._pinned("records", n, RECORD_DTYPE)
 
     # -- stages
     def hash_keys(self, records, key_type: bool = False) -> np.ndarray:

@@ -140,3 +140,12 @@ def test_row_capacity_is_an_error_not_a_fault():
         keys, pairs = small.build(tiny, time_ordered=True)
         okeys, opairs = O.build_pair_table(tiny)
         assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_pinned_buffers(builder):
+    rec = trace.generate(trace.config("c1", 30_000))
+    buf = builder.pinned_records(len(rec))
+    buf[:] = rec
+    keys, pairs = builder.build(buf, time_ordered=True, pinned=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert_tables_match(keys, pairs, okeys, opairs)
