@@ -284,8 +284,8 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
     KS_CUDA(h, cudaFuncSetAttribute(k_decode_hash, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes()));
     attr_set = true;
   }
-  const uint64_t ntiles = (n + kDecodeThreads - 1) / kDecodeThreads;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
+  const uint64_t ntiles = (n + kDecodeTile - 1) / kDecodeTile;
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 3);
   k_decode_hash<<<grid, kDecodeThreads, decode_smem_bytes(), h->stream>>>(a);
   ++h->launches;
   KS_CUDA(h, cudaGetLastError());

@@ -1,7 +1,7 @@
 // ks_decode.cuh -- K1: record decode, kernel-key hash and key dictionary in one read of the trace.
 //
-// A CTA streams tiles of 256 records (12,288 contiguous bytes) into shared memory with bulk asynchronous copies
-// (cp.async.bulk, completion on an mbarrier, three tiles in flight), so global memory is read as whole 128-byte
+// A CTA streams tiles of 512 records (24,576 contiguous bytes) into shared memory with bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier, two tiles in flight), so global memory is read as whole 128-byte
 // lines although a record is 48 bytes; each thread then takes its record from shared memory as three 128-bit
 // loads (a 48-byte stride is conflict-free for 128-bit shared loads).  Per record it
 //   * computes the 64-bit kernel key (ks_common.cuh kernel_key),
@@ -19,7 +19,9 @@ namespace ks {
 
 constexpr int kDecodeThreads = 256;
 constexpr int kDecodeStages = 2;
-constexpr int kDecodeTileBytes = kDecodeThreads * 48;
+constexpr int kDecodePerThread = 2;  // two records per thread: two dictionary probes in flight
+constexpr int kDecodeTile = kDecodeThreads * kDecodePerThread;
+constexpr int kDecodeTileBytes = kDecodeTile * 48;
 constexpr uint32_t kCtaCountSlots = 1024;  // per-CTA launch-count cache (open addressing on the dictionary slot)
 
 struct DecodeArgs {
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
   uint32_t* cc_solo = cc_cnt + kCtaCountSlots;                                             // solo launches
 
   const uint32_t tid = threadIdx.x, lane = tid & 31u;
-  const uint64_t ntiles = (a.n + kDecodeThreads - 1) / kDecodeThreads;
+  const uint64_t ntiles = (a.n + kDecodeTile - 1) / kDecodeTile;
   for (uint32_t i = tid; i < kCtaCountSlots; i += kDecodeThreads) { cc_slot[i] = 0; cc_cnt[i] = 0; cc_solo[i] = 0; }
   if (tid == 0) {
     for (int s = 0; s < kDecodeStages; ++s) mbar_init(&bars[s], 1);
@@ -106,8 +108,8 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
   __syncthreads();
 
   auto issue = [&](uint64_t tile, int stage) {
-    const uint64_t first = tile * kDecodeThreads;
-    const uint32_t cnt = (uint32_t)min((uint64_t)kDecodeThreads, a.n - first);
+    const uint64_t first = tile * kDecodeTile;
+    const uint32_t cnt = (uint32_t)min((uint64_t)kDecodeTile, a.n - first);
     const uint32_t bytes = cnt * 48u;
     mbar_expect_tx(&bars[stage], bytes);
     bulk_load(tiles + stage * kDecodeTileBytes, a.records + first * 48ull, bytes, &bars[stage]);
@@ -128,85 +130,94 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
     const uint32_t parity = (it / kDecodeStages) & 1u;
     if (!mbar_wait_bounded(&bars[stage], parity)) err |= kErrWait;  // carry on: the CTA still terminates
 
-    const uint64_t r = tile * kDecodeThreads + tid;
-    const bool valid = r < a.n;
-    const unsigned char* rp = tiles + stage * kDecodeTileBytes + tid * 48;
-    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
-    if (valid) {
-      w0 = *reinterpret_cast<const uint4*>(rp);
-      w1 = *reinterpret_cast<const uint4*>(rp + 16);
-      w2 = *reinterpret_cast<const uint4*>(rp + 32);
-    }
-    const unsigned long long start = (unsigned long long)w2.x | ((unsigned long long)w2.y << 32);
-    const unsigned long long end = (unsigned long long)w2.z | ((unsigned long long)w2.w << 32);
-    // start of the previous record (for the order check)
-    unsigned long long prev = 0;
-    if (valid && r > 0) {
-      if (tid > 0) prev = *reinterpret_cast<const unsigned long long*>(rp - 48 + 32);
-      else prev = *reinterpret_cast<const unsigned long long*>(a.records + (r - 1) * 48ull + 32);
-    }
-    const bool solo = (w1.w & kMetaSoloBit) != 0;
-    const uint64_t key = kernel_key(w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, a.type_mode != 0);
-
-    // every lane looks its key up itself: the keys of a warp are mostly distinct (a Zipf law over a thousand keys), so
-    // grouping equal keys first costs more than the few duplicate probes it saves; the probes hit L2
-    const uint32_t solo_ballot = __ballot_sync(0xFFFFFFFFu, valid && solo && !a.halo);
-    uint32_t slot = 0;
-    if (valid) {
-      bool inserted;
-      slot = dict_find_or_insert(a.dict_keys, key, &inserted);
-      if (slot >= kDictSlots) { err |= kErrTooManyKeys; slot = 0; inserted = false; }
-      if (inserted) {
-        uint4 k0 = w0, k1 = w1;
-        k1.w &= ~kMetaSoloBit;
-        if (a.type_mode) { k0.y = k0.z = k0.w = 0; k1.w &= 0xFF000000u; }
-        a.dict_words[2 * (size_t)slot] = k0;
-        a.dict_words[2 * (size_t)slot + 1] = k1;
+    // ---- phase 1, both records of the thread: fields, key, and the first dictionary probe of each is put in flight
+    uint4 w0[kDecodePerThread], w1[kDecodePerThread];
+    unsigned long long start[kDecodePerThread], end[kDecodePerThread], prev[kDecodePerThread], key[kDecodePerThread], seen[kDecodePerThread];
+    uint64_t r[kDecodePerThread];
+    bool valid[kDecodePerThread];
+#pragma unroll
+    for (int u = 0; u < kDecodePerThread; ++u) {
+      const uint32_t li = u * kDecodeThreads + tid;  // consecutive lanes, consecutive records
+      r[u] = tile * kDecodeTile + li;
+      valid[u] = r[u] < a.n;
+      const unsigned char* rp = tiles + stage * kDecodeTileBytes + li * 48;
+      uint4 w2 = make_uint4(0, 0, 0, 0);
+      w0[u] = w2; w1[u] = w2;
+      prev[u] = 0;
+      if (valid[u]) {
+        w0[u] = *reinterpret_cast<const uint4*>(rp);
+        w1[u] = *reinterpret_cast<const uint4*>(rp + 16);
+        w2 = *reinterpret_cast<const uint4*>(rp + 32);
+        if (li > 0) prev[u] = *reinterpret_cast<const unsigned long long*>(rp - 48 + 32);
+        else if (r[u] > 0) prev[u] = *reinterpret_cast<const unsigned long long*>(a.records + (r[u] - 1) * 48ull + 32);
       }
-      if (!a.halo) {
-        // launch counts: CTA-local cache first (a plain load finds the key's entry once it exists), global atomics when
-        // the cache is crowded
-        uint32_t h = (slot * 2654435761u) >> (32 - 10);
-        bool cached = false;
-        for (int probe = 0; probe < 8; ++probe) {
-          uint32_t cur = cc_slot[h];
-          if (cur == 0u) cur = atomicCAS(&cc_slot[h], 0u, slot + 1);
-          if (cur == 0u || cur == slot + 1) {
-            atomicAdd(&cc_cnt[h], 1u);
-            if (solo) atomicAdd(&cc_solo[h], 1u);
-            cached = true;
-            break;
+      start[u] = (unsigned long long)w2.x | ((unsigned long long)w2.y << 32);
+      end[u] = (unsigned long long)w2.z | ((unsigned long long)w2.w << 32);
+      key[u] = kernel_key(w0[u].x, w0[u].y, w0[u].z, w0[u].w, w1[u].x, w1[u].y, w1[u].z, w1[u].w, a.type_mode != 0);
+      seen[u] = valid[u] ? ld_volatile_u64(reinterpret_cast<const uint64_t*>(a.dict_keys + dict_home(key[u]))) : 0ull;
+    }
+
+    // ---- phase 2: finish the lookups (keys of a warp are mostly distinct, so every lane probes for itself; the
+    // dictionary is 2 MB and lives in L2), count, write
+#pragma unroll
+    for (int u = 0; u < kDecodePerThread; ++u) {
+      const bool solo = (w1[u].w & kMetaSoloBit) != 0;
+      const uint32_t solo_ballot = __ballot_sync(0xFFFFFFFFu, valid[u] && solo && !a.halo);
+      uint32_t slot = 0;
+      if (valid[u]) {
+        bool inserted = false;
+        slot = dict_home(key[u]);
+        if (seen[u] != key[u]) slot = dict_find_or_insert(a.dict_keys, key[u], &inserted);
+        if (slot >= kDictSlots) { err |= kErrTooManyKeys; slot = 0; inserted = false; }
+        if (inserted) {
+          uint4 k0 = w0[u], k1 = w1[u];
+          k1.w &= ~kMetaSoloBit;
+          if (a.type_mode) { k0.y = k0.z = k0.w = 0; k1.w &= 0xFF000000u; }
+          a.dict_words[2 * (size_t)slot] = k0;
+          a.dict_words[2 * (size_t)slot + 1] = k1;
+        }
+        if (!a.halo) {
+          // launch counts: CTA-local cache first (a plain load finds the key's entry once it exists), global atomics
+          // when the cache is crowded
+          uint32_t h = (slot * 2654435761u) >> (32 - 10);
+          bool cached = false;
+          for (int probe = 0; probe < 8; ++probe) {
+            uint32_t cur = cc_slot[h];
+            if (cur == 0u) cur = atomicCAS(&cc_slot[h], 0u, slot + 1);
+            if (cur == 0u || cur == slot + 1) {
+              atomicAdd(&cc_cnt[h], 1u);
+              if (solo) atomicAdd(&cc_solo[h], 1u);
+              cached = true;
+              break;
+            }
+            h = (h + 1) & (kCtaCountSlots - 1);
           }
-          h = (h + 1) & (kCtaCountSlots - 1);
+          if (!cached) {
+            atomicAdd(&a.dict_launches[slot], 1u);
+            if (solo) atomicAdd(&a.dict_solo[slot], 1u);
+          }
         }
-        if (!cached) {
-          atomicAdd(&a.dict_launches[slot], 1u);
-          if (solo) atomicAdd(&a.dict_solo[slot], 1u);
-        }
+        if (end[u] < start[u] || end[u] - start[u] >= 0x80000000ull) err |= kErrRecord;
+        if (start[u] < prev[u] && !(a.halo && r[u] == 0)) err |= kErrUnordered;
+        const uint32_t dur = (uint32_t)(end[u] - start[u]);
+        const uint32_t meta = slot | (w1[u].w & (kMetaSoloBit | 0xFF000000u));
+        a.tl_start[r[u]] = start[u];
+        a.tl_dm[r[u]] = (unsigned long long)dur | ((unsigned long long)meta << 32);
+        if (a.keys_out) a.keys_out[r[u]] = key[u];
+        max_dur = max(max_dur, dur);
+        min_start = min(min_start, start[u]);
+        max_start = max(max_start, start[u]);
       }
-    }
-
-    if (valid) {
-      if (end < start || end - start >= 0x80000000ull) err |= kErrRecord;
-      if (start < prev && !(a.halo && r == 0)) err |= kErrUnordered;
-      const uint32_t dur = (uint32_t)(end - start);
-      const uint32_t meta = slot | (w1.w & (kMetaSoloBit | 0xFF000000u));
-      a.tl_start[r] = start;
-      a.tl_dm[r] = (unsigned long long)dur | ((unsigned long long)meta << 32);
-      if (a.keys_out) a.keys_out[r] = key;
-      max_dur = max(max_dur, dur);
-      min_start = min(min_start, start);
-      max_start = max(max_start, start);
-    }
-    // solo stream: one counter update per warp
-    if (solo_ballot) {
-      uint32_t base = 0;
-      const uint32_t first = __ffs(solo_ballot) - 1;
-      if (lane == first) base = atomicAdd(&a.ctl->n_solo, (uint32_t)__popc(solo_ballot));
-      base = __shfl_sync(0xFFFFFFFFu, base, first);
-      if (valid && solo) {
-        const uint32_t dur = (uint32_t)(end - start);
-        a.solo_stream[base + __popc(solo_ballot & lanemask_lt())] = (unsigned long long)slot | ((unsigned long long)dur << 32);
+      // solo stream: one counter update per warp
+      if (solo_ballot) {
+        uint32_t base = 0;
+        const uint32_t first = __ffs(solo_ballot) - 1;
+        if (lane == first) base = atomicAdd(&a.ctl->n_solo, (uint32_t)__popc(solo_ballot));
+        base = __shfl_sync(0xFFFFFFFFu, base, first);
+        if (valid[u] && solo) {
+          const uint32_t dur = (uint32_t)(end[u] - start[u]);
+          a.solo_stream[base + __popc(solo_ballot & lanemask_lt())] = (unsigned long long)slot | ((unsigned long long)dur << 32);
+        }
       }
     }
 
