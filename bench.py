@@ -267,8 +267,8 @@ def main():
         # algorithmic bytes per launch: decode reads 48 B and writes 16 B per record; the join reads the 16-byte timeline
         # entry of every record and writes one 16-byte sample per overlapping pair.
         # traffic: dram__bytes_read + dram__bytes_write of one ncu capture at 4 M records, scaled by the record count
-        # (both kernels stream the trace once, so traffic grows in proportion): 59.6 B/record and 16.9 B/record.
-        cand = {"ms_decode": ("k_decode_hash", 64.0 * N, 59.6 * N), "ms_join": ("k_join", 16.0 * N + 16.0 * P, 16.9 * N)}
+        # (both kernels stream the trace once, so traffic grows in proportion): 59.3 B/record and 17.7 B/record.
+        cand = {"ms_decode": ("k_decode_hash", 64.0 * N, 59.3 * N), "ms_join": ("k_join", 16.0 * N + 16.0 * P, 17.7 * N)}
         dom = max(cand, key=lambda k: per_stage[k])
         dom_name, dom_bytes, dom_traffic = cand[dom]
         achieved = dom_bytes / (per_stage[dom] * 1e-3) / 1e9
