@@ -192,6 +192,20 @@ int64_t ks_mg_row_count(ks_handle* h);                                          
 int64_t ks_mg_solo(ks_handle* h, double* solo, int import);                                     /* solo times by dense id, out (0) or in (1) */
 int64_t ks_mg_finalize(ks_handle* h);                                                           /* tables of this rank's key range; then ks_copy_*_rows */
 
+/* ---- the agent's timing log (text) -> launch records, on the device.  Replaces the pandas read of the 17-column TSV the
+ * agent writes (scheduler/agent.cpp:692-705; read at scheduler/postprocess.py:12-13).  Rows without end_ns (no completion
+ * callback, agent.cpp:702) are dropped.  Three steps because names are canonicalised on the host (ks_function_base), once
+ * per DISTINCT symbol:
+ *   ks_tsv_parse       text in; returns the number of valid launch rows
+ *   ks_tsv_dictionary  the distinct kernel symbols (which = 0) or models (1): hashes[slot] != 0 marks a used slot,
+ *                      where[slot] = offset << 20 | length of the string's first occurrence in the text (HOST arrays)
+ *   ks_tsv_finish      name id and tenant per dictionary slot in (HOST arrays over all slots), records out, file order */
+#define KS_TSV_NAME_SLOTS 65536
+#define KS_TSV_MODEL_SLOTS 256
+int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t flags);
+int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* where);
+int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags);
+
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
  * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */
 int64_t ks_function_base(const char* symbol, char* out, uint64_t capacity);

@@ -79,6 +79,9 @@ KS_API = [
     ("ks_mg_row_count", [c_void_p], c_int64),
     ("ks_mg_solo", [c_void_p, c_void_p, c_int], c_int64),
     ("ks_mg_finalize", [c_void_p], c_int64),
+    ("ks_tsv_parse", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
+    ("ks_tsv_dictionary", [c_void_p, c_int, c_void_p, c_void_p], c_int64),
+    ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),
 ]
 

@@ -13,6 +13,7 @@
 #include "ks_misc.cuh"
 #include "ks_reduce.cuh"
 #include "ks_sort.cuh"
+#include "ks_tsv.cuh"
 
 using namespace ks;
 
@@ -52,6 +53,9 @@ struct ks_handle {
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
   DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows;
   DevBuf tmp[6];
+  DevBuf tsv_text, tsv_lines, tsv_parsed, tsv_valid, tsv_cnt, tsv_vcnt, tsv_dict, tsv_maps;
+  uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0;
+  const unsigned char* tsv_dev_text = nullptr;
 
   // results of the last ks_build_table
   uint64_t n_pair_rows = 0, n_key_rows = 0;
@@ -548,7 +552,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
@@ -1277,6 +1281,124 @@ int64_t ks_mg_finalize(ks_handle* h) {
   h->n_key_rows = h->h_ctl->n_keys;
   h->n_pair_rows = h->h_ctl->n_rows - h->h_ctl->ticket2;
   return (int64_t)h->n_pair_rows;
+}
+
+}  // extern "C"
+
+// =========================================================================================================
+// Agent timing log (TSV text) -> launch records on the device.  Three calls: parse (text in, counts out), dictionaries
+// out (the distinct kernel symbols and models, for the host to canonicalise and number), finish (ids in, records out).
+namespace {
+TsvArgs tsv_args(ks_handle* h) {
+  TsvArgs a{};
+  a.text = h->tsv_dev_text;
+  a.n_bytes = h->tsv_n_bytes;
+  a.tile_cnt = as<uint32_t>(h->tsv_cnt);
+  a.line_start = as<unsigned long long>(h->tsv_lines);
+  a.max_lines = h->tsv_n_lines;
+  a.parsed = as<ks_record>(h->tsv_parsed);
+  a.valid = as<unsigned char>(h->tsv_valid);
+  a.vtile_cnt = as<uint32_t>(h->tsv_vcnt);
+  unsigned long long* d = as<unsigned long long>(h->tsv_dict);
+  a.name_hash = d;
+  a.name_where = d + kTsvNameSlots;
+  a.model_hash = d + 2 * (size_t)kTsvNameSlots;
+  a.model_where = a.model_hash + kTsvModelSlots;
+  a.ctl = h->d_ctl;
+  return a;
+}
+}  // namespace
+
+extern "C" {
+
+int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t flags) {
+  if (!h || (!text && n_bytes) || (flags & ~KS_ON_DEVICE)) return -KS_ERR_ARG;
+  if (n_bytes >= (1ull << 40)) return fail(h, KS_ERR_TOO_LARGE, "ks_tsv_parse: text of 2^40 bytes or more");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = reset_run(h); if (r) return r; }
+  const unsigned char* d_text = nullptr;
+  { int r = stage_in<unsigned char>(h, h->tsv_text, reinterpret_cast<const unsigned char*>(text), n_bytes, (flags & KS_ON_DEVICE) != 0, &d_text); if (r) return r; }
+  h->tsv_dev_text = d_text;
+  h->tsv_n_bytes = n_bytes;
+  h->tsv_n_lines = h->tsv_n_valid = 0;
+  const uint64_t ntiles = (n_bytes + kTsvTile - 1) / kTsvTile;
+  KS_ENSURE(h, h->tsv_cnt, (ntiles + 1) * 4);
+  KS_ENSURE(h, h->tsv_dict, (2 * (size_t)kTsvNameSlots + 2 * kTsvModelSlots) * 8);
+  {  // hashes start empty (0), first-occurrence words start at the maximum (they are lowered with atomicMin)
+    unsigned long long* d = as<unsigned long long>(h->tsv_dict);
+    KS_CUDA(h, cudaMemsetAsync(d, 0, (size_t)kTsvNameSlots * 8, h->stream));
+    KS_CUDA(h, cudaMemsetAsync(d + kTsvNameSlots, 0xFF, (size_t)kTsvNameSlots * 8, h->stream));
+    KS_CUDA(h, cudaMemsetAsync(d + 2 * (size_t)kTsvNameSlots, 0, (size_t)kTsvModelSlots * 8, h->stream));
+    KS_CUDA(h, cudaMemsetAsync(d + 2 * (size_t)kTsvNameSlots + kTsvModelSlots, 0xFF, (size_t)kTsvModelSlots * 8, h->stream));
+  }
+  if (n_bytes == 0) return 0;
+  TsvArgs a = tsv_args(h);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 8);
+  k_tsv_nl_count<<<grid, 256, 0, h->stream>>>(a);
+  k_tsv_scan<<<1, 1024, 0, h->stream>>>(a.tile_cnt, ntiles, &h->d_ctl->scratch0, d_text, n_bytes);
+  { int r = read_ctl(h); if (r) return r; }
+  const uint64_t n_lines = h->h_ctl->scratch0;
+  h->tsv_n_lines = n_lines;
+  KS_ENSURE(h, h->tsv_lines, (n_lines + 2) * 8);
+  KS_ENSURE(h, h->tsv_parsed, std::max<uint64_t>(n_lines, 1) * sizeof(ks_record));
+  KS_ENSURE(h, h->tsv_valid, std::max<uint64_t>(n_lines, 1));
+  const uint64_t vtiles = (n_lines + 255) / 256;
+  KS_ENSURE(h, h->tsv_vcnt, (vtiles + 1) * 4);
+  a = tsv_args(h);
+  k_tsv_nl_fill<<<grid, 256, 0, h->stream>>>(a);
+  const int lgrid = (int)std::max<uint64_t>(1, std::min<uint64_t>((n_lines + 255) / 256, (uint64_t)h->sm_count * 16));
+  k_tsv_parse<<<lgrid, 256, 0, h->stream>>>(a);
+  k_tsv_valid_count<<<lgrid, 256, 0, h->stream>>>(a);
+  k_tsv_scan<<<1, 1024, 0, h->stream>>>(a.vtile_cnt, vtiles, &h->d_ctl->n_pairs, nullptr, 0);
+  h->launches += 6;
+  KS_CUDA(h, cudaGetLastError());
+  { int r = read_ctl(h); if (r) return r; }
+  if (h->h_ctl->err & kErrTooManyKeys) return fail(h, KS_ERR_TOO_MANY_KEYS, "ks_tsv_parse: more than 65,536 distinct kernel symbols or 256 models in one file");
+  h->tsv_n_valid = h->h_ctl->n_pairs;
+  return (int64_t)h->tsv_n_valid;
+}
+
+// which = 0: kernel symbols (KS_TSV_NAME_SLOTS entries), 1: models (KS_TSV_MODEL_SLOTS).  hashes[i] != 0 marks a used slot;
+// where[i] = offset << 20 | length of the string's first occurrence in the text.  HOST pointers.
+int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* where) {
+  if (!h || !hashes || !where || which < 0 || which > 1) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (!h->tsv_dict.p) return fail(h, KS_ERR_ARG, "ks_tsv_dictionary: no parsed text");
+  const uint32_t slots = which ? kTsvModelSlots : kTsvNameSlots;
+  const unsigned long long* base = as<unsigned long long>(h->tsv_dict) + (which ? 2 * (size_t)kTsvNameSlots : 0);
+  KS_CUDA(h, cudaMemcpyAsync(hashes, base, (size_t)slots * 8, cudaMemcpyDeviceToHost, h->stream));
+  KS_CUDA(h, cudaMemcpyAsync(where, base + slots, (size_t)slots * 8, cudaMemcpyDeviceToHost, h->stream));
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)slots;
+}
+
+// name_ids[slot], tenants[slot]: HOST arrays over the dictionary slots; out: records (host, or device with KS_ON_DEVICE)
+int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags) {
+  if (!h || !name_ids || !tenants || (!out && h->tsv_n_valid) || (flags & ~KS_ON_DEVICE)) return -KS_ERR_ARG;
+  if (capacity < h->tsv_n_valid) return fail(h, KS_ERR_CAPACITY, "ks_tsv_finish: output buffer too small");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const uint64_t n = h->tsv_n_valid;
+  if (n == 0) return 0;
+  KS_ENSURE(h, h->tsv_maps, ((size_t)kTsvNameSlots + kTsvModelSlots) * 4);
+  uint32_t* maps = as<uint32_t>(h->tsv_maps);
+  KS_CUDA(h, cudaMemcpyAsync(maps, name_ids, (size_t)kTsvNameSlots * 4, cudaMemcpyHostToDevice, h->stream));
+  KS_CUDA(h, cudaMemcpyAsync(maps + kTsvNameSlots, tenants, (size_t)kTsvModelSlots * 4, cudaMemcpyHostToDevice, h->stream));
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  ks_record* d_out = out;
+  if (!dev) { KS_ENSURE(h, h->records, n * sizeof(ks_record)); d_out = as<ks_record>(h->records); }
+  TsvArgs a = tsv_args(h);
+  a.out = d_out;
+  a.out_capacity = n;
+  a.name_map = maps;
+  a.model_map = maps + kTsvNameSlots;
+  a.solo = solo;
+  const int lgrid = (int)std::max<uint64_t>(1, std::min<uint64_t>((h->tsv_n_lines + 255) / 256, (uint64_t)h->sm_count * 16));
+  k_tsv_compact<<<lgrid, 256, 0, h->stream>>>(a);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  if (!dev) { int r = copy_out(h, out, d_out, n * sizeof(ks_record), false); if (r) return r; }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)n;
 }
 
 }  // extern "C"

@@ -5,7 +5,8 @@
 
 Input: the 17-column logs the agent writes (scheduler/agent.cpp:692-705), one file per process; ``--solo`` files
 come from a one-kernel-at-a-time run (profiling/pairprof_daemon.cpp:46).  Rows without ``end_ns`` (no completion
-callback, agent.cpp:702) are dropped.  Kernel symbols are reduced to their short names (kernel_key.hpp) and
+callback, agent.cpp:702) are dropped.  The logs are parsed on the GPU (``records_from_log``); ``TraceIngest.records``
+is the same ingest from a pandas frame.  Kernel symbols are reduced to their short names (kernel_key.hpp) and
 numbered; the ``model`` column is the tenant.
 
 Output, in the layout ``load_pair_eff`` / ``load_kernel_us`` parse (scheduler_daemon.cpp:193-202, :230-264):
@@ -23,7 +24,7 @@ import pandas as pd
 
 from . import _lib
 from .pair_table import PairTableBuilder
-from .records import pack_records
+from .records import RECORD_DTYPE, pack_records
 
 _DIMS = re.compile(r"\d+")
 
@@ -46,29 +47,57 @@ class TraceIngest:
         self._base_cache: dict[str, str] = {}
         self.models: list[str] = []
 
+    def name_id(self, symbol: str) -> int:
+        """Id of the symbol's canonical short name (new names are numbered in order of appearance)."""
+        base = self._base_cache.get(symbol)
+        if base is None:
+            base = self._base_cache[symbol] = _lib.function_base(str(symbol))
+        if base not in self._name_id:
+            self._name_id[base] = len(self.names)
+            self.names.append(base)
+        return self._name_id[base]
+
+    def tenant_id(self, model: str) -> int:
+        if model not in self.models:
+            self.models.append(model)
+        return self.models.index(model)
+
     def _name_ids(self, symbols: pd.Series) -> np.ndarray:
-        ids = {}
-        for sym in symbols.unique():
-            base = self._base_cache.get(sym)
-            if base is None:
-                base = self._base_cache[sym] = _lib.function_base(str(sym))
-            if base not in self._name_id:
-                self._name_id[base] = len(self.names)
-                self.names.append(base)
-            ids[sym] = self._name_id[base]
+        ids = {sym: self.name_id(sym) for sym in symbols.unique()}
         return symbols.map(ids).to_numpy(dtype=np.uint32)
 
     def records(self, frame: pd.DataFrame, solo: bool) -> np.ndarray:
         f = frame[frame["end_ns"].notna()]
-        tenants = []
-        for m in f["model"].astype(str):
-            if m not in self.models:
-                self.models.append(m)
-            tenants.append(self.models.index(m))
+        tenants = [self.tenant_id(m) for m in f["model"].astype(str)]
         n = len(f)
         return pack_records(
             self._name_ids(f["kernel_name"]), _dims(f["grid"]), _dims(f["block"]), np.zeros(n, np.uint32), np.array(tenants, dtype=np.uint32),
             np.full(n, solo), f["start_ns"].to_numpy(dtype=np.uint64), f["end_ns"].to_numpy(dtype=np.uint64))
+
+
+def records_from_log(ing: "TraceIngest", builder: PairTableBuilder, path_or_bytes, solo: bool) -> np.ndarray:
+    """One agent timing log -> launch records, parsed on the GPU (``ks_tsv_parse``): line splitting, tab walking, number
+    and dimension parsing and the string dictionaries run on the device; the host only canonicalises each DISTINCT kernel
+    symbol (``ks_function_base``) and numbers names and models in their order of first appearance -- the same ids the
+    pandas route (``TraceIngest.records``) assigns."""
+    text = np.fromfile(path_or_bytes, dtype=np.uint8) if isinstance(path_or_bytes, (str, os.PathLike)) else np.frombuffer(path_or_bytes, dtype=np.uint8)
+    lib, h = builder._lib, builder._h
+    n = builder._check(lib.ks_tsv_parse(h, _lib.ptr(text), len(text), 0), "ks_tsv_parse")
+    maps = []
+    for which, slots in ((0, 65536), (1, 256)):
+        hashes, where = np.zeros(slots, dtype=np.uint64), np.zeros(slots, dtype=np.uint64)
+        builder._check(lib.ks_tsv_dictionary(h, which, _lib.ptr(hashes), _lib.ptr(where)), "ks_tsv_dictionary")
+        used = np.flatnonzero(hashes)
+        used = used[np.argsort(where[used] >> np.uint64(20), kind="stable")]  # order of first appearance in the file
+        ids = np.zeros(slots, dtype=np.uint32)
+        for slot in used:
+            off, ln = int(where[slot] >> np.uint64(20)), int(where[slot] & np.uint64((1 << 20) - 1))
+            string = text[off: off + ln].tobytes().decode()
+            ids[slot] = ing.name_id(string) if which == 0 else ing.tenant_id(string)
+        maps.append(ids)
+    rec = np.zeros(n, dtype=RECORD_DTYPE)
+    builder._check(lib.ks_tsv_finish(h, _lib.ptr(maps[0]), _lib.ptr(maps[1]), int(bool(solo)), _lib.ptr(rec), n, 0), "ks_tsv_finish")
+    return rec
 
 
 def _xyz(v) -> str:
@@ -116,10 +145,11 @@ def main(argv=None) -> int:
     ap.add_argument("--out-dir", default=".")
     args = ap.parse_args(argv)
     ing = TraceIngest()
-    parts = [ing.records(pd.read_csv(p, sep="\t"), solo=False) for p in args.corun]
-    parts += [ing.records(pd.read_csv(p, sep="\t"), solo=True) for p in args.solo]
-    rec = np.concatenate(parts)
-    us, eff = write_tables(args.out_dir, build_tables(rec), ing.names, ing.models)
+    with PairTableBuilder() as b:
+        parts = [records_from_log(ing, b, p, solo=False) for p in args.corun]
+        parts += [records_from_log(ing, b, p, solo=True) for p in args.solo]
+        rec = np.concatenate(parts)
+        us, eff = write_tables(args.out_dir, build_tables(rec, b), ing.names, ing.models)
     print(f"{len(rec)} launches, {len(ing.names)} kernel names, {len(ing.models)} models -> {us}, {eff}")
     return 0
 

@@ -69,3 +69,27 @@ def test_make_pair_eff_end_to_end(tmp_path):
     exact = [c for c in got_eff.columns if "mean" not in c]
     assert got_eff[exact].equals(want_eff[exact])
     assert np.allclose(got_eff[["slowdown_mean_a", "slowdown_mean_b"]].to_numpy(), want_eff[["slowdown_mean_a", "slowdown_mean_b"]].to_numpy(), rtol=1e-6, atol=0)
+
+
+def test_device_tsv_parse_equals_pandas_ingest(builder, tmp_path):
+    rec, frames = synthetic_timing_frames(6000)
+    f = frames[("qwen", False)].copy()
+    f.loc[[5, 77], "end_ns"] = np.nan  # launches whose completion callback was never seen: dropped by both routes
+    f["block"] = [b.replace("(", "").replace(")", "").replace(" ", "") if i % 2 else b for i, b in enumerate(f["block"])]  # "x,y,z" spelling
+    texts = {}
+    for key, frame in ((("qwen", False), f), (("whisper", False), frames[("whisper", False)]), (("qwen", True), frames[("qwen", True)])):
+        p = str(tmp_path / f"{key[0]}_{int(key[1])}.tsv")
+        frame.to_csv(p, sep="\t", index=False)
+        texts[key] = (p, frame)
+    ing_a, ing_b = M.TraceIngest(), M.TraceIngest()
+    for key, (p, frame) in texts.items():
+        want = ing_a.records(pd.read_csv(p, sep="\t"), key[1])
+        got = M.records_from_log(ing_b, builder, p, key[1])
+        assert len(got) == len(want) and got.tobytes() == want.tobytes(), key
+    assert ing_a.names == ing_b.names and ing_a.models == ing_b.models
+    # no trailing newline, CRLF line ends, an empty file body
+    raw = open(texts[("whisper", False)][0], "rb").read()
+    want = ing_a.records(texts[("whisper", False)][1], False)
+    assert M.records_from_log(ing_b, builder, raw.rstrip(b"\n"), False).tobytes() == want.tobytes()
+    assert M.records_from_log(ing_b, builder, raw.replace(b"\n", b"\r\n"), False).tobytes() == want.tobytes()
+    assert len(M.records_from_log(ing_b, builder, raw.split(b"\n")[0] + b"\n", False)) == 0
