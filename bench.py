@@ -166,6 +166,7 @@ def main():
         shift = sum(int(x[0]) for x in spans[:rank])
         rec["start_ns"] += np.uint64(shift)
         rec["end_ns"] += np.uint64(shift)
+    first_start = int(rec["start_ns"][0])
     host = torch.from_numpy(rec.view(np.uint8).reshape(-1)).pin_memory()
     dev = host.cuda(non_blocking=False)
     stream = torch.cuda.Stream()
@@ -183,7 +184,7 @@ def main():
         if world == 1:
             return builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
         with torch.cuda.stream(stream):
-            keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev), rank, world, on_device=True))
+            keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev, first_start), rank, world, on_device=True))
         builder.info = {"n_pairs": 0, "n_rows": table_t.numel() // 128, "n_keys": keys_t.numel() // 72}
         return table_t.numel() // 128
 
@@ -222,13 +223,22 @@ def main():
     e2e = None
     if not args.no_e2e:
         rec_pinned = host.numpy().view(RECORD_DTYPE)
+        out_pinned = None
 
         def step_e2e():
             if world == 1:
                 return builder.build(rec_pinned, time_ordered=True, pinned=True)
             with torch.cuda.stream(stream):
-                d = host.to("cuda", non_blocking=True)
-                return parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, d), rank, world))
+                dev.copy_(host, non_blocking=True)  # this step's records from pinned host memory
+                keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev, first_start), rank, world, on_device=True))
+                nonlocal out_pinned
+                need = keys_t.numel() + table_t.numel()
+                if out_pinned is None or out_pinned.numel() < need:
+                    out_pinned = torch.empty(need + need // 4, dtype=torch.uint8).pin_memory()
+                out_pinned[: keys_t.numel()].copy_(keys_t, non_blocking=True)  # the whole table back to pinned host memory
+                out_pinned[keys_t.numel(): need].copy_(table_t, non_blocking=True)
+                stream.synchronize()
+                return out_pinned[: keys_t.numel()].numpy(), out_pinned[keys_t.numel(): need].numpy()
 
         for _ in range(2):
             keys, pairs = step_e2e()

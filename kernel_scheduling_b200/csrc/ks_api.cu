@@ -732,7 +732,7 @@ int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows
   if (capacity_rows < h->n_pair_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_pair_rows: buffer too small");
   KS_CUDA(h, cudaSetDevice(h->device));
   { int r = copy_out(h, dst, h->pair_rows.p, h->n_pair_rows * sizeof(ks_pair_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
-  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  if (!(flags & KS_ON_DEVICE)) KS_CUDA(h, cudaStreamSynchronize(h->stream));  // device destinations are ordered by the stream
   return (int64_t)h->n_pair_rows;
 }
 
@@ -741,7 +741,7 @@ int64_t ks_copy_key_rows(ks_handle* h, ks_key_row* dst, uint64_t capacity_rows, 
   if (capacity_rows < h->n_key_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_key_rows: buffer too small");
   KS_CUDA(h, cudaSetDevice(h->device));
   { int r = copy_out(h, dst, h->key_rows, h->n_key_rows * sizeof(ks_key_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
-  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  if (!(flags & KS_ON_DEVICE)) KS_CUDA(h, cudaStreamSynchronize(h->stream));
   return (int64_t)h->n_key_rows;
 }
 
@@ -1049,7 +1049,6 @@ int64_t ks_mg_tail(ks_handle* h, void* out_records, uint64_t capacity) {
   if (n_tail) {
     k_gather_records<<<(n_tail * 3 + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const uint4*>(h->mg_rec), idx, n_tail, reinterpret_cast<uint4*>(out_records));
     ++h->launches;
-    KS_CUDA(h, cudaStreamSynchronize(h->stream));
   }
   return (int64_t)n_tail;
 }
@@ -1081,7 +1080,6 @@ int64_t ks_mg_local_keys(ks_handle* h, uint64_t* keys_out, void* words_out, uint
     k_export_keys<<<(nk + 255) / 256, 256, 0, h->stream>>>(h->dkeys, h->dslot, h->dict_words, nk, reinterpret_cast<unsigned long long*>(keys_out),
                                                            reinterpret_cast<uint4*>(words_out));
     ++h->launches;
-    KS_CUDA(h, cudaStreamSynchronize(h->stream));
   }
   return (int64_t)nk;
 }
@@ -1276,9 +1274,8 @@ int64_t ks_mg_finalize(ks_handle* h) {
   k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
   h->launches += nk ? 2 : 1;
   KS_CUDA(h, cudaGetLastError());
-  { int r = read_ctl(h); if (r) return r; }
-  { int r = mg_status(h, "ks_mg_finalize"); if (r) return r; }
-  h->n_key_rows = h->h_ctl->n_keys;
+  // no host round trip: the counts are known since ks_mg_reduce read them back
+  h->n_key_rows = nk;
   h->n_pair_rows = h->h_ctl->n_rows - h->h_ctl->ticket2;
   return (int64_t)h->n_pair_rows;
 }

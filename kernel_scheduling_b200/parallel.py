@@ -210,7 +210,7 @@ def run_in_process(gens):
 class GpuStages:
     """One rank's compute through the C ABI (ks_mg_*).  ``records`` is a uint8 CUDA tensor of 48-byte records."""
 
-    def __init__(self, builder, records: torch.Tensor):
+    def __init__(self, builder, records: torch.Tensor, first_start: int | None = None):
         if records.is_cuda and builder.stream != torch.cuda.current_stream(records.device).cuda_stream:
             # the collectives run on torch's current stream; the library must launch on the same one, or a collective
             # could still be writing a buffer the next phase reads
@@ -223,6 +223,7 @@ class GpuStages:
         self.n_owned = records.numel() // 48
         self.n_keys = 0
         self._keep = []
+        self._first_start = first_start  # start_ns of the first record when the caller knows it (saves a device read)
 
     # tensors
     def zeros(self, shape, dtype):
@@ -238,6 +239,8 @@ class GpuStages:
         """start_ns of the window's first record, or None for an empty window."""
         if self.n_owned == 0:
             return None
+        if self._first_start is not None:
+            return self._first_start
         return int(np.frombuffer(self.records[:48].cpu().numpy().tobytes(), dtype=RECORD_DTYPE)["start_ns"][0])
 
     def _ck(self, r, what):
