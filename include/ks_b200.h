@@ -83,7 +83,7 @@ typedef struct ks_key_row {
 typedef struct ks_config {
   uint64_t max_records;   /* scratch is sized for this many records up front (it grows on demand) */
   uint64_t max_pairs;     /* ... and this many overlapping launch pairs */
-  uint32_t max_pair_rows; /* capacity of the pair dictionary in rows (rounded up to a power of two, x2 slots) */
+  uint32_t max_pair_rows; /* limit on the rows of the pair table (KS_ERR_TOO_LARGE beyond); 0 = no limit, the arrays grow */
   uint32_t reserved;
 } ks_config;
 

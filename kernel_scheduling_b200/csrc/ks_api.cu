@@ -33,6 +33,7 @@ struct ks_handle {
   bool own_stream = false;
   std::string last_error;
   ks_config cfg{};
+  bool rows_auto = true;  // max_pair_rows was not given: the row arrays grow to what a trace needs
 
   Control* d_ctl = nullptr;
   Control* h_ctl = nullptr;  // pinned
@@ -501,6 +502,7 @@ ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
   h->device = device;
   cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device);
   if (cfg) h->cfg = *cfg;
+  h->rows_auto = h->cfg.max_pair_rows == 0;
   if (h->cfg.max_pair_rows == 0) h->cfg.max_pair_rows = 1u << 22;
   bool ok = true;
   if (stream) {
@@ -690,6 +692,12 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
       h->hint_valid = false;
       return ks_build_table(h, records, n, flags, info);
     }
+  }
+  if ((h->h_ctl->err & kErrTooLarge) && h->rows_auto && h->h_ctl->pad2[0] > h->cfg.max_pair_rows && h->h_ctl->pad2[0] < (1ull << 31)) {
+    // more table rows than the arrays were sized for, and no limit was asked for: size them for this trace and run again
+    h->cfg.max_pair_rows = (uint32_t)std::min<uint64_t>(h->h_ctl->pad2[0] + h->h_ctl->pad2[0] / 8, 0x7FFFFFFFull);
+    h->hint_valid = false;
+    return ks_build_table(h, records, n, flags, info);
   }
   const int st = status_of_err(h->h_ctl->err, assume_ordered);
   if (st) { h->hint_valid = false; return fail(h, st, std::string("ks_build_table: ") + ks_status_string(st)); }

@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(1024) k_rows_scan(const RowsArgs a) {
       // more rows than the arrays hold: report it and leave NO rows, so that no later kernel walks stale row offsets
       atomicOr(&a.ctl->err, kErrTooLarge);
       a.ctl->n_rows = 0;
+      a.ctl->pad2[0] = rows;  // how many rows there are, so that the host can size the arrays and run again
       a.row_start[0] = 0;
     } else {
       a.ctl->n_rows = rows;

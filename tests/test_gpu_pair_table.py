@@ -149,3 +149,36 @@ def test_pinned_buffers(builder):
     keys, pairs = builder.build(buf, time_ordered=True, pinned=True)
     okeys, opairs = O.build_pair_table(rec)
     assert_tables_match(keys, pairs, okeys, opairs)
+
+
+def test_full_size_c2_properties(builder):
+    """The benchmark configuration at its full size (10 M records): properties that need no oracle."""
+    rec = trace.generate(trace.config("c2"))
+    keys, pairs = builder.build(rec, time_ordered=True)
+    info = dict(builder.info)
+    assert info["n_records"] == len(rec) == 10_000_000
+    assert int(keys["launches"].sum()) == len(rec)                       # every launch is counted under exactly one key
+    assert int(keys["solo_launches"].sum()) == info["n_solo"]
+    assert int(pairs["count"].sum()) == info["n_pairs"]                   # every overlapping pair lands in exactly one row
+    assert (np.diff(keys["key"].astype(np.uint64).view(np.int64)) != 0).all() and (keys["key"][1:] > keys["key"][:-1]).all()
+    order = np.lexsort((pairs["key_b"], pairs["key_a"]))
+    assert (order == np.arange(len(pairs))).all()                         # rows sorted by (key_a, key_b), no duplicates
+    assert len(np.unique(np.stack([pairs["key_a"], pairs["key_b"]], axis=1), axis=0)) == len(pairs)
+    tenant_of = dict(zip(keys["key"].tolist(), keys["tenant"].tolist()))
+    assert all(tenant_of[a] < tenant_of[b] for a, b in zip(pairs["key_a"][:2000].tolist(), pairs["key_b"][:2000].tolist()))
+    for side in "ab":
+        ok = (pairs["flags"] >> (0 if side == "a" else 1)) & 1 == 1
+        mn, md, mx, mean = (pairs[f"{c}_{side}"][ok] for c in ("min", "median", "max", "mean"))
+        assert (mn <= md).all() and (md <= mx).all() and (mn <= mean * (1 + 1e-12)).all() and (mean <= mx * (1 + 1e-12)).all()
+        assert np.isnan(pairs[f"median_{side}"][~ok]).all()
+        single = ok & (pairs["count"] == 1)
+        assert np.array_equal(pairs[f"min_{side}"][single], pairs[f"max_{side}"][single])
+        assert np.array_equal(pairs[f"median_{side}"][single], pairs[f"min_{side}"][single])
+    # the same launches in another order give the same table bit for bit (exact columns) -- the sort in front is exercised
+    keys2, pairs2 = builder.build(trace.shuffled(rec), time_ordered=False)
+    assert keys2.tobytes() == keys.tobytes()
+    for c in pairs.dtype.names:
+        if c.startswith(("sum", "mean")):
+            assert np.allclose(pairs2[c], pairs[c], rtol=1e-6, atol=0, equal_nan=True), c
+        else:
+            assert np.array_equal(pairs2[c], pairs[c], equal_nan=True), c
