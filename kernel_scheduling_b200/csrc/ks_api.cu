@@ -69,6 +69,7 @@ struct ks_handle {
   int mg_cur = 0;
 
   // what the last ks_build_table saw: lets the next call queue every stage without reading counts back in between
+  bool attr_sort16 = false, attr_decode = false;  // kernel attributes set on this handle's device
   bool hint_valid = false;
   uint64_t hint_samples = 0, hint_nk = 0, hint_rows = 0;
   cudaEvent_t ev[12]{};
@@ -115,6 +116,8 @@ int ensure(ks_handle* h, DevBuf& b, size_t bytes) {
 template <typename T>
 T* as(const DevBuf& b) { return reinterpret_cast<T*>(b.p); }
 
+constexpr int kSort16Threads = 512;  // threads per CTA of the sample sort: tiles of 4096 items, runs of 16 items per digit
+
 int bit_length(uint64_t v) {
   int b = 0;
   while (v) { ++b; v >>= 1; }
@@ -159,11 +162,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
   h->launches += 2 + passes;
   auto kern = k_onesweep_pass<KeyT, ValT, NV, ITEMS>;
   constexpr size_t smem = sort_smem_bytes<KeyT, ValT, ITEMS>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    KS_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
+  KS_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  // per device: set every time
   int cur = 0;
   const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
   for (int p = 0; p < passes; ++p) {
@@ -191,7 +190,8 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 // holds the result.
 int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr) {
   constexpr int ITEMS = 8;
-  constexpr int TILE = kSortThreads * ITEMS;
+  constexpr int THREADS = kSort16Threads;
+  constexpr int TILE = THREADS * ITEMS;
   if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
   const int passes = (end_bit + 7) / 8;
   if (passes <= 0 || n == 0) return 0;
@@ -206,14 +206,13 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
   k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(as<uint32_t>(h->samples[0]), 4u, n_dev, (uint32_t)n, 0, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
-  constexpr size_t smem = sort16_smem_bytes<ITEMS>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
+  constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
+  if (!h->attr_sort16) {  // the attribute is per device, so it is remembered per handle
+    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    h->attr_sort16 = true;
   }
   int cur = 0;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 4);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * (1024 / THREADS));
   for (int p = 0; p < passes; ++p) {
     KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
     SortPass16Args a{};
@@ -227,7 +226,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
     a.lookback = as<uint32_t>(h->lookback);
     a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
     a.err = &h->d_ctl->err;
-    k_onesweep_pass16<ITEMS><<<grid, kSortThreads, smem, h->stream>>>(a);
+    k_onesweep_pass16<ITEMS, THREADS><<<grid, THREADS, smem, h->stream>>>(a);
     cur ^= 1;
   }
   KS_CUDA(h, cudaGetLastError());
@@ -284,10 +283,9 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
   a.solo_stream = as<unsigned long long>(h->solo_stream);
   a.keys_out = keys_out;
   a.ctl = h->d_ctl;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!h->attr_decode) {
     KS_CUDA(h, cudaFuncSetAttribute(k_decode_hash, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes()));
-    attr_set = true;
+    h->attr_decode = true;
   }
   const uint64_t ntiles = (n + kDecodeTile - 1) / kDecodeTile;
   const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 3);
@@ -351,12 +349,6 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
   j.idx_b = idx_b;
   j.capacity = capacity;
   j.ctl = h->d_ctl;
-  static bool attr_set = false;
-  if (!attr_set) {
-    KS_CUDA(h, cudaFuncSetAttribute(k_join<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem_bytes()));
-    KS_CUDA(h, cudaFuncSetAttribute(k_join<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem_bytes()));
-    attr_set = true;
-  }
   const unsigned grid = (unsigned)((n + kJoinTile - 1) / kJoinTile);
   if (idx_a) k_join<true><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
   else k_join<false><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
@@ -1171,7 +1163,8 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   const uint64_t n = h->mg_n_samples;
   if (n > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_partition: send buffer too small");
   constexpr int ITEMS = 8;
-  constexpr int TILE = kSortThreads * ITEMS;
+  constexpr int THREADS = kSort16Threads;
+  constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
   const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
   KS_ENSURE(h, h->lookback, lb_bytes);
@@ -1196,11 +1189,11 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   a.err = &h->d_ctl->err;
   if (counts) for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = 0;
   if (n) {
-    constexpr size_t smem = sort16_smem_bytes<ITEMS>();
-    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
+    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_dest_hist<<<h->sm_count * 2, 256, 0, h->stream>>>(a, hist);
     k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, 1);
-    k_onesweep_pass16<ITEMS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * 5), kSortThreads, smem, h->stream>>>(a);
+    k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * (1024 / THREADS)), THREADS, smem, h->stream>>>(a);
     h->launches += 3;
     if (counts) {
       uint32_t hc[16];

@@ -292,13 +292,14 @@ __global__ void __launch_bounds__(256) k_dest_hist(const SortPass16Args a, uint3
   if (threadIdx.x < 16 && sh[threadIdx.x]) atomicAdd(&hist[threadIdx.x], sh[threadIdx.x]);
 }
 
-template <int ITEMS>
-__global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortPass16Args a) {
-  constexpr int TILE = kSortThreads * ITEMS;
+template <int ITEMS, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(const SortPass16Args a) {
+  constexpr int TILE = THREADS * ITEMS;
+  constexpr int WARPS = THREADS / 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* s_items = reinterpret_cast<uint4*>(smem_raw);                       // [TILE]
   uint32_t* warp_hist = reinterpret_cast<uint32_t*>(s_items + TILE);          // [warps][256]
-  uint32_t* s_gpos = warp_hist + kSortWarps * 256;                            // [256]
+  uint32_t* s_gpos = warp_hist + WARPS * 256;                            // [256]
   uint32_t* s_misc = s_gpos + 256;                                            // [16]
 
   const uint32_t n = a.n_dev ? min(*a.n_dev, a.n) : a.n;  // with n_dev, a.n is the bound the buffers were sized for
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
   while (true) {
     __syncthreads();
     if (tid == 0) s_misc[0] = atomicAdd(a.ticket, 1u);
-    for (int i = tid; i < kSortWarps * 256; i += kSortThreads) warp_hist[i] = 0;
+    for (int i = tid; i < WARPS * 256; i += THREADS) warp_hist[i] = 0;
     __syncthreads();
     const uint32_t tile = s_misc[0];
     if (tile >= ntiles) break;
@@ -341,15 +342,16 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
     }
     __syncthreads();
     {
-      const uint32_t d = tid;
-      uint32_t acc = 0;
+      const bool digit_thread = tid < 256;  // one thread per digit; the other threads only keep the barriers company
+      const uint32_t d = tid & 255u;
+      uint32_t acc = 0, excl = 0;
+      if (digit_thread) {
 #pragma unroll
-      for (int w = 0; w < kSortWarps; ++w) {
+      for (int w = 0; w < WARPS; ++w) {
         const uint32_t t = warp_hist[w * 256 + d];
         warp_hist[w * 256 + d] = acc;
         acc += t;
       }
-      uint32_t excl = 0;
       volatile uint32_t* lb = a.lookback + (size_t)tile * 256 + d;
       if (tile == 0) {
         *lb = acc | kFlagPrefix;
@@ -370,15 +372,18 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
         }
         *lb = ((excl + acc) & kCountMask) | kFlagPrefix;
       }
+      }
       const uint32_t inc = warp_incl_scan(acc);
-      if (lane == 31) s_misc[1 + warp] = inc;
+      if (digit_thread && lane == 31) s_misc[1 + warp] = inc;
       __syncthreads();
-      uint32_t off = 0;
-      for (uint32_t w = 0; w < warp; ++w) off += s_misc[1 + w];
-      const uint32_t dstart = off + inc - acc;
-      s_gpos[d] = a.gbase[d] + excl - dstart;
+      if (digit_thread) {
+        uint32_t off = 0;
+        for (uint32_t w = 0; w < warp; ++w) off += s_misc[1 + w];
+        const uint32_t dstart = off + inc - acc;
+        s_gpos[d] = a.gbase[d] + excl - dstart;
 #pragma unroll
-      for (int w = 0; w < kSortWarps; ++w) warp_hist[w * 256 + d] += dstart;
+        for (int w = 0; w < WARPS; ++w) warp_hist[w * 256 + d] += dstart;
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -389,7 +394,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-      const uint32_t si = i * kSortThreads + tid;
+      const uint32_t si = i * THREADS + tid;
       if (si < tile_n) {
         const uint4 it = s_items[si];
         a.out[s_gpos[digit16(a, it.x, dmask)] + si] = it;
@@ -398,9 +403,9 @@ __global__ void __launch_bounds__(kSortThreads, 4) k_onesweep_pass16(const SortP
   }
 }
 
-template <int ITEMS>
+template <int ITEMS, int THREADS>
 constexpr size_t sort16_smem_bytes() {
-  return (size_t)kSortThreads * ITEMS * sizeof(uint4) + (kSortWarps * 256 + 256 + 16) * sizeof(uint32_t);
+  return (size_t)THREADS * ITEMS * sizeof(uint4) + ((THREADS / 32) * 256 + 256 + 16) * sizeof(uint32_t);
 }
 
 template <typename KeyT, typename ValT, int ITEMS>
