@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--max-records", type=int, default=10_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mg-driver", default="native", choices=["native", "python"], help="N > 1: who issues the exchanges (the library through NCCL, or torch.distributed)")
     return ap.parse_args()
 
 
@@ -184,9 +185,15 @@ def main():
 
     from kernel_scheduling_b200 import parallel
 
+    # N > 1: the native driver (exchanges issued by the library through NCCL); --mg-driver python runs the same phases with
+    # the exchanges in torch.distributed
+    session = parallel.NativeSession(builder, rank, world) if world > 1 and args.mg_driver == "native" else None
+
     def step_device():
         if world == 1:
             return builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+        if session is not None:
+            return session.build_device(dev)
         with torch.cuda.stream(stream):
             keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev, first_start), rank, world, on_device=True))
         builder.info = {"n_pairs": 0, "n_rows": table_t.numel() // 128, "n_keys": keys_t.numel() // 72}
@@ -215,10 +222,10 @@ def main():
     launches = builder.launch_count - launches0
     if world > 1:
         # per-kernel times for the roofline: the same kernels over the local window alone, after the timed region
-        for _ in range(3):
+        for i in range(4):  # the first call after the sharded runs has no size hints from a previous call: not counted
             builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
             for k in stage_names:
-                stage_ms[k] += builder.info[k] * args.steps / 3.0
+                stage_ms[k] += builder.info[k] * args.steps / 3.0 if i else 0.0
         torch.cuda.synchronize()
     ms_dev = e0.elapsed_time(e1)
     info = dict(builder.info)
@@ -232,8 +239,12 @@ def main():
         def step_e2e():
             if world == 1:
                 return builder.build(rec_pinned, time_ordered=True, pinned=True)
+            if session is not None:
+                with torch.cuda.stream(stream):
+                    dev.copy_(host, non_blocking=True)  # this step's records from pinned host memory
+                return session.build(dev, pinned=True)  # the whole table back to pinned host memory
             with torch.cuda.stream(stream):
-                dev.copy_(host, non_blocking=True)  # this step's records from pinned host memory
+                dev.copy_(host, non_blocking=True)
                 keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev, first_start), rank, world, on_device=True))
                 nonlocal out_pinned
                 need = keys_t.numel() + table_t.numel()

@@ -36,6 +36,7 @@ extern "C" {
 #define KS_ERR_WAIT 8         /* a bounded device-side wait ran out (the result is not valid) */
 #define KS_ERR_DUPLICATE 9    /* ks_count_batches: a start_ns occurs twice in one file (the reference asserts) */
 #define KS_ERR_TOO_LARGE 10   /* more items than one call supports (2^30 per sort, 2^32 overlapping pairs) */
+#define KS_ERR_COMM 11        /* NCCL is missing or one of its calls failed (ks_mg_build and its communicator) */
 
 /* ---- flags */
 #define KS_ON_DEVICE 1u            /* pointer arguments are device pointers */
@@ -191,6 +192,22 @@ int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n);            
 int64_t ks_mg_row_count(ks_handle* h);                                                          /* pair rows of this rank's range (after ks_mg_reduce) */
 int64_t ks_mg_solo(ks_handle* h, double* solo, int import);                                     /* solo times by dense id, out (0) or in (1) */
 int64_t ks_mg_finalize(ks_handle* h);                                                           /* tables of this rank's key range; then ks_copy_*_rows */
+
+/* The same build as ONE call per rank: the phases above with the five exchanges issued by the library itself through NCCL
+ * on the handle's stream (NCCL is bound at run time: libnccl.so.2, or the file named by the environment variable
+ * KS_NCCL_LIBRARY).  No counterpart in the reference.
+ *   ks_mg_unique_id     rank 0 makes the 128-byte NCCL id; the caller hands it to every rank (any transport)
+ *   ks_mg_comm_init     collective over the ranks: the handle's communicator (world <= 16)
+ *   ks_mg_build         collective: records = this rank's window (DEVICE pointer, start order, 16-byte aligned).  Returns
+ *                       the rows of the WHOLE table, which every rank then holds (ks_copy_pair_rows / ks_copy_key_rows);
+ *                       queued on the handle's stream, the copies are ordered behind it.  flags: KS_KEY_TYPE or 0.
+ *                       Errors found on the device (bad record, order, capacity) are returned by ALL ranks alike; an
+ *                       argument, CUDA or NCCL failure is local to its rank and fatal for the job.
+ *   ks_mg_comm_destroy  releases the communicator and the exchange buffers (ks_destroy does it too) */
+int ks_mg_unique_id(void* id128);
+int ks_mg_comm_init(ks_handle* h, const void* id128, int rank, int world);
+int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags, ks_table_info* info);
+int ks_mg_comm_destroy(ks_handle* h);
 
 /* ---- the agent's timing log (text) -> launch records, on the device.  Replaces the pandas read of the 17-column TSV the
  * agent writes (scheduler/agent.cpp:692-705; read at scheduler/postprocess.py:12-13).  Rows without end_ns (no completion

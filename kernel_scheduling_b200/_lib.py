@@ -22,7 +22,7 @@ ASSUME_TIME_ORDERED = 2
 KEY_TYPE = 4
 
 ERR_ARG, ERR_CUDA, ERR_RECORD, ERR_NOT_ORDERED, ERR_TOO_MANY_KEYS = 1, 2, 3, 4, 5
-ERR_TABLE_FULL, ERR_CAPACITY, ERR_WAIT, ERR_DUPLICATE, ERR_TOO_LARGE = 6, 7, 8, 9, 10
+ERR_TABLE_FULL, ERR_CAPACITY, ERR_WAIT, ERR_DUPLICATE, ERR_TOO_LARGE, ERR_COMM = 6, 7, 8, 9, 10, 11
 
 
 class KsConfig(ctypes.Structure):
@@ -79,6 +79,10 @@ KS_API = [
     ("ks_mg_row_count", [c_void_p], c_int64),
     ("ks_mg_solo", [c_void_p, c_void_p, c_int], c_int64),
     ("ks_mg_finalize", [c_void_p], c_int64),
+    ("ks_mg_unique_id", [c_void_p], c_int),
+    ("ks_mg_comm_init", [c_void_p, c_void_p, c_int, c_int], c_int),
+    ("ks_mg_build", [c_void_p, c_void_p, c_uint64, c_uint32, POINTER(KsTableInfo)], c_int64),
+    ("ks_mg_comm_destroy", [c_void_p], c_int),
     ("ks_tsv_parse", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_tsv_dictionary", [c_void_p, c_int, c_void_p, c_void_p], c_int64),
     ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),

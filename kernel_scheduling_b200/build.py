@@ -20,6 +20,7 @@ NVCC_FLAGS = [
     "-fmad=false",  # the float tables are defined as single IEEE operations: no contraction
     "-Xcompiler", "-fPIC", "-shared",
     "--expt-relaxed-constexpr",
+    "-ldl",  # NCCL is bound at run time (dlopen)
 ]
 
 

@@ -68,6 +68,15 @@ struct ks_handle {
   uint32_t mg_flags = 0;
   int mg_cur = 0;
 
+  // native multi-GPU driver (ks_mg_comm_init / ks_mg_build): an NCCL communicator of this handle's own
+  void* mg_comm = nullptr;
+  int mg_rank = 0, mg_world = 1;
+  uint32_t mg_key_cap = 4096;  // keys per rank that fit the first exchange; grows on every rank alike
+  DevBuf mg_block, mg_gathered, mg_recv;
+  uint32_t* mg_counts = nullptr;        // device: [0] launches in the tail, [1] launches in the halo
+  unsigned char* mg_host = nullptr;     // pinned: the headers (and histograms) of all ranks
+  size_t mg_host_cap = 0;
+
   // what the last ks_build_table saw: lets the next call queue every stage without reading counts back in between
   bool attr_sort16 = false, attr_decode = false;  // kernel attributes set on this handle's device
   bool hint_valid = false;
@@ -453,6 +462,8 @@ __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start,
   out[6 * (size_t)r + 5] = st.hi[0];
 }
 
+void mg_native_release(ks_handle* h);  // ks_mg_native.cuh
+
 float ev_ms(cudaEvent_t a, cudaEvent_t b) {
   float ms = 0.f;
   cudaEventElapsedTime(&ms, a, b);
@@ -479,6 +490,7 @@ const char* ks_status_string(int status) {
     case KS_ERR_WAIT: return "a bounded device-side wait ran out";
     case KS_ERR_DUPLICATE: return "duplicate start_ns inside one file";
     case KS_ERR_TOO_LARGE: return "too many items for one call";
+    case KS_ERR_COMM: return "NCCL missing or failed";
     default: return "unknown status";
   }
 }
@@ -540,6 +552,7 @@ void ks_destroy(ks_handle* h) {
   if (!h) return;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
+  mg_native_release(h);
   auto fr = [](void* p) { if (p) cudaFree(p); };
   fr(h->d_ctl); fr(h->dict_keys); fr(h->dict_words); fr(h->dict_launches); fr(h->dict_solo); fr(h->kid_of_slot);
   fr(h->dkeys); fr(h->dslot); fr(h->drank); fr(h->slot_of_kid); fr(h->row_of_kid); fr(h->keys_sorted); fr(h->solo_ns); fr(h->key_rows);
@@ -1010,6 +1023,55 @@ int mg_status(ks_handle* h, const char* what) {
   return 0;
 }
 
+// K2 + K4 over the n samples in sample set 0 (this rank's key range), then the solo times of the keys reduced here.
+// Queues only; the caller reads the control words back.
+int mg_reduce_queue(ks_handle* h, uint64_t n) {
+  // counters of the row / statistics kernels start from zero
+  { int r = mg_zero_u32(h, &h->d_ctl->n_rows, 2); if (r) return r; }
+  { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
+  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->scratch0, 0, 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  const uint64_t nk = h->mg_nk;
+  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk));
+  if (cur < 0) return cur;
+  h->mg_cur = cur;
+  h->mg_n_samples = n;
+  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
+  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n, max_rows); if (r) return r; }
+  if (nk) {
+    k_solo_ns<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(as<RowStats>(h->stats), h->row_of_kid, (uint32_t)nk, h->solo_ns);
+    ++h->launches;
+  }
+  return 0;
+}
+
+// key rows of every key and the pair rows of this rank's range (written to `out`, room for max_rows)
+int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows) {
+  const uint64_t nk = h->mg_nk;
+  FinalArgs f{};
+  f.stats = as<RowStats>(h->stats);
+  f.row_start = as<uint32_t>(h->row_start);
+  f.row_key = as<uint32_t>(h->row_key);
+  f.row_of_kid = h->row_of_kid;
+  f.slot_of_kid = h->slot_of_kid;
+  f.keys_sorted = h->keys_sorted;
+  f.dict_words = h->dict_words;
+  f.dict_launches = h->dict_launches;
+  f.dict_solo = h->dict_solo;
+  f.solo_ns = h->solo_ns;
+  f.solo_given = 1;
+  f.key_rows = h->key_rows;
+  f.pair_rows = out;
+  f.max_pair_rows = max_rows;
+  f.ctl = h->d_ctl;
+  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
+  k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
+  h->launches += nk ? 2 : 1;
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1212,23 +1274,7 @@ int64_t ks_mg_reduce(ks_handle* h, const void* samples, uint64_t n) {
   KS_CUDA(h, cudaSetDevice(h->device));
   { int r = ensure_samples(h, std::max<uint64_t>(n, 16)); if (r) return r; }
   if (n) KS_CUDA(h, cudaMemcpyAsync(h->samples[0].p, samples, n * 16, cudaMemcpyDeviceToDevice, h->stream));
-  // counters of the row / statistics kernels start from zero
-  { int r = mg_zero_u32(h, &h->d_ctl->n_rows, 2); if (r) return r; }
-  { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
-  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->scratch0, 0, 8, h->stream));
-  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
-  KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
-  const uint64_t nk = h->mg_nk;
-  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk));
-  if (cur < 0) return cur;
-  h->mg_cur = cur;
-  h->mg_n_samples = n;
-  const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
-  { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n, max_rows); if (r) return r; }
-  if (nk) {
-    k_solo_ns<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(as<RowStats>(h->stats), h->row_of_kid, (uint32_t)nk, h->solo_ns);
-    ++h->launches;
-  }
+  { int r = mg_reduce_queue(h, n); if (r) return r; }
   { int r = read_ctl(h); if (r) return r; }
   { int r = mg_status(h, "ks_mg_reduce"); if (r) return r; }
   return (int64_t)h->h_ctl->n_rows;
@@ -1255,26 +1301,7 @@ int64_t ks_mg_finalize(ks_handle* h) {
   const uint64_t nk = h->mg_nk, n = h->mg_n_samples;
   const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
   KS_ENSURE(h, h->pair_rows, (size_t)max_rows * sizeof(ks_pair_row));
-  FinalArgs f{};
-  f.stats = as<RowStats>(h->stats);
-  f.row_start = as<uint32_t>(h->row_start);
-  f.row_key = as<uint32_t>(h->row_key);
-  f.row_of_kid = h->row_of_kid;
-  f.slot_of_kid = h->slot_of_kid;
-  f.keys_sorted = h->keys_sorted;
-  f.dict_words = h->dict_words;
-  f.dict_launches = h->dict_launches;
-  f.dict_solo = h->dict_solo;
-  f.solo_ns = h->solo_ns;
-  f.solo_given = 1;
-  f.key_rows = h->key_rows;
-  f.pair_rows = as<ks_pair_row>(h->pair_rows);
-  f.max_pair_rows = max_rows;
-  f.ctl = h->d_ctl;
-  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
-  k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
-  h->launches += nk ? 2 : 1;
-  KS_CUDA(h, cudaGetLastError());
+  { int r = mg_finalize_queue(h, as<ks_pair_row>(h->pair_rows), max_rows); if (r) return r; }
   // no host round trip: the counts are known since ks_mg_reduce read them back
   h->n_key_rows = nk;
   h->n_pair_rows = h->h_ctl->n_rows - h->h_ctl->ticket2;
@@ -1282,6 +1309,8 @@ int64_t ks_mg_finalize(ks_handle* h) {
 }
 
 }  // extern "C"
+
+#include "ks_mg_native.cuh"
 
 // =========================================================================================================
 // Agent timing log (TSV text) -> launch records on the device.  Three calls: parse (text in, counts out), dictionaries

@@ -130,4 +130,206 @@ __global__ void __launch_bounds__(256) k_solo_ns(const RowStats* __restrict__ st
   solo_ns[kid] = row == 0xFFFFFFFFu ? __longlong_as_double(0x7FF8000000000000ll) : ((double)stats[row].lo[0] + (double)stats[row].hi[0]) * 0.5;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Kernels of the native driver (ks_mg_build): the same phases, but every count a later kernel needs is read on the
+// device, so the host waits only three times per table (after the three header exchanges).
+
+// First 256 bytes of every exchanged block: the sender's control words and the counts the other ranks need.
+struct MgHeader {
+  Control ctl;
+  uint32_t n_tail;                 // launches in the sender's tail (block 1)
+  uint32_t reserved0;
+  unsigned long long capacity;     // sample capacity of the sender (block 2): n_pairs above it means "grow and repeat"
+  unsigned long long first_start;  // start_ns of the sender's first record
+  unsigned char pad[256 - sizeof(Control) - 24];
+};
+static_assert(sizeof(MgHeader) == 256, "exchange header is 256 bytes");
+
+__global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n_tail, const unsigned char* records, uint64_t n_owned, uint64_t capacity) {
+  const uint32_t t = threadIdx.x;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(ctl);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(&out->ctl);
+  if (t < sizeof(Control) / 4) dst[t] = src[t];
+  if (t == 0) {
+    out->n_tail = n_tail ? *n_tail : 0u;
+    out->reserved0 = 0;
+    out->capacity = capacity;
+    out->first_start = n_owned ? *reinterpret_cast<const unsigned long long*>(records + 32) : 0ull;
+  }
+}
+
+// k_gather_records with the count on the device
+__global__ void __launch_bounds__(256) k_gather_records_dev(const uint4* __restrict__ records, const uint32_t* __restrict__ idx, const uint32_t* __restrict__ n_dev,
+                                                            uint32_t capacity, uint4* __restrict__ out) {
+  const uint32_t n = min(*n_dev, capacity);
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * 3) return;
+  out[t] = records[(size_t)idx[t / 3] * 3 + t % 3];
+}
+
+// k_export_keys with the count on the device (ctl->n_keys, clamped to what the block holds)
+__global__ void __launch_bounds__(256) k_export_keys_dev(const unsigned long long* __restrict__ dkeys, const uint32_t* __restrict__ dslot, const uint4* __restrict__ dict_words,
+                                                         const Control* __restrict__ ctl, uint32_t capacity, unsigned long long* __restrict__ keys_out, uint4* __restrict__ words_out) {
+  const uint32_t n = min(ctl->n_keys, capacity);
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  keys_out[i] = dkeys[i];
+  words_out[2 * (size_t)i] = dict_words[2 * (size_t)dslot[i]];
+  words_out[2 * (size_t)i + 1] = dict_words[2 * (size_t)dslot[i] + 1];
+}
+
+// The halo of this rank, straight from the gathered blocks onto the timeline: of the tails of all earlier ranks, the
+// launches that end after this window's first start, in start order, placed in the last entries of the kHaloMax timeline
+// slots in front of the window.  The unused slots in front of them become inert entries (solo flag, no duration, a start
+// no later than any halo start), so the join always sees exactly kHaloMax halo slots and needs no count from the host.
+struct HaloArgs {
+  const unsigned char* gathered;  // block 1 of every rank, `stride` bytes apart; tails start 256 bytes into a block
+  size_t stride;
+  uint32_t rank;
+  const unsigned char* own_records;
+  uint64_t n_owned;
+  unsigned long long* dict_keys;
+  int type_mode;
+  unsigned long long* tl_start;  // timeline set 0, entries [0, kHaloMax) are the halo slots
+  unsigned long long* tl_dm;
+  uint32_t* n_halo;              // out: launches found (above kHaloMax: nothing was placed)
+  Control* ctl;
+};
+
+__global__ void __launch_bounds__(1024) k_halo_place(const HaloArgs a) {
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_total;
+  __shared__ unsigned long long s_min;
+  const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+  const unsigned long long first = a.n_owned ? *reinterpret_cast<const unsigned long long*>(a.own_records + 32) : 0ull;
+  if (tid == 0) { s_total = 0; s_min = ~0ull; }
+  __syncthreads();
+  auto tail_count = [&](uint32_t q) { return min(reinterpret_cast<const MgHeader*>(a.gathered + q * a.stride)->n_tail, kHaloMax); };
+  auto tail_rec = [&](uint32_t q, uint32_t i) { return a.gathered + q * a.stride + sizeof(MgHeader) + (size_t)i * 48; };
+  // pass 1: how many, and the earliest start among them
+  uint32_t mine = 0;
+  unsigned long long my_min = ~0ull;
+  if (a.n_owned) {
+    for (uint32_t q = 0; q < a.rank; ++q) {
+      const uint32_t nq = tail_count(q);
+      for (uint32_t i = tid; i < nq; i += blockDim.x) {
+        const unsigned long long* se = reinterpret_cast<const unsigned long long*>(tail_rec(q, i) + 32);
+        if (se[1] > first) { ++mine; my_min = min(my_min, se[0]); }
+      }
+    }
+  }
+  mine = warp_sum(mine);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) my_min = min(my_min, __shfl_xor_sync(0xFFFFFFFFu, my_min, o));
+  if (lane == 0) { if (mine) atomicAdd(&s_total, mine); if (my_min != ~0ull) atomicMin(&s_min, my_min); }
+  __syncthreads();
+  const uint32_t total = s_total;
+  if (tid == 0) *a.n_halo = total;
+  const uint32_t placed = total <= kHaloMax ? total : 0u;
+  const unsigned long long filler_start = placed ? s_min : first;
+  for (uint32_t i = tid; i < kHaloMax - placed; i += blockDim.x) {
+    a.tl_start[i] = filler_start;
+    a.tl_dm[i] = (unsigned long long)kMetaSoloBit << 32;
+  }
+  if (!placed) return;
+  // pass 2: ordered placement (ranks ascending, tails are in start order, windows are ordered in time)
+  uint32_t base = kHaloMax - placed, max_dur = 0, err = 0;
+  for (uint32_t q = 0; q < a.rank; ++q) {
+    const uint32_t nq = tail_count(q);
+    for (uint32_t i0 = 0; i0 < nq; i0 += blockDim.x) {
+      const uint32_t i = i0 + tid;
+      bool take = false;
+      uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
+      if (i < nq) {
+        const uint4* rp = reinterpret_cast<const uint4*>(tail_rec(q, i));
+        w2 = rp[2];
+        const unsigned long long end = (unsigned long long)w2.z | ((unsigned long long)w2.w << 32);
+        take = end > first;
+        if (take) { w0 = rp[0]; w1 = rp[1]; }
+      }
+      const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, take);
+      if (lane == 0) s_warp[warp] = __popc(ballot);
+      __syncthreads();
+      uint32_t before = 0, chunk = 0;
+      for (uint32_t w = 0; w < blockDim.x / 32; ++w) { if (w < warp) before += s_warp[w]; chunk += s_warp[w]; }
+      if (take) {
+        const uint32_t at = base + before + __popc(ballot & lanemask_lt());
+        const unsigned long long start = (unsigned long long)w2.x | ((unsigned long long)w2.y << 32);
+        const unsigned long long end = (unsigned long long)w2.z | ((unsigned long long)w2.w << 32);
+        const uint64_t key = kernel_key(w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, a.type_mode != 0);
+        bool inserted = false;
+        uint32_t slot = dict_find_or_insert(a.dict_keys, key, &inserted);
+        if (slot >= kDictSlots || inserted) { err |= kErrTooManyKeys; slot = 0; }  // every halo key came with its owner's key list
+        const uint32_t dur = (uint32_t)(end - start);
+        a.tl_start[at] = start;
+        a.tl_dm[at] = (unsigned long long)dur | ((unsigned long long)(slot | (w1.w & (kMetaSoloBit | 0xFF000000u))) << 32);
+        max_dur = max(max_dur, dur);
+      }
+      base += chunk;
+      __syncthreads();
+    }
+  }
+  max_dur = warp_max(max_dur);
+  err = __reduce_or_sync(0xFFFFFFFFu, err);
+  if (lane == 0) { if (max_dur) atomicMax(&a.ctl->max_dur, max_dur); if (err) atomicOr(&a.ctl->err, err); }
+}
+
+// per-key launch counts by dense key id out of the dictionary, count on the device
+__global__ void __launch_bounds__(256) k_counts_export_dev(const uint32_t* __restrict__ slot_of_kid, const uint32_t* __restrict__ dict_launches,
+                                                           const uint32_t* __restrict__ dict_solo, const Control* __restrict__ ctl, uint32_t capacity,
+                                                           unsigned long long* __restrict__ launches, unsigned long long* __restrict__ solo) {
+  const uint32_t nk = min(ctl->n_keys, capacity);
+  const uint32_t kid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (kid >= nk) return;
+  const uint32_t slot = slot_of_kid[kid];
+  launches[kid] = dict_launches[slot];
+  solo[kid] = dict_solo[slot];
+}
+
+// the counts of all ranks summed, back into the dictionary (blocks `stride` bytes apart, counts at the given offsets)
+__global__ void __launch_bounds__(256) k_counts_sum_import(const unsigned char* __restrict__ gathered, size_t stride, uint32_t world, size_t off_launches, size_t off_solo,
+                                                           const uint32_t* __restrict__ slot_of_kid, uint32_t nk, uint32_t* dict_launches, uint32_t* dict_solo) {
+  const uint32_t kid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (kid >= nk) return;
+  unsigned long long l = 0, s = 0;
+  for (uint32_t q = 0; q < world; ++q) {
+    l += reinterpret_cast<const unsigned long long*>(gathered + q * stride + off_launches)[kid];
+    s += reinterpret_cast<const unsigned long long*>(gathered + q * stride + off_solo)[kid];
+  }
+  const uint32_t slot = slot_of_kid[kid];
+  dict_launches[slot] = (uint32_t)l;
+  dict_solo[slot] = (uint32_t)s;
+}
+
+// k_key_hist with the sample count and the key count on the device: bin = sort key >> shift, shift from the key count
+__device__ __forceinline__ uint32_t key_hist_shift(unsigned long long nk) {
+  const unsigned long long top = nk + nk * nk;
+  const int bits = top ? 64 - __clzll(top) : 0;
+  return bits > 12 ? (uint32_t)(bits - 12) : 0u;
+}
+__global__ void __launch_bounds__(256) k_key_hist_dev(const uint4* __restrict__ samples, const Control* __restrict__ ctl, uint64_t capacity, unsigned long long* __restrict__ hist) {
+  __shared__ uint32_t sh[kKeyHistBins];
+  const uint32_t n = (uint32_t)min((unsigned long long)capacity, ctl->n_pairs);
+  const uint32_t shift = key_hist_shift(ctl->n_keys);
+  for (uint32_t i = threadIdx.x; i < kKeyHistBins; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&sh[min(samples[i].x >> shift, kKeyHistBins - 1)], 1u);
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < kKeyHistBins; i += blockDim.x)
+    if (sh[i]) atomicAdd(&hist[i], (unsigned long long)sh[i]);
+}
+
+// every key's solo time: the rank that reduced the key's solo row has a number, the others NaN
+__global__ void __launch_bounds__(256) k_solo_merge(const unsigned char* __restrict__ gathered, size_t stride, uint32_t world, size_t off_solo, uint32_t nk,
+                                                    double* __restrict__ solo_ns) {
+  const uint32_t kid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (kid >= nk) return;
+  double best = __longlong_as_double(0x7FF8000000000000ll);
+  for (uint32_t q = 0; q < world; ++q) {
+    const double v = reinterpret_cast<const double*>(gathered + q * stride + off_solo)[kid];
+    if (v == v && !(best >= v)) best = v;  // the maximum of the numbers
+  }
+  solo_ns[kid] = best;
+}
+
 }  // namespace ks

@@ -1,0 +1,436 @@
+// ks_mg_native.cuh -- the multi-GPU table build as ONE library call per rank: the phases of the ks_mg_* session with the
+// collectives issued from C++ through NCCL on the handle's stream.  Part of ks_api.cu (included behind the handle and the
+// phase functions); not a translation unit of its own.
+//
+// One process per GPU calls ks_mg_build with its window of the start-ordered trace.  The five exchanges:
+//   1. all-gather  [header | tail launches | distinct keys + launch fields]      -> global key ids, halo
+//   2. all-gather  [header | sample-key histogram | per-key launch counts]       -> splitters, transfer sizes
+//   3. all-to-all  samples to the rank that owns their key range                 (send/recv pairs, exact sizes)
+//   4. all-gather  [header | solo times of the keys reduced here]                -> every key's solo time, shard sizes
+//   5. all-gather  table shards, straight into place in the whole table          (send/recv pairs, exact sizes)
+// Every block starts with a 256-byte header that carries the sender's control words, so after exchanges 1, 2 and 4 every
+// rank knows every rank's error bits and counts: an error on any rank makes ALL ranks return it from the same point, and
+// decisions that change what is exchanged next (a larger key block, a larger sample stream) are taken alike everywhere.
+// The host waits for the device three times per table (after the header exchanges); everything else is queued.
+//
+// NCCL is bound at run time (dlopen of libnccl.so.2, or the library named by KS_NCCL_LIBRARY): the library has no link-time
+// dependency on it, and a process that already loaded NCCL (PyTorch) shares that copy.
+#pragma once
+
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <mutex>
+
+namespace {
+
+struct NcclId { char internal[128]; };  // ncclUniqueId
+
+struct NcclApi {
+  void* lib = nullptr;
+  int (*GetUniqueId)(NcclId*) = nullptr;
+  int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  std::string error;
+};
+constexpr int kNcclUint8 = 1;  // ncclUint8
+
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* named = getenv("KS_NCCL_LIBRARY");
+    const char* names[] = {named, "libnccl.so.2", "libnccl.so"};
+    for (const char* name : names) {
+      if (!name || !*name) continue;
+      api.lib = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+      if (api.lib) break;
+    }
+    if (!api.lib) { api.error = "NCCL not found (libnccl.so.2); name the library in KS_NCCL_LIBRARY"; return; }
+    auto sym = [&](const char* name) {
+      void* p = dlsym(api.lib, name);
+      if (!p && api.error.empty()) api.error = std::string("NCCL symbol missing: ") + name;
+      return p;
+    };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+  });
+  return &api;
+}
+
+#define KS_NCCL(h, call)                                                                                              \
+  do {                                                                                                                \
+    int e__ = (call);                                                                                                 \
+    if (e__ != 0) return fail((h), KS_ERR_COMM, std::string(#call) + ": " + nccl_api()->GetErrorString(e__));         \
+  } while (0)
+
+void mg_native_release(ks_handle* h) {
+  if (h->mg_comm) {
+    nccl_api()->CommDestroy(h->mg_comm);
+    h->mg_comm = nullptr;
+  }
+  for (DevBuf* b : {&h->mg_block, &h->mg_gathered, &h->mg_recv}) {
+    if (b->p) cudaFree(b->p);
+    b->p = nullptr;
+    b->cap = 0;
+  }
+  if (h->mg_counts) cudaFree(h->mg_counts);
+  h->mg_counts = nullptr;
+  if (h->mg_host) cudaFreeHost(h->mg_host);
+  h->mg_host = nullptr;
+  h->mg_host_cap = 0;
+}
+
+constexpr size_t kMgTailBytes = (size_t)kHaloMax * 48;
+constexpr size_t kMgHistBytes = (size_t)kKeyHistBins * 8;
+
+// the first `width` bytes of every rank's gathered block -> pinned host memory, then wait for the device
+int mg_fetch_heads(ks_handle* h, size_t stride, size_t width) {
+  const size_t need = width * (size_t)h->mg_world;
+  if (need > h->mg_host_cap) {
+    if (h->mg_host) cudaFreeHost(h->mg_host);
+    h->mg_host = nullptr;
+    h->mg_host_cap = 0;
+    KS_CUDA(h, cudaMallocHost(reinterpret_cast<void**>(&h->mg_host), need));
+    h->mg_host_cap = need;
+  }
+  KS_CUDA(h, cudaMemcpy2DAsync(h->mg_host, width, h->mg_gathered.p, stride, width, (size_t)h->mg_world, cudaMemcpyDeviceToHost, h->stream));
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return 0;
+}
+
+const MgHeader& mg_head(const ks_handle* h, size_t width, int q) { return *reinterpret_cast<const MgHeader*>(h->mg_host + width * (size_t)q); }
+
+// the same verdict on every rank: the first rank (in rank order) whose control words carry an error decides
+int mg_any_error(ks_handle* h, size_t width, const char* where) {
+  for (int q = 0; q < h->mg_world; ++q) {
+    const int st = status_of_err(mg_head(h, width, q).ctl.err, true);
+    if (st) return fail(h, st, std::string("ks_mg_build (") + where + "), rank " + std::to_string(q) + ": " + ks_status_string(st));
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ks_mg_unique_id(void* id128) {
+  if (!id128) return -KS_ERR_ARG;
+  NcclApi* api = nccl_api();
+  if (!api->error.empty()) { g_null_error = api->error; return -KS_ERR_COMM; }
+  NcclId id;
+  const int e = api->GetUniqueId(&id);
+  if (e != 0) { g_null_error = std::string("ncclGetUniqueId: ") + api->GetErrorString(e); return -KS_ERR_COMM; }
+  memcpy(id128, id.internal, sizeof(id.internal));
+  return KS_OK;
+}
+
+int ks_mg_comm_init(ks_handle* h, const void* id128, int rank, int world) {
+  if (!h || !id128 || world < 1 || world > 16 || rank < 0 || rank >= world) return -KS_ERR_ARG;
+  NcclApi* api = nccl_api();
+  if (!api->error.empty()) return fail(h, KS_ERR_COMM, api->error);
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (h->mg_comm) { api->CommDestroy(h->mg_comm); h->mg_comm = nullptr; }
+  NcclId id;
+  memcpy(id.internal, id128, sizeof(id.internal));
+  KS_NCCL(h, api->CommInitRank(&h->mg_comm, world, id, rank));
+  h->mg_rank = rank;
+  h->mg_world = world;
+  if (!h->mg_counts) KS_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->mg_counts), 16));
+  return KS_OK;
+}
+
+int ks_mg_comm_destroy(ks_handle* h) {
+  if (!h) return -KS_ERR_ARG;
+  cudaSetDevice(h->device);
+  if (h->stream) cudaStreamSynchronize(h->stream);
+  mg_native_release(h);
+  return KS_OK;
+}
+
+int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags, ks_table_info* info) {
+  if (!h || (!records && n_owned) || (flags & ~KS_KEY_TYPE)) return -KS_ERR_ARG;
+  if (!h->mg_comm) return fail(h, KS_ERR_ARG, "ks_mg_build: no communicator (ks_mg_comm_init)");
+  NcclApi* api = nccl_api();
+  const int world = h->mg_world, rank = h->mg_rank;
+  const unsigned char* rec = reinterpret_cast<const unsigned char*>(records);
+  constexpr size_t H = sizeof(MgHeader);
+
+  // ---- phase 1: K1 over the window, its tail, its distinct keys                                 (queued, no wait)
+  { int64_t r = ks_mg_begin(h, records, n_owned, flags); if (r < 0) return r; }
+  KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
+  uint32_t* tail_idx = as<uint32_t>(h->tmp[0]);
+  KS_CUDA(h, cudaMemsetAsync(h->mg_counts, 0, 16, h->stream));
+  if (n_owned) {
+    k_tail_select<<<1, 1024, 0, h->stream>>>(as<unsigned long long>(h->tl_start[0]) + kHaloMax, as<unsigned long long>(h->tl_dm[0]) + kHaloMax, (uint32_t)n_owned,
+                                             tail_idx, kHaloMax, h->mg_counts, h->d_ctl);
+    ++h->launches;
+  }
+  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+  DictArgs d{};
+  d.dict_keys = h->dict_keys; d.dkeys = h->dkeys; d.dslot = h->dslot; d.drank = h->drank; d.kid_of_slot = h->kid_of_slot;
+  d.slot_of_kid = h->slot_of_kid; d.keys_sorted = h->keys_sorted; d.ctl = h->d_ctl;
+  k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
+  ++h->launches;
+
+  // blocks 2 and 4 at their largest, so that the exchange buffers are sized once per key capacity
+  const size_t block_other = std::max(H + kMgHistBytes + (size_t)kMaxKeys * 16, H + (size_t)kMaxKeys * 8);
+  size_t block1 = 0, off_keys = 0, off_words = 0;
+  uint64_t key_sum = 0;
+  for (;;) {
+    const uint32_t cap = h->mg_key_cap;
+    off_keys = H + kMgTailBytes;
+    off_words = off_keys + (size_t)cap * 8;
+    block1 = off_words + (size_t)cap * 32;
+    KS_ENSURE(h, h->mg_block, std::max(block1, block_other));
+    KS_ENSURE(h, h->mg_gathered, std::max(block1, block_other) * (size_t)world);
+    unsigned char* blk = as<unsigned char>(h->mg_block);
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, 0);
+    if (n_owned)
+      k_gather_records_dev<<<(kHaloMax * 3 + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const uint4*>(rec), tail_idx, h->mg_counts, kHaloMax,
+                                                                              reinterpret_cast<uint4*>(blk + H));
+    k_export_keys_dev<<<(cap + 255) / 256, 256, 0, h->stream>>>(h->dkeys, h->dslot, h->dict_words, h->d_ctl, cap, reinterpret_cast<unsigned long long*>(blk + off_keys),
+                                                                reinterpret_cast<uint4*>(blk + off_words));
+    h->launches += n_owned ? 3 : 2;
+    KS_CUDA(h, cudaGetLastError());
+    KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block1, kNcclUint8, h->mg_comm, h->stream));
+    { int r = mg_fetch_heads(h, block1, H); if (r) return r; }                                         // ---- wait 1
+    { int r = mg_any_error(h, H, "decode"); if (r) return r; }
+    uint32_t need = 0;
+    key_sum = 0;
+    for (int q = 0; q < world; ++q) {
+      const MgHeader& hd = mg_head(h, H, q);
+      if (hd.n_tail > kHaloMax)
+        return fail(h, KS_ERR_CAPACITY, "ks_mg_build: rank " + std::to_string(q) + " has more launches reaching into the next window than the halo can hold");
+      need = std::max(need, hd.ctl.n_keys);
+      key_sum += hd.ctl.n_keys;
+    }
+    if (need <= cap) break;
+    uint32_t grown = cap;
+    while (grown < need) grown <<= 1;
+    h->mg_key_cap = grown;  // every rank saw the same headers and grows alike
+  }
+
+  // ---- phase 2: global key ids, halo, samples, histogram + launch counts                        (queued, no wait)
+  unsigned char* gathered = as<unsigned char>(h->mg_gathered);
+  for (int q = 0; q < world; ++q) {
+    const uint32_t nq = mg_head(h, H, q).ctl.n_keys;
+    if (!nq) continue;
+    k_dict_insert<<<(nq + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const unsigned long long*>(gathered + q * block1 + off_keys),
+                                                           reinterpret_cast<const uint4*>(gathered + q * block1 + off_words), nq, h->dict_keys, h->dict_words, h->d_ctl);
+    ++h->launches;
+  }
+  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+  KS_CUDA(h, cudaMemsetAsync(h->drank, 0, (size_t)(kMaxKeys + 1) * 4, h->stream));
+  { int r = run_dict(h); if (r) return r; }
+  {
+    HaloArgs ha{};
+    ha.gathered = gathered;
+    ha.stride = block1;
+    ha.rank = (uint32_t)rank;
+    ha.own_records = rec;
+    ha.n_owned = n_owned;
+    ha.dict_keys = h->dict_keys;
+    ha.type_mode = (flags & KS_KEY_TYPE) ? 1 : 0;
+    ha.tl_start = as<unsigned long long>(h->tl_start[0]);
+    ha.tl_dm = as<unsigned long long>(h->tl_dm[0]);
+    ha.n_halo = h->mg_counts + 1;
+    ha.ctl = h->d_ctl;
+    k_halo_place<<<1, 1024, 0, h->stream>>>(ha);
+    ++h->launches;
+  }
+  h->mg_n_halo = kHaloMax;  // the join always sees all halo slots (unused ones are inert)
+  const uint32_t cap2 = (uint32_t)std::min<uint64_t>(key_sum, kMaxKeys);  // the global key count is at most the sum
+  const size_t off_launches = H + kMgHistBytes, off_solo = off_launches + (size_t)cap2 * 8;
+  const size_t block2 = (off_solo + (size_t)cap2 * 8 + 15) & ~(size_t)15;
+  const uint64_t n_tl = n_owned + kHaloMax;
+  uint64_t cap_s = sample_capacity(h);
+  if (cap_s < std::max<uint64_t>(2 * n_tl, 1u << 16)) {
+    cap_s = std::max<uint64_t>(2 * n_tl, 1u << 16);
+    int r = ensure_samples(h, cap_s);
+    if (r) return r;
+  }
+  const size_t width2 = H + kMgHistBytes;
+  for (int attempt = 0;; ++attempt) {
+    unsigned char* blk = as<unsigned char>(h->mg_block);
+    KS_CUDA(h, cudaMemsetAsync(blk + H, 0, block2 - H, h->stream));
+    if (cap2)
+      k_counts_export_dev<<<(cap2 + 255) / 256, 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, h->d_ctl, cap2,
+                                                                     reinterpret_cast<unsigned long long*>(blk + off_launches),
+                                                                     reinterpret_cast<unsigned long long*>(blk + off_solo));
+    SoloArgs s{};
+    s.solo_stream = as<unsigned long long>(h->solo_stream);
+    s.kid_of_slot = h->kid_of_slot;
+    s.samples = as<uint4>(h->samples[0]);
+    s.capacity = cap_s;
+    s.ctl = h->d_ctl;
+    k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+    { int r = run_join(h, 0, n_tl, cap_s, nullptr, nullptr, 0, kHaloMax); if (r) return r; }
+    k_key_hist_dev<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s);
+    h->launches += cap2 ? 4 : 3;
+    KS_CUDA(h, cudaGetLastError());
+    KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block2, kNcclUint8, h->mg_comm, h->stream));
+    { int r = mg_fetch_heads(h, block2, width2); if (r) return r; }                                    // ---- wait 2
+    { int r = mg_any_error(h, width2, "join"); if (r) return r; }
+    bool any_over = false;
+    for (int q = 0; q < world; ++q) {
+      const MgHeader& hd = mg_head(h, width2, q);
+      if (hd.n_tail > kHaloMax)  // here: the launches of earlier windows that reach into window q
+        return fail(h, KS_ERR_CAPACITY, "ks_mg_build: " + std::to_string(hd.n_tail) + " launches of earlier windows reach into window " + std::to_string(q) +
+                                            "; the halo holds " + std::to_string(kHaloMax));
+      if (hd.ctl.n_keys != mg_head(h, width2, 0).ctl.n_keys) return fail(h, KS_ERR_COMM, "ks_mg_build: the ranks disagree on the number of keys");
+      if (hd.ctl.n_pairs >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more on rank " + std::to_string(q));
+      if (hd.ctl.n_pairs > hd.capacity) any_over = true;
+    }
+    if (!any_over) break;
+    if (attempt == 1) return fail(h, KS_ERR_CAPACITY, "ks_mg_build: sample stream still too small");
+    const uint64_t mine = mg_head(h, width2, rank).ctl.n_pairs;
+    if (mine > cap_s) {  // only the ranks that ran over grow; all of them repeat the step
+      cap_s = mine + mine / 16;
+      int r = ensure_samples(h, cap_s);
+      if (r) return r;
+    }
+  }
+  const Control ctl2 = mg_head(h, width2, rank).ctl;  // a copy: the pinned area is reused by the next exchange
+  const uint64_t nk = ctl2.n_keys;
+  h->mg_nk = nk;
+  h->mg_n_samples = ctl2.n_pairs;
+  const uint64_t n_solo = ctl2.n_solo, n_samples_local = ctl2.n_pairs;
+
+  // ---- phase 3: splitters, partition, the samples travel                                        (queued, no wait)
+  std::vector<uint64_t> total(kKeyHistBins, 0);
+  auto hist_of = [&](int q) { return reinterpret_cast<const uint64_t*>(h->mg_host + width2 * (size_t)q + H); };
+  for (int q = 0; q < world; ++q)
+    for (uint32_t b = 0; b < kKeyHistBins; ++b) total[b] += hist_of(q)[b];
+  uint64_t all = 0;
+  for (uint64_t v : total) all += v;
+  // rank r owns bins [edge[r], edge[r+1]): the first bin with at least r/world of the samples in front of it
+  std::vector<uint32_t> edge(world + 1, kKeyHistBins);
+  edge[0] = 0;
+  {
+    uint64_t before = 0;
+    uint32_t b = 0;
+    for (int r = 1; r < world; ++r) {
+      const uint64_t target = (all * (uint64_t)r + (uint64_t)world - 1) / (uint64_t)world;
+      while (b < kKeyHistBins && before < target) before += total[b++];
+      edge[r] = b;
+    }
+  }
+  std::vector<uint64_t> send_cnt(world, 0), recv_cnt(world, 0);
+  auto range_sum = [&](int q, int r) { uint64_t s = 0; for (uint32_t b = edge[r]; b < edge[r + 1]; ++b) s += hist_of(q)[b]; return s; };
+  uint64_t n_recv = 0;
+  for (int q = 0; q < world; ++q) {
+    send_cnt[q] = range_sum(rank, q);
+    recv_cnt[q] = range_sum(q, rank);
+    n_recv += recv_cnt[q];
+  }
+  for (int r = 0; r < world; ++r) {  // every rank's inbound total, so that all ranks refuse together
+    uint64_t in = 0;
+    for (int q = 0; q < world; ++q) in += range_sum(q, r);
+    if (in >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more in the key range of rank " + std::to_string(r));
+  }
+  if (nk) {
+    k_counts_sum_import<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block2, (uint32_t)world, off_launches, off_solo, h->slot_of_kid, (uint32_t)nk,
+                                                                             h->dict_launches, h->dict_solo);
+    ++h->launches;
+  }
+  const int key_bits = bit_length(nk + nk * nk);
+  const uint32_t shift = key_bits > 12 ? (uint32_t)(key_bits - 12) : 0u;
+  uint32_t splitters[16] = {0};
+  for (int r = 1; r < world; ++r) splitters[r - 1] = edge[r];
+  { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
+  const bool in_place = n_recv <= sample_capacity(h);
+  if (!in_place) KS_ENSURE(h, h->mg_recv, n_recv * 16);
+  unsigned char* recv_base = in_place ? as<unsigned char>(h->samples[0]) : as<unsigned char>(h->mg_recv);
+  const unsigned char* send_base = as<unsigned char>(h->samples[1]);
+  {
+    std::vector<uint64_t> soff(world + 1, 0), roff(world + 1, 0);
+    for (int q = 0; q < world; ++q) { soff[q + 1] = soff[q] + send_cnt[q]; roff[q + 1] = roff[q] + recv_cnt[q]; }
+    if (soff[world] != n_samples_local) return fail(h, KS_ERR_COMM, "ks_mg_build: histogram and sample count disagree");
+    if (send_cnt[rank])
+      KS_CUDA(h, cudaMemcpyAsync(recv_base + roff[rank] * 16, send_base + soff[rank] * 16, send_cnt[rank] * 16, cudaMemcpyDeviceToDevice, h->stream));
+    if (world > 1) {
+      KS_NCCL(h, api->GroupStart());
+      for (int q = 0; q < world; ++q) {
+        if (q == rank) continue;
+        if (send_cnt[q]) KS_NCCL(h, api->Send(send_base + soff[q] * 16, send_cnt[q] * 16, kNcclUint8, q, h->mg_comm, h->stream));
+        if (recv_cnt[q]) KS_NCCL(h, api->Recv(recv_base + roff[q] * 16, recv_cnt[q] * 16, kNcclUint8, q, h->mg_comm, h->stream));
+      }
+      KS_NCCL(h, api->GroupEnd());
+    }
+  }
+  if (!in_place) {  // growing frees both sample sets; the free waits for the sends that still read set 1
+    { int r = ensure_samples(h, n_recv); if (r) return r; }
+    KS_CUDA(h, cudaMemcpyAsync(h->samples[0].p, h->mg_recv.p, n_recv * 16, cudaMemcpyDeviceToDevice, h->stream));
+  }
+
+  // ---- phase 4: K2 + K4 over the received key range; solo times                                 (queued, then wait 3)
+  { int r = mg_reduce_queue(h, n_recv); if (r) return r; }
+  const size_t block4 = (H + (size_t)nk * 8 + 15) & ~(size_t)15;
+  {
+    unsigned char* blk = as<unsigned char>(h->mg_block);
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0);
+    ++h->launches;
+    if (nk) KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+    KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block4, kNcclUint8, h->mg_comm, h->stream));
+  }
+  { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 3
+  { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
+  std::vector<uint64_t> row_off(world + 1, 0);
+  for (int q = 0; q < world; ++q) {
+    const Control& c = mg_head(h, H, q).ctl;
+    row_off[q + 1] = row_off[q] + (c.n_rows > c.ticket2 ? c.n_rows - c.ticket2 : 0u);
+  }
+  const uint64_t rows_total = row_off[world], rows_mine = row_off[rank + 1] - row_off[rank];
+  *h->h_ctl = mg_head(h, H, rank).ctl;
+
+  // ---- phase 5: every key's solo time, this rank's rows straight into their place, the other ranks' rows around them
+  if (nk) {
+    k_solo_merge<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, H, (uint32_t)nk, h->solo_ns);
+    ++h->launches;
+  }
+  KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
+  ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
+  { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine); if (r) return r; }
+  if (world > 1) {
+    KS_NCCL(h, api->GroupStart());
+    for (int q = 0; q < world; ++q) {
+      if (q == rank) continue;
+      const uint64_t rows_q = row_off[q + 1] - row_off[q];
+      if (rows_mine) KS_NCCL(h, api->Send(table + row_off[rank], rows_mine * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+      if (rows_q) KS_NCCL(h, api->Recv(table + row_off[q], rows_q * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+    }
+    KS_NCCL(h, api->GroupEnd());
+  }
+  h->n_key_rows = nk;
+  h->n_pair_rows = rows_total;
+  if (info) {
+    memset(info, 0, sizeof(*info));
+    info->n_records = n_owned;
+    info->n_keys = nk;
+    info->n_solo = n_solo;
+    info->n_pairs = n_samples_local - n_solo;
+    info->n_rows = rows_total;
+    info->max_duration_ns = ctl2.max_dur;
+    info->min_start_ns = ctl2.min_start;
+    info->max_start_ns = ctl2.max_start;
+    info->was_time_ordered = 1;
+  }
+  return (int64_t)rows_total;
+}
+
+}  // extern "C"

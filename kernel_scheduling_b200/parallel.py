@@ -332,6 +332,51 @@ class GpuStages:
         return keys[: self.n_keys * KEY_ROW_DTYPE.itemsize], pairs[: self.n_rows * PAIR_ROW_DTYPE.itemsize]
 
 
+class NativeSession:
+    """One rank of the native build: ``ks_mg_build`` runs the phases AND the five exchanges inside the library (NCCL on the
+    builder's stream, three host waits per table).  The production path on GPUs; ``build_steps`` is the same algorithm
+    with the exchanges in Python, which also runs without NCCL (gloo, in-process).
+
+    Creating a session is collective over the ranks: rank 0 makes the NCCL id, ``torch.distributed`` (any backend) hands
+    it round.  ``world == 1`` needs no process group.
+    """
+
+    def __init__(self, builder, rank: int = 0, world: int = 1, group=None):
+        self.b, self.rank, self.world = builder, rank, world
+        lib = builder._lib
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            r = lib.ks_mg_unique_id(ident)
+            if r < 0:
+                raise _lib.KsError(int(-r), "ks_mg_unique_id: NCCL is not available")
+        if world > 1:
+            import torch.distributed as dist
+
+            box = [ident.raw]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            ident = ctypes.create_string_buffer(box[0], 128)
+        builder._check(lib.ks_mg_comm_init(builder._h, ident, rank, world), "ks_mg_comm_init")
+
+    def build_device(self, records: torch.Tensor, key_type: bool = False) -> int:
+        """Collective.  ``records``: this rank's window as a uint8 CUDA tensor (48 bytes per record, start order), ready on
+        the builder's stream.  Returns the rows of the whole table, which stays on this rank's device (``builder.fetch``)."""
+        if not records.is_cuda or records.dtype != torch.uint8 or records.numel() % 48:
+            raise ValueError("records: a uint8 CUDA tensor of 48-byte records")
+        info = _lib.KsTableInfo()
+        p = ctypes.c_void_p(records.data_ptr()) if records.numel() else None
+        rows = self.b._check(self.b._lib.ks_mg_build(self.b._h, p, records.numel() // 48, _lib.KEY_TYPE if key_type else 0, ctypes.byref(info)), "ks_mg_build")
+        self.b.info = info.as_dict()
+        return rows
+
+    def build(self, records: torch.Tensor, key_type: bool = False, pinned: bool = False):
+        """-> (key_rows, pair_rows) of the whole table as numpy arrays, on every rank."""
+        self.build_device(records, key_type)
+        return self.b.fetch(pinned)
+
+    def close(self):
+        self.b._lib.ks_mg_comm_destroy(self.b._h)
+
+
 def split_windows(n_records: int, world: int) -> list[tuple[int, int]]:
     """Record ranges [lo, hi) of the windows: equal record counts, the remainder to the first windows."""
     base, extra = divmod(n_records, world)

@@ -9,6 +9,7 @@ import torch.distributed as dist
 
 from kernel_scheduling_b200 import parallel, trace
 from kernel_scheduling_b200.pair_table import PairTableBuilder
+from kernel_scheduling_b200.records import pack_records
 
 rank, world, port, out = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
 torch.cuda.set_device(rank)
@@ -20,5 +21,23 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     st = parallel.GpuStages(b, torch.from_numpy(rec[lo:hi].view(np.uint8).reshape(-1).copy()).cuda())
     keys, pairs = parallel.run_distributed(parallel.build_steps(st, rank, world))
     torch.cuda.synchronize()
-np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs)
+    # the same table through the native driver (exchanges inside the library), twice: the second call reuses every buffer
+    session = parallel.NativeSession(b, rank, world)
+    window = torch.from_numpy(rec[lo:hi].view(np.uint8).reshape(-1).copy()).cuda()
+    torch.cuda.synchronize()
+    session.build(window)
+    nkeys, npairs = session.build(window)
+    # a launch that spans every window, type keys
+    n = 4000
+    start = np.arange(n, dtype=np.uint64) * 100 + 1000
+    dur = np.full(n, 60, dtype=np.uint64)
+    tenant = 1 + (np.arange(n) % 2)
+    tenant[3], dur[3] = 0, 100 * n
+    rec2 = pack_records(tenant, np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, np.zeros(n, bool), start, start + dur)
+    lo2, hi2 = parallel.split_windows(n, world)[rank]
+    window2 = torch.from_numpy(rec2[lo2:hi2].view(np.uint8).reshape(-1).copy()).cuda()
+    torch.cuda.synchronize()
+    skeys, spairs = session.build(window2, key_type=True)
+    session.close()
+np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs)
 dist.destroy_process_group()

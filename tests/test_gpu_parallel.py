@@ -77,6 +77,32 @@ def test_two_nccl_ranks(tmp_path):
     assert [p.wait(timeout=300) for p in procs] == [0, 0]
     rec = trace.generate(trace.config("c3", 400_000))
     okeys, opairs = O.build_pair_table(rec)
+    n = 4000
+    start = np.arange(n, dtype=np.uint64) * 100 + 1000
+    dur = np.full(n, 60, dtype=np.uint64)
+    tenant = 1 + (np.arange(n) % 2)
+    tenant[3], dur[3] = 0, 100 * n
+    rec2 = pack_records(tenant, np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, np.zeros(n, bool), start, start + dur)
+    skeys, spairs = O.build_pair_table(rec2, key_mode=O.KEY_TYPE)
     for r in range(2):
         d = np.load(tmp_path / f"rank{r}.npz")
         assert_tables_match(d["keys"], d["pairs"], okeys, opairs)
+        # the native driver: same table, bit for bit the one the Python-driven exchanges gave
+        assert_tables_match(d["nkeys"], d["npairs"], okeys, opairs)
+        assert d["nkeys"].tobytes() == d["keys"].tobytes() and d["npairs"].tobytes() == d["pairs"].tobytes()
+        assert_tables_match(d["skeys"], d["spairs"], skeys, spairs)
+
+
+@pytest.mark.parametrize("cfg,n,key_type", [("c1", 60_000, False), ("c2", 300_000, True), ("c1", 0, False)])
+def test_native_driver_single_rank(cfg, n, key_type):
+    """ks_mg_build with a communicator of one rank: every phase and exchange of the native driver except the halo."""
+    rec = trace.generate(trace.config(cfg, max(n, 4096)))[:n]
+    okeys, opairs = O.build_pair_table(rec, key_mode=O.KEY_TYPE if key_type else O.KEY_SHAPE)
+    with PairTableBuilder(device=0) as b:
+        session = parallel.NativeSession(b)
+        window = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).cuda()
+        torch.cuda.synchronize()
+        for _ in range(2):
+            keys, pairs = session.build(window, key_type=key_type)
+            assert_tables_match(keys, pairs, okeys, opairs)
+        session.close()
