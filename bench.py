@@ -220,7 +220,11 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     launches = builder.launch_count - launches0
+    phase_ms = None
     if world > 1:
+        # device time of the five phases of the sharded build (each with its exchange), as the library measured them
+        phase_ms = {k: v / args.steps for k, v in stage_ms.items() if v}
+        stage_ms = {k: 0.0 for k in stage_names}
         # per-kernel times for the roofline: the same kernels over the local window alone, after the timed region
         for i in range(4):  # the first call after the sharded runs has no size hints from a previous call: not counted
             builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
@@ -308,6 +312,7 @@ def main():
             "clocks": clocks,
             "gpu_launches": int(launches),
             "stage_ms": per_stage,
+            **({"phase_ms": phase_ms} if phase_ms else {}),
             "roofline": {"bound": "hbm", "kernel": dom_name,
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": dom_traffic, "peak_source": peak_src,
                          "path_algorithmic_bytes": path_bytes, "path_frac": path_bytes / (ms_per_step * 1e-3) / 1e9 / peak},

@@ -201,6 +201,9 @@ int64_t ks_mg_finalize(ks_handle* h);                                           
  *   ks_mg_build         collective: records = this rank's window (DEVICE pointer, start order, 16-byte aligned).  Returns
  *                       the rows of the WHOLE table, which every rank then holds (ks_copy_pair_rows / ks_copy_key_rows);
  *                       queued on the handle's stream, the copies are ordered behind it.  flags: KS_KEY_TYPE or 0.
+ *                       info (optional, costs one more host wait): this rank's counts and the device time of the five
+ *                       phases, each with its exchange: ms_decode, ms_join, ms_order (partition + sample exchange),
+ *                       ms_reduce (K2 + K4), ms_finalize.
  *                       Errors found on the device (bad record, order, capacity) are returned by ALL ranks alike; an
  *                       argument, CUDA or NCCL failure is local to its rank and fatal for the job.
  *   ks_mg_comm_destroy  releases the communicator and the exchange buffers (ks_destroy does it too) */
@@ -208,6 +211,13 @@ int ks_mg_unique_id(void* id128);
 int ks_mg_comm_init(ks_handle* h, const void* id128, int rank, int world);
 int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags, ks_table_info* info);
 int ks_mg_comm_destroy(ks_handle* h);
+/* The two bulk exchanges of ks_mg_build (samples to their key range's owner; table shards to everyone) go through PEER
+ * MEMORY when every rank can map every other rank's buffers (CUDA IPC, decided once in ks_mg_comm_init; KS_MG_NO_P2P in
+ * the environment of any rank turns it off): the partition kernel and the finalize kernel store straight into the other
+ * GPUs' buffers over NVLink, and a 16-byte all-gather orders the stores before the readers.  Otherwise they are NCCL
+ * send/recv pairs.  Returns 1 for peer memory, 0 for NCCL.  ks_mg_comm_destroy is collective in peer-memory mode (every
+ * rank unmaps before any rank frees). */
+int ks_mg_peer_memory(ks_handle* h);
 
 /* ---- the agent's timing log (text) -> launch records, on the device.  Replaces the pandas read of the 17-column TSV the
  * agent writes (scheduler/agent.cpp:692-705; read at scheduler/postprocess.py:12-13).  Rows without end_ns (no completion

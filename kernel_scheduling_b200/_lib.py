@@ -83,6 +83,7 @@ KS_API = [
     ("ks_mg_comm_init", [c_void_p, c_void_p, c_int, c_int], c_int),
     ("ks_mg_build", [c_void_p, c_void_p, c_uint64, c_uint32, POINTER(KsTableInfo)], c_int64),
     ("ks_mg_comm_destroy", [c_void_p], c_int),
+    ("ks_mg_peer_memory", [c_void_p], c_int),
     ("ks_tsv_parse", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_tsv_dictionary", [c_void_p, c_int, c_void_p, c_void_p], c_int64),
     ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),

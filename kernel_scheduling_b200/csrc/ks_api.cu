@@ -60,6 +60,7 @@ struct ks_handle {
 
   // results of the last ks_build_table
   uint64_t n_pair_rows = 0, n_key_rows = 0;
+  const void* pair_rows_src = nullptr;  // where the last build left its pair rows (ks_copy_pair_rows reads here)
   uint64_t launches = 0;  // kernels launched so far (cumulative)
 
   // multi-GPU session state (ks_mg_*)
@@ -73,6 +74,13 @@ struct ks_handle {
   int mg_rank = 0, mg_world = 1;
   uint32_t mg_key_cap = 4096;  // keys per rank that fit the first exchange; grows on every rank alike
   DevBuf mg_block, mg_gathered, mg_recv;
+  // peer memory (one process per GPU, buffers shared through CUDA IPC): the sample exchange and the table exchange become
+  // plain stores into the other ranks' buffers from the kernels that produce the data
+  bool mg_p2p = false;
+  struct Exported { void* p = nullptr; size_t cap = 0; unsigned long long gen = 0; cudaIpcMemHandle_t handle{}; } mg_recv_x, mg_table_x;
+  struct Imported { void* p = nullptr; unsigned long long gen = 0; } mg_peer_recv[16], mg_peer_table[16];
+  std::vector<void*> mg_retired;  // exported buffers that were replaced by larger ones: freed when the session ends
+  unsigned char* mg_bar = nullptr;  // device: 16 bytes to send, 16 per rank to receive (the barrier behind peer stores)
   uint32_t* mg_counts = nullptr;        // device: [0] launches in the tail, [1] launches in the halo
   unsigned char* mg_host = nullptr;     // pinned: the headers (and histograms) of all ranks
   size_t mg_host_cap = 0;
@@ -197,7 +205,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 
 // K2 driver for the 16-byte sample stream: sorts set 0/1 of h->samples on key bits [0, end_bit); returns the set that
 // holds the result.
-int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr) {
+int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr) {
   constexpr int ITEMS = 8;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
@@ -212,7 +220,9 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
   uint32_t* gbase = hist + 8 * 256;
   KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
   const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
-  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(as<uint32_t>(h->samples[0]), 4u, n_dev, (uint32_t)n, 0, end_bit, hist);
+  // first_in: the unsorted items live outside the two sets (a receive buffer); the first pass reads them from there
+  const uint4* src0 = first_in ? first_in : as<uint4>(h->samples[0]);
+  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(reinterpret_cast<const uint32_t*>(src0), 4u, n_dev, (uint32_t)n, 0, end_bit, hist);
   k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
   constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
@@ -225,7 +235,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
   for (int p = 0; p < passes; ++p) {
     KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
     SortPass16Args a{};
-    a.in = as<uint4>(h->samples[cur]);
+    a.in = p == 0 ? src0 : as<uint4>(h->samples[cur]);
     a.out = as<uint4>(h->samples[cur ^ 1]);
     a.n_dev = n_dev;
     a.n = (uint32_t)n;
@@ -716,6 +726,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   const Control& c = *h->h_ctl;
   h->n_key_rows = c.n_keys;
   h->n_pair_rows = c.n_rows - c.ticket2;
+  h->pair_rows_src = h->pair_rows.p;
   if (info) {
     std::memset(info, 0, sizeof(*info));
     info->n_records = n;
@@ -744,7 +755,7 @@ int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows
   if (!h || (!dst && h->n_pair_rows)) return -KS_ERR_ARG;
   if (capacity_rows < h->n_pair_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_pair_rows: buffer too small");
   KS_CUDA(h, cudaSetDevice(h->device));
-  { int r = copy_out(h, dst, h->pair_rows.p, h->n_pair_rows * sizeof(ks_pair_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
+  { int r = copy_out(h, dst, h->pair_rows_src, h->n_pair_rows * sizeof(ks_pair_row), (flags & KS_ON_DEVICE) != 0); if (r) return r; }
   if (!(flags & KS_ON_DEVICE)) KS_CUDA(h, cudaStreamSynchronize(h->stream));  // device destinations are ordered by the stream
   return (int64_t)h->n_pair_rows;
 }
@@ -1025,7 +1036,7 @@ int mg_status(ks_handle* h, const char* what) {
 
 // K2 + K4 over the n samples in sample set 0 (this rank's key range), then the solo times of the keys reduced here.
 // Queues only; the caller reads the control words back.
-int mg_reduce_queue(ks_handle* h, uint64_t n) {
+int mg_reduce_queue(ks_handle* h, uint64_t n, const uint4* first_in = nullptr) {
   // counters of the row / statistics kernels start from zero
   { int r = mg_zero_u32(h, &h->d_ctl->n_rows, 2); if (r) return r; }
   { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
@@ -1033,7 +1044,7 @@ int mg_reduce_queue(ks_handle* h, uint64_t n) {
   KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
   KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
   const uint64_t nk = h->mg_nk;
-  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk));
+  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk), nullptr, first_in);
   if (cur < 0) return cur;
   h->mg_cur = cur;
   h->mg_n_samples = n;
@@ -1047,7 +1058,7 @@ int mg_reduce_queue(ks_handle* h, uint64_t n) {
 }
 
 // key rows of every key and the pair rows of this rank's range (written to `out`, room for max_rows)
-int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows) {
+int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows, uint32_t n_peers = 0, ks_pair_row* const* peers = nullptr) {
   const uint64_t nk = h->mg_nk;
   FinalArgs f{};
   f.stats = as<RowStats>(h->stats);
@@ -1065,6 +1076,8 @@ int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows) {
   f.pair_rows = out;
   f.max_pair_rows = max_rows;
   f.ctl = h->d_ctl;
+  f.n_peer_tables = n_peers;
+  for (uint32_t q = 0; q < n_peers; ++q) f.peer_rows[q] = peers[q];
   if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
   k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
   h->launches += nk ? 2 : 1;
@@ -1305,6 +1318,7 @@ int64_t ks_mg_finalize(ks_handle* h) {
   // no host round trip: the counts are known since ks_mg_reduce read them back
   h->n_key_rows = nk;
   h->n_pair_rows = h->h_ctl->n_rows - h->h_ctl->ticket2;
+  h->pair_rows_src = h->pair_rows.p;
   return (int64_t)h->n_pair_rows;
 }
 

@@ -141,11 +141,20 @@ struct MgHeader {
   uint32_t reserved0;
   unsigned long long capacity;     // sample capacity of the sender (block 2): n_pairs above it means "grow and repeat"
   unsigned long long first_start;  // start_ns of the sender's first record
-  unsigned char pad[256 - sizeof(Control) - 24];
+  // peer-memory mode: the buffer the other ranks store into next (block 2: the sample receive buffer, block 4: the table)
+  unsigned char ipc[64];           // cudaIpcMemHandle_t
+  unsigned long long buf_gen;      // changes whenever the sender replaced the buffer
+  unsigned long long buf_cap;      // its size in bytes
+  unsigned char pad[256 - sizeof(Control) - 24 - 64 - 16];
+};
+struct MgIpc {
+  unsigned char handle[64];
+  unsigned long long gen, cap;
 };
 static_assert(sizeof(MgHeader) == 256, "exchange header is 256 bytes");
 
-__global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n_tail, const unsigned char* records, uint64_t n_owned, uint64_t capacity) {
+__global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n_tail, const unsigned char* records, uint64_t n_owned, uint64_t capacity,
+                            const MgIpc ipc) {
   const uint32_t t = threadIdx.x;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(ctl);
   uint32_t* dst = reinterpret_cast<uint32_t*>(&out->ctl);
@@ -155,7 +164,10 @@ __global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n
     out->reserved0 = 0;
     out->capacity = capacity;
     out->first_start = n_owned ? *reinterpret_cast<const unsigned long long*>(records + 32) : 0ull;
+    out->buf_gen = ipc.gen;
+    out->buf_cap = ipc.cap;
   }
+  if (t < 16) reinterpret_cast<uint32_t*>(out->ipc)[t] = reinterpret_cast<const uint32_t*>(ipc.handle)[t];
 }
 
 // k_gather_records with the count on the device

@@ -77,7 +77,21 @@ NcclApi* nccl_api() {
     if (e__ != 0) return fail((h), KS_ERR_COMM, std::string(#call) + ": " + nccl_api()->GetErrorString(e__));         \
   } while (0)
 
+void mg_close_imports(ks_handle* h);
+void mg_free_exports(ks_handle* h);
+
+// not collective (ks_destroy must never wait for another rank): mappings of the other ranks' buffers are closed, then the
+// own buffers are freed.  ks_mg_comm_destroy is the orderly, collective way (all mappings closed before any buffer goes).
 void mg_native_release(ks_handle* h) {
+  if (h->pair_rows_src && h->pair_rows_src != h->pair_rows.p) {  // the last table lives in an exported buffer
+    h->pair_rows_src = nullptr;
+    h->n_pair_rows = 0;
+  }
+  mg_close_imports(h);
+  mg_free_exports(h);
+  if (h->mg_bar) cudaFree(h->mg_bar);
+  h->mg_bar = nullptr;
+  h->mg_p2p = false;
   if (h->mg_comm) {
     nccl_api()->CommDestroy(h->mg_comm);
     h->mg_comm = nullptr;
@@ -92,6 +106,98 @@ void mg_native_release(ks_handle* h) {
   if (h->mg_host) cudaFreeHost(h->mg_host);
   h->mg_host = nullptr;
   h->mg_host_cap = 0;
+}
+
+// KS_MG_TRACE=1 in the environment: rank 0 prints the device time between the driver's steps of every call to stderr
+struct MgTrace {
+  bool on = false;
+  cudaStream_t stream = nullptr;
+  std::vector<std::pair<const char*, cudaEvent_t>> marks;
+  void mark(const char* name) {
+    if (!on) return;
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, stream);
+    marks.emplace_back(name, e);
+  }
+  void report() {
+    if (!on) return;
+    cudaStreamSynchronize(stream);
+    std::string line = "ks_mg_build trace (ms):";
+    for (size_t i = 1; i < marks.size(); ++i) {
+      char buf[96];
+      snprintf(buf, sizeof(buf), " %s=%.3f", marks[i].first, ev_ms(marks[i - 1].second, marks[i].second));
+      line += buf;
+    }
+    fprintf(stderr, "%s\n", line.c_str());
+    for (auto& m : marks) cudaEventDestroy(m.second);
+    marks.clear();
+  }
+};
+
+// An exported buffer of at least `bytes`.  A larger one REPLACES it; the old one is retired, not freed: other ranks may
+// still have it mapped, and exported memory must outlive its mappings.  Retired buffers are freed when the session ends.
+int mg_export_ensure(ks_handle* h, ks_handle::Exported& x, size_t bytes) {
+  if (bytes <= x.cap) return 0;
+  if (x.p) h->mg_retired.push_back(x.p);
+  x.p = nullptr;
+  x.cap = 0;
+  const size_t want = (bytes + ((size_t)1 << 21) - 1) & ~(((size_t)1 << 21) - 1);
+  cudaError_t e = cudaMalloc(&x.p, want);
+  if (e != cudaSuccess) return fail(h, KS_ERR_CUDA, "cudaMalloc of " + std::to_string(want) + " bytes: " + cudaGetErrorString(e));
+  x.cap = want;
+  ++x.gen;
+  if (h->mg_p2p) KS_CUDA(h, cudaIpcGetMemHandle(&x.handle, x.p));
+  return 0;
+}
+
+MgIpc mg_ipc_of(const ks_handle::Exported& x) {
+  MgIpc m{};
+  static_assert(sizeof(cudaIpcMemHandle_t) == sizeof(m.handle), "IPC handle is 64 bytes");
+  memcpy(m.handle, &x.handle, sizeof(m.handle));
+  m.gen = x.gen;
+  m.cap = x.cap;
+  return m;
+}
+
+// maps the buffer a header advertises (again, if its sender replaced it since the last call)
+int mg_import(ks_handle* h, ks_handle::Imported& im, const MgHeader& hd) {
+  if (im.p && im.gen == hd.buf_gen) return 0;
+  if (im.p) {
+    KS_CUDA(h, cudaIpcCloseMemHandle(im.p));
+    im.p = nullptr;
+  }
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, hd.ipc, sizeof(handle));
+  KS_CUDA(h, cudaIpcOpenMemHandle(&im.p, handle, cudaIpcMemLazyEnablePeerAccess));
+  im.gen = hd.buf_gen;
+  return 0;
+}
+
+// Stores into peer memory become visible to the peer's later kernels through this: every rank's collective kernel is
+// ordered behind its own storing kernel on its stream, and completes only after every rank has entered it.
+int mg_barrier(ks_handle* h) {
+  KS_NCCL(h, nccl_api()->AllGather(h->mg_bar, h->mg_bar + 16, 16, kNcclUint8, h->mg_comm, h->stream));
+  return 0;
+}
+
+void mg_close_imports(ks_handle* h) {
+  for (auto* set : {h->mg_peer_recv, h->mg_peer_table})
+    for (int q = 0; q < 16; ++q) {
+      if (set[q].p) cudaIpcCloseMemHandle(set[q].p);
+      set[q].p = nullptr;
+      set[q].gen = 0;
+    }
+}
+
+void mg_free_exports(ks_handle* h) {
+  for (auto* x : {&h->mg_recv_x, &h->mg_table_x}) {
+    if (x->p) cudaFree(x->p);
+    x->p = nullptr;
+    x->cap = 0;
+  }
+  for (void* p : h->mg_retired) cudaFree(p);
+  h->mg_retired.clear();
 }
 
 constexpr size_t kMgTailBytes = (size_t)kHaloMax * 48;
@@ -123,6 +229,41 @@ int mg_any_error(ks_handle* h, size_t width, const char* where) {
   return 0;
 }
 
+// the partition pass of ks_mg_partition with the destinations in peer memory: no separate count (the host knows every
+// count from the exchanged histograms), one pass over the samples
+int mg_partition_to_peers(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, uint4* const* dest) {
+  const uint64_t n = h->mg_n_samples;
+  if (!n) return 0;
+  constexpr int ITEMS = 8;
+  constexpr int THREADS = kSort16Threads;
+  constexpr int TILE = THREADS * ITEMS;
+  const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
+  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  KS_ENSURE(h, h->lookback, lb_bytes);
+  KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+  SortPass16Args a{};
+  a.by_dest = 2;
+  a.n_split = n_ranks - 1;
+  a.split_shift = shift;
+  for (uint32_t i = 0; i + 1 < n_ranks; ++i) a.split[i] = splitters[i];
+  for (uint32_t d = 0; d < n_ranks; ++d) a.dest[d] = dest[d];
+  a.in = as<uint4>(h->samples[0]);
+  a.out = nullptr;
+  a.n = (uint32_t)n;
+  a.shift = 0;
+  a.bits = 8;
+  a.gbase = nullptr;
+  a.lookback = as<uint32_t>(h->lookback);
+  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+  a.err = &h->d_ctl->err;
+  constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
+  KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * (1024 / THREADS)), THREADS, smem, h->stream>>>(a);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -150,13 +291,65 @@ int ks_mg_comm_init(ks_handle* h, const void* id128, int rank, int world) {
   h->mg_rank = rank;
   h->mg_world = world;
   if (!h->mg_counts) KS_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->mg_counts), 16));
+  if (!h->mg_bar) {
+    KS_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->mg_bar), 16 * 17));
+    KS_CUDA(h, cudaMemset(h->mg_bar, 0, 16 * 17));
+  }
+  // Peer memory or NCCL for the two bulk exchanges?  Every rank exports a probe buffer and tries to map all the others;
+  // the mode is peer memory only if every rank could (KS_MG_NO_P2P in the environment of ANY rank votes no).
+  h->mg_p2p = false;
+  if (world > 1) {
+    constexpr size_t H = sizeof(MgHeader);
+    KS_ENSURE(h, h->mg_block, H);
+    KS_ENSURE(h, h->mg_gathered, H * (size_t)world);
+    ks_handle::Exported probe;
+    h->mg_p2p = true;  // so that the probe gets a handle
+    int vote = getenv("KS_MG_NO_P2P") ? 0 : 1;
+    if (mg_export_ensure(h, probe, 4096)) { vote = 0; cudaGetLastError(); }
+    h->mg_p2p = false;
+    auto exchange = [&](uint64_t word) -> int {
+      k_mg_header<<<1, 32, 0, h->stream>>>(as<MgHeader>(h->mg_block), h->d_ctl, nullptr, nullptr, 0, word, mg_ipc_of(probe));
+      KS_NCCL(h, api->AllGather(h->mg_block.p, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));
+      return mg_fetch_heads(h, H, H);
+    };
+    { int r = exchange((uint64_t)vote); if (r) return r; }
+    void* mapped[16] = {nullptr};
+    for (int q = 0; q < world; ++q) {
+      const MgHeader& hd = mg_head(h, H, q);
+      if (hd.capacity != 1) vote = 0;
+      if (q == rank || !vote || hd.capacity != 1) continue;
+      cudaIpcMemHandle_t handle;
+      memcpy(&handle, hd.ipc, sizeof(handle));
+      if (cudaIpcOpenMemHandle(&mapped[q], handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        mapped[q] = nullptr;
+        vote = 0;
+        cudaGetLastError();  // not an error of the handle: this pair of devices just stays on NCCL
+      }
+    }
+    { int r = exchange((uint64_t)vote); if (r) return r; }
+    bool all = true;
+    for (int q = 0; q < world; ++q) all = all && mg_head(h, H, q).capacity == 1;
+    for (int q = 0; q < world; ++q)
+      if (mapped[q]) cudaIpcCloseMemHandle(mapped[q]);
+    { int r = exchange(0); if (r) return r; }  // every rank has closed its mappings: the probes can go
+    if (probe.p) cudaFree(probe.p);
+    h->mg_p2p = all;
+  }
   return KS_OK;
 }
+
+/* 1 if the two bulk exchanges of ks_mg_build go through peer memory (stores over NVLink from the producing kernels),
+ * 0 if they go through NCCL send/recv */
+int ks_mg_peer_memory(ks_handle* h) { return h && h->mg_p2p ? 1 : 0; }
 
 int ks_mg_comm_destroy(ks_handle* h) {
   if (!h) return -KS_ERR_ARG;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
+  if (h->mg_comm && h->mg_p2p && h->mg_world > 1) {  // collective: all mappings are closed before any exported buffer is freed
+    mg_close_imports(h);
+    if (mg_barrier(h) == 0) cudaStreamSynchronize(h->stream);
+  }
   mg_native_release(h);
   return KS_OK;
 }
@@ -169,7 +362,13 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   const unsigned char* rec = reinterpret_cast<const unsigned char*>(records);
   constexpr size_t H = sizeof(MgHeader);
 
+  MgTrace tr;
+  tr.on = rank == 0 && getenv("KS_MG_TRACE") != nullptr;
+  tr.stream = h->stream;
+  tr.mark("start");
+  cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only when info is asked for)
   // ---- phase 1: K1 over the window, its tail, its distinct keys                                 (queued, no wait)
+  cudaEventRecord(ev[0], h->stream);
   { int64_t r = ks_mg_begin(h, records, n_owned, flags); if (r < 0) return r; }
   KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
   uint32_t* tail_idx = as<uint32_t>(h->tmp[0]);
@@ -185,6 +384,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   d.slot_of_kid = h->slot_of_kid; d.keys_sorted = h->keys_sorted; d.ctl = h->d_ctl;
   k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
   ++h->launches;
+  tr.mark("decode+tail+compact");
 
   // blocks 2 and 4 at their largest, so that the exchange buffers are sized once per key capacity
   const size_t block_other = std::max(H + kMgHistBytes + (size_t)kMaxKeys * 16, H + (size_t)kMaxKeys * 8);
@@ -198,7 +398,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     KS_ENSURE(h, h->mg_block, std::max(block1, block_other));
     KS_ENSURE(h, h->mg_gathered, std::max(block1, block_other) * (size_t)world);
     unsigned char* blk = as<unsigned char>(h->mg_block);
-    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, 0);
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, 0, MgIpc{});
     if (n_owned)
       k_gather_records_dev<<<(kHaloMax * 3 + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const uint4*>(rec), tail_idx, h->mg_counts, kHaloMax,
                                                                               reinterpret_cast<uint4*>(blk + H));
@@ -206,7 +406,9 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
                                                                 reinterpret_cast<uint4*>(blk + off_words));
     h->launches += n_owned ? 3 : 2;
     KS_CUDA(h, cudaGetLastError());
+    tr.mark("pack1");
     KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block1, kNcclUint8, h->mg_comm, h->stream));
+    tr.mark("allgather1");
     { int r = mg_fetch_heads(h, block1, H); if (r) return r; }                                         // ---- wait 1
     { int r = mg_any_error(h, H, "decode"); if (r) return r; }
     uint32_t need = 0;
@@ -225,6 +427,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   }
 
   // ---- phase 2: global key ids, halo, samples, histogram + launch counts                        (queued, no wait)
+  cudaEventRecord(ev[1], h->stream);
   unsigned char* gathered = as<unsigned char>(h->mg_gathered);
   for (int q = 0; q < world; ++q) {
     const uint32_t nq = mg_head(h, H, q).ctl.n_keys;
@@ -252,6 +455,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     k_halo_place<<<1, 1024, 0, h->stream>>>(ha);
     ++h->launches;
   }
+  tr.mark("wait1+dict+halo");
   h->mg_n_halo = kHaloMax;  // the join always sees all halo slots (unused ones are inert)
   const uint32_t cap2 = (uint32_t)std::min<uint64_t>(key_sum, kMaxKeys);  // the global key count is at most the sum
   const size_t off_launches = H + kMgHistBytes, off_solo = off_launches + (size_t)cap2 * 8;
@@ -263,6 +467,8 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     int r = ensure_samples(h, cap_s);
     if (r) return r;
   }
+  const bool p2p = h->mg_p2p && world > 1;
+  if (p2p) { int r = mg_export_ensure(h, h->mg_recv_x, cap_s * 16); if (r) return r; }
   const size_t width2 = H + kMgHistBytes;
   for (int attempt = 0;; ++attempt) {
     unsigned char* blk = as<unsigned char>(h->mg_block);
@@ -279,11 +485,14 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     s.ctl = h->d_ctl;
     k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
     { int r = run_join(h, 0, n_tl, cap_s, nullptr, nullptr, 0, kHaloMax); if (r) return r; }
+    tr.mark("samples+join");
     k_key_hist_dev<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
-    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s);
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
     h->launches += cap2 ? 4 : 3;
     KS_CUDA(h, cudaGetLastError());
+    tr.mark("hist+pack2");
     KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block2, kNcclUint8, h->mg_comm, h->stream));
+    tr.mark("allgather2");
     { int r = mg_fetch_heads(h, block2, width2); if (r) return r; }                                    // ---- wait 2
     { int r = mg_any_error(h, width2, "join"); if (r) return r; }
     bool any_over = false;
@@ -312,6 +521,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   const uint64_t n_solo = ctl2.n_solo, n_samples_local = ctl2.n_pairs;
 
   // ---- phase 3: splitters, partition, the samples travel                                        (queued, no wait)
+  cudaEventRecord(ev[2], h->stream);
   std::vector<uint64_t> total(kKeyHistBins, 0);
   auto hist_of = [&](int q) { return reinterpret_cast<const uint64_t*>(h->mg_host + width2 * (size_t)q + H); };
   for (int q = 0; q < world; ++q)
@@ -352,15 +562,57 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   const uint32_t shift = key_bits > 12 ? (uint32_t)(key_bits - 12) : 0u;
   uint32_t splitters[16] = {0};
   for (int r = 1; r < world; ++r) splitters[r - 1] = edge[r];
-  { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
-  const bool in_place = n_recv <= sample_capacity(h);
-  if (!in_place) KS_ENSURE(h, h->mg_recv, n_recv * 16);
-  unsigned char* recv_base = in_place ? as<unsigned char>(h->samples[0]) : as<unsigned char>(h->mg_recv);
-  const unsigned char* send_base = as<unsigned char>(h->samples[1]);
-  {
-    std::vector<uint64_t> soff(world + 1, 0), roff(world + 1, 0);
-    for (int q = 0; q < world; ++q) { soff[q + 1] = soff[q] + send_cnt[q]; roff[q + 1] = roff[q] + recv_cnt[q]; }
-    if (soff[world] != n_samples_local) return fail(h, KS_ERR_COMM, "ks_mg_build: histogram and sample count disagree");
+  std::vector<uint64_t> soff(world + 1, 0), roff(world + 1, 0);
+  for (int q = 0; q < world; ++q) { soff[q + 1] = soff[q] + send_cnt[q]; roff[q + 1] = roff[q] + recv_cnt[q]; }
+  if (soff[world] != n_samples_local) return fail(h, KS_ERR_COMM, "ks_mg_build: histogram and sample count disagree");
+  const uint4* sort_input = nullptr;  // null: sample set 0
+  if (p2p) {
+    // -- peer memory: the partition pass stores every item straight into its place in the destination's receive buffer
+    // where my items start in rank d's buffer: behind those of the ranks in front of me
+    uint64_t my_off_at[16] = {0};
+    bool grow = false;
+    for (int d = 0; d < world; ++d) {
+      uint64_t in = 0;
+      for (int q = 0; q < world; ++q) {
+        if (q == rank) my_off_at[d] = in;
+        in += range_sum(q, d);
+      }
+      if (in * 16 > mg_head(h, width2, d).buf_cap) grow = true;  // rank d's buffer is too small: decided alike everywhere
+    }
+    if (grow) {
+      if (n_recv * 16 > h->mg_recv_x.cap) { int r = mg_export_ensure(h, h->mg_recv_x, n_recv * 16 + n_recv * 4); if (r) return r; }
+      unsigned char* blk = as<unsigned char>(h->mg_block);
+      k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
+      ++h->launches;
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));  // behind k_counts_sum_import, which read the old blocks
+      { int r = mg_fetch_heads(h, H, H); if (r) return r; }
+    }
+    const size_t wh = grow ? H : width2;  // layout of the pinned header copies
+    uint4* dest[16] = {nullptr};
+    for (int d = 0; d < world; ++d) {
+      unsigned char* base = nullptr;
+      if (d == rank) {
+        base = reinterpret_cast<unsigned char*>(h->mg_recv_x.p);
+      } else {
+        { int r = mg_import(h, h->mg_peer_recv[d], mg_head(h, wh, d)); if (r) return r; }
+        base = reinterpret_cast<unsigned char*>(h->mg_peer_recv[d].p);
+      }
+      dest[d] = reinterpret_cast<uint4*>(base + my_off_at[d] * 16);
+    }
+    { int r = mg_partition_to_peers(h, splitters, shift, (uint32_t)world, dest); if (r) return r; }
+    tr.mark("wait2+partition to peers");
+    { int r = mg_barrier(h); if (r) return r; }
+    tr.mark("barrier");
+    sort_input = reinterpret_cast<const uint4*>(h->mg_recv_x.p);
+    if (sample_capacity(h) < n_recv) { int r = ensure_samples(h, n_recv); if (r) return r; }  // the sort's two sets
+  } else {
+    // -- NCCL: partition into sample set 1, one send/recv pair per peer with exact sizes, own part by a local copy
+    { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
+    tr.mark("wait2+partition");
+    const bool in_place = n_recv <= sample_capacity(h);
+    if (!in_place) KS_ENSURE(h, h->mg_recv, n_recv * 16);
+    unsigned char* recv_base = in_place ? as<unsigned char>(h->samples[0]) : as<unsigned char>(h->mg_recv);
+    const unsigned char* send_base = as<unsigned char>(h->samples[1]);
     if (send_cnt[rank])
       KS_CUDA(h, cudaMemcpyAsync(recv_base + roff[rank] * 16, send_base + soff[rank] * 16, send_cnt[rank] * 16, cudaMemcpyDeviceToDevice, h->stream));
     if (world > 1) {
@@ -372,22 +624,27 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
       }
       KS_NCCL(h, api->GroupEnd());
     }
-  }
-  if (!in_place) {  // growing frees both sample sets; the free waits for the sends that still read set 1
-    { int r = ensure_samples(h, n_recv); if (r) return r; }
-    KS_CUDA(h, cudaMemcpyAsync(h->samples[0].p, h->mg_recv.p, n_recv * 16, cudaMemcpyDeviceToDevice, h->stream));
+    tr.mark("sample exchange");
+    if (!in_place) {  // growing frees both sample sets; the free waits for the sends that still read set 1
+      { int r = ensure_samples(h, n_recv); if (r) return r; }
+      KS_CUDA(h, cudaMemcpyAsync(h->samples[0].p, h->mg_recv.p, n_recv * 16, cudaMemcpyDeviceToDevice, h->stream));
+    }
   }
 
   // ---- phase 4: K2 + K4 over the received key range; solo times                                 (queued, then wait 3)
-  { int r = mg_reduce_queue(h, n_recv); if (r) return r; }
+  cudaEventRecord(ev[3], h->stream);
+  { int r = mg_reduce_queue(h, n_recv, sort_input); if (r) return r; }
+  tr.mark("sort+stats");
+  if (p2p) { int r = mg_export_ensure(h, h->mg_table_x, std::max<size_t>(h->mg_table_x.cap, (size_t)8 << 20)); if (r) return r; }
   const size_t block4 = (H + (size_t)nk * 8 + 15) & ~(size_t)15;
   {
     unsigned char* blk = as<unsigned char>(h->mg_block);
-    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0);
+    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
     ++h->launches;
     if (nk) KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
     KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block4, kNcclUint8, h->mg_comm, h->stream));
   }
+  tr.mark("allgather4");
   { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 3
   { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
   std::vector<uint64_t> row_off(world + 1, 0);
@@ -399,23 +656,56 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   *h->h_ctl = mg_head(h, H, rank).ctl;
 
   // ---- phase 5: every key's solo time, this rank's rows straight into their place, the other ranks' rows around them
+  cudaEventRecord(ev[4], h->stream);
   if (nk) {
     k_solo_merge<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, H, (uint32_t)nk, h->solo_ns);
     ++h->launches;
   }
-  KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
-  ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
-  { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine); if (r) return r; }
-  if (world > 1) {
-    KS_NCCL(h, api->GroupStart());
+  if (p2p) {
+    // -- peer memory: the finalize kernel stores this rank's rows into every rank's copy of the table
+    const size_t table_bytes = std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row);
+    bool grow = false;
+    for (int q = 0; q < world; ++q) grow = grow || table_bytes > mg_head(h, H, q).buf_cap;
+    if (grow) {
+      if (table_bytes > h->mg_table_x.cap) { int r = mg_export_ensure(h, h->mg_table_x, table_bytes + table_bytes / 4); if (r) return r; }
+      unsigned char* blk = as<unsigned char>(h->mg_block);
+      k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
+      ++h->launches;
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));  // behind k_solo_merge, which read the old blocks
+      { int r = mg_fetch_heads(h, H, H); if (r) return r; }
+    }
+    ks_pair_row* peers[15];
+    uint32_t n_peers = 0;
     for (int q = 0; q < world; ++q) {
       if (q == rank) continue;
-      const uint64_t rows_q = row_off[q + 1] - row_off[q];
-      if (rows_mine) KS_NCCL(h, api->Send(table + row_off[rank], rows_mine * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
-      if (rows_q) KS_NCCL(h, api->Recv(table + row_off[q], rows_q * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+      { int r = mg_import(h, h->mg_peer_table[q], mg_head(h, H, q)); if (r) return r; }
+      peers[n_peers++] = reinterpret_cast<ks_pair_row*>(h->mg_peer_table[q].p) + row_off[rank];
     }
-    KS_NCCL(h, api->GroupEnd());
+    ks_pair_row* table = reinterpret_cast<ks_pair_row*>(h->mg_table_x.p);
+    { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine, n_peers, peers); if (r) return r; }
+    tr.mark("wait3+finalize to peers");
+    { int r = mg_barrier(h); if (r) return r; }
+    tr.mark("barrier");
+    h->pair_rows_src = table;
+  } else {
+    KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
+    ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
+    { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine); if (r) return r; }
+    tr.mark("wait3+finalize");
+    if (world > 1) {
+      KS_NCCL(h, api->GroupStart());
+      for (int q = 0; q < world; ++q) {
+        if (q == rank) continue;
+        const uint64_t rows_q = row_off[q + 1] - row_off[q];
+        if (rows_mine) KS_NCCL(h, api->Send(table + row_off[rank], rows_mine * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+        if (rows_q) KS_NCCL(h, api->Recv(table + row_off[q], rows_q * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+      }
+      KS_NCCL(h, api->GroupEnd());
+    }
+    tr.mark("shard exchange");
+    h->pair_rows_src = table;
   }
+  tr.report();
   h->n_key_rows = nk;
   h->n_pair_rows = rows_total;
   if (info) {
@@ -429,6 +719,15 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     info->min_start_ns = ctl2.min_start;
     info->max_start_ns = ctl2.max_start;
     info->was_time_ordered = 1;
+    // device time of the five phases, each up to and including its exchange (asking for info costs one more wait)
+    cudaEventRecord(ev[5], h->stream);
+    KS_CUDA(h, cudaStreamSynchronize(h->stream));
+    info->ms_decode = ev_ms(ev[0], ev[1]);
+    info->ms_join = ev_ms(ev[1], ev[2]);
+    info->ms_order = ev_ms(ev[2], ev[3]);   // partition by key range + the sample exchange
+    info->ms_reduce = ev_ms(ev[3], ev[4]);  // K2 + K4
+    info->ms_finalize = ev_ms(ev[4], ev[5]);
+    info->ms_total = ev_ms(ev[0], ev[5]);
   }
   return (int64_t)rows_total;
 }

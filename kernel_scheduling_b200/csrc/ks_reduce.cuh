@@ -157,6 +157,10 @@ struct FinalArgs {
   ks_pair_row* pair_rows; // [max_pair_rows]
   uint32_t max_pair_rows;
   Control* ctl;
+  // multi-GPU, peer memory: the rows are ALSO written to the same place in these tables (the other ranks' copies of the
+  // whole table, plain stores over NVLink), so the table needs no exchange afterwards
+  uint32_t n_peer_tables;
+  ks_pair_row* peer_rows[15];
 };
 
 __global__ void __launch_bounds__(256) k_finalize_keys(const FinalArgs a) {
@@ -250,7 +254,11 @@ __global__ void __launch_bounds__(256) k_finalize_pairs(const FinalArgs a) {
     __syncthreads();
     uint4* dst = reinterpret_cast<uint4*>(a.pair_rows + out0);
     const uint4* sv = reinterpret_cast<const uint4*>(stage);
-    for (uint32_t i = threadIdx.x; i < here * (kOutWords / 4); i += 256) dst[i] = sv[(i / (kOutWords / 4)) * kRowVec + i % (kOutWords / 4)];
+    for (uint32_t i = threadIdx.x; i < here * (kOutWords / 4); i += 256) {
+      const uint4 v = sv[(i / (kOutWords / 4)) * kRowVec + i % (kOutWords / 4)];
+      dst[i] = v;
+      for (uint32_t q = 0; q < a.n_peer_tables; ++q) reinterpret_cast<uint4*>(a.peer_rows[q] + out0)[i] = v;
+    }
   }
 }
 

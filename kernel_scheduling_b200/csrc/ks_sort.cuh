@@ -257,6 +257,8 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
 // run of two equal digits fills a whole 32-byte sector.
 struct SortPass16Args {
   // by_dest != 0: the "digit" is the destination rank of the item = number of splitters <= (key >> split_shift)
+  // by_dest == 2: the items of destination d go to dest[d] (this rank's place in rank d's receive buffer, peer memory for
+  // d != own rank: plain stores over NVLink) instead of out + gbase[d]
   uint32_t by_dest;
   uint32_t n_split;
   uint32_t split_shift;
@@ -271,6 +273,7 @@ struct SortPass16Args {
   uint32_t* lookback;
   uint32_t* ticket;
   uint32_t* err;
+  uint4* dest[16];
 };
 
 __device__ __forceinline__ uint32_t digit16(const SortPass16Args& a, uint32_t key, uint32_t dmask) {
@@ -380,7 +383,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(con
         uint32_t off = 0;
         for (uint32_t w = 0; w < warp; ++w) off += s_misc[1 + w];
         const uint32_t dstart = off + inc - acc;
-        s_gpos[d] = a.gbase[d] + excl - dstart;
+        s_gpos[d] = (a.by_dest == 2 ? 0u : a.gbase[d]) + excl - dstart;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) warp_hist[w * 256 + d] += dstart;
       }
@@ -397,7 +400,9 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(con
       const uint32_t si = i * THREADS + tid;
       if (si < tile_n) {
         const uint4 it = s_items[si];
-        a.out[s_gpos[digit16(a, it.x, dmask)] + si] = it;
+        const uint32_t d = digit16(a, it.x, dmask);
+        uint4* o = a.by_dest == 2 ? a.dest[d] : a.out;
+        o[s_gpos[d] + si] = it;
       }
     }
   }

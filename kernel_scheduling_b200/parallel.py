@@ -357,6 +357,13 @@ class NativeSession:
             ident = ctypes.create_string_buffer(box[0], 128)
         builder._check(lib.ks_mg_comm_init(builder._h, ident, rank, world), "ks_mg_comm_init")
 
+    @property
+    def peer_memory(self) -> bool:
+        """True when the two bulk exchanges are stores into the other GPUs' memory (CUDA IPC over NVLink) from the kernels
+        that produce the data; False when they are NCCL send/recv pairs (``KS_MG_NO_P2P`` set, or a GPU pair without peer
+        access)."""
+        return bool(self.b._lib.ks_mg_peer_memory(self.b._h))
+
     def build_device(self, records: torch.Tensor, key_type: bool = False) -> int:
         """Collective.  ``records``: this rank's window as a uint8 CUDA tensor (48 bytes per record, start order), ready on
         the builder's stream.  Returns the rows of the whole table, which stays on this rank's device (``builder.fetch``)."""
@@ -374,6 +381,7 @@ class NativeSession:
         return self.b.fetch(pinned)
 
     def close(self):
+        """Collective (in peer-memory mode every rank unmaps the others' buffers before any buffer is freed)."""
         self.b._lib.ks_mg_comm_destroy(self.b._h)
 
 

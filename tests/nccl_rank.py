@@ -38,6 +38,14 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     window2 = torch.from_numpy(rec2[lo2:hi2].view(np.uint8).reshape(-1).copy()).cuda()
     torch.cuda.synchronize()
     skeys, spairs = session.build(window2, key_type=True)
+    peer_memory = session.peer_memory
     session.close()
-np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs)
+    # once more with the bulk exchanges forced onto NCCL send/recv
+    os.environ["KS_MG_NO_P2P"] = "1"
+    session = parallel.NativeSession(b, rank, world)
+    assert not session.peer_memory
+    ckeys, cpairs = session.build(window)
+    session.close()
+np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs, ckeys=ckeys, cpairs=cpairs,
+         peer_memory=peer_memory)
 dist.destroy_process_group()

@@ -91,6 +91,9 @@ def test_two_nccl_ranks(tmp_path):
         assert_tables_match(d["nkeys"], d["npairs"], okeys, opairs)
         assert d["nkeys"].tobytes() == d["keys"].tobytes() and d["npairs"].tobytes() == d["pairs"].tobytes()
         assert_tables_match(d["skeys"], d["spairs"], skeys, spairs)
+        # ... and the one with the bulk exchanges on NCCL instead of peer memory
+        assert d["ckeys"].tobytes() == d["keys"].tobytes() and d["cpairs"].tobytes() == d["pairs"].tobytes()
+        print("peer memory:", bool(d["peer_memory"]))
 
 
 @pytest.mark.parametrize("cfg,n,key_type", [("c1", 60_000, False), ("c2", 300_000, True), ("c1", 0, False)])
