@@ -42,6 +42,7 @@ extern "C" {
 #define KS_ON_DEVICE 1u            /* pointer arguments are device pointers */
 #define KS_ASSUME_TIME_ORDERED 2u  /* records are ordered by start_ns: verified, not sorted */
 #define KS_KEY_TYPE 4u             /* key = tenant + name + block (a TYPE row); default is the SHAPE key */
+#define KS_TIMING 8u               /* ks_mg_build: wait for the call to finish and fill the ms_ fields of info */
 
 /* 48-byte launch record.  Replaces one row of the agent's timing log: scheduler/agent.cpp:500-508 (TimingResult)
  * as written at :692-705, with the kernel name (kernel_key.hpp:13-55 short form) replaced by a dictionary id. */
@@ -200,10 +201,10 @@ int64_t ks_mg_finalize(ks_handle* h);                                           
  *   ks_mg_comm_init     collective over the ranks: the handle's communicator (world <= 16)
  *   ks_mg_build         collective: records = this rank's window (DEVICE pointer, start order, 16-byte aligned).  Returns
  *                       the rows of the WHOLE table, which every rank then holds (ks_copy_pair_rows / ks_copy_key_rows);
- *                       queued on the handle's stream, the copies are ordered behind it.  flags: KS_KEY_TYPE or 0.
- *                       info (optional, costs one more host wait): this rank's counts and the device time of the five
- *                       phases, each with its exchange: ms_decode, ms_join, ms_order (partition + sample exchange),
- *                       ms_reduce (K2 + K4), ms_finalize.
+ *                       queued on the handle's stream, the copies are ordered behind it.  flags: KS_KEY_TYPE, KS_TIMING.
+ *                       info (optional): this rank's counts; with KS_TIMING (one more host wait) also the device time
+ *                       of the five phases, each with its exchange: ms_decode, ms_join, ms_order (partition + sample
+ *                       exchange), ms_reduce (K2 + K4), ms_finalize.
  *                       Errors found on the device (bad record, order, capacity) are returned by ALL ranks alike; an
  *                       argument, CUDA or NCCL failure is local to its rank and fatal for the job.
  *   ks_mg_comm_destroy  releases the communicator and the exchange buffers (ks_destroy does it too) */

@@ -20,6 +20,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libks_b200.so"
 ON_DEVICE = 1
 ASSUME_TIME_ORDERED = 2
 KEY_TYPE = 4
+TIMING = 8
 
 ERR_ARG, ERR_CUDA, ERR_RECORD, ERR_NOT_ORDERED, ERR_TOO_MANY_KEYS = 1, 2, 3, 4, 5
 ERR_TABLE_FULL, ERR_CAPACITY, ERR_WAIT, ERR_DUPLICATE, ERR_TOO_LARGE, ERR_COMM = 6, 7, 8, 9, 10, 11

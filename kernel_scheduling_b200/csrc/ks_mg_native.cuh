@@ -355,7 +355,7 @@ int ks_mg_comm_destroy(ks_handle* h) {
 }
 
 int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_t flags, ks_table_info* info) {
-  if (!h || (!records && n_owned) || (flags & ~KS_KEY_TYPE)) return -KS_ERR_ARG;
+  if (!h || (!records && n_owned) || (flags & ~(KS_KEY_TYPE | KS_TIMING))) return -KS_ERR_ARG;
   if (!h->mg_comm) return fail(h, KS_ERR_ARG, "ks_mg_build: no communicator (ks_mg_comm_init)");
   NcclApi* api = nccl_api();
   const int world = h->mg_world, rank = h->mg_rank;
@@ -369,7 +369,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only when info is asked for)
   // ---- phase 1: K1 over the window, its tail, its distinct keys                                 (queued, no wait)
   cudaEventRecord(ev[0], h->stream);
-  { int64_t r = ks_mg_begin(h, records, n_owned, flags); if (r < 0) return r; }
+  { int64_t r = ks_mg_begin(h, records, n_owned, flags & KS_KEY_TYPE); if (r < 0) return r; }
   KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
   uint32_t* tail_idx = as<uint32_t>(h->tmp[0]);
   KS_CUDA(h, cudaMemsetAsync(h->mg_counts, 0, 16, h->stream));
@@ -719,15 +719,16 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     info->min_start_ns = ctl2.min_start;
     info->max_start_ns = ctl2.max_start;
     info->was_time_ordered = 1;
-    // device time of the five phases, each up to and including its exchange (asking for info costs one more wait)
-    cudaEventRecord(ev[5], h->stream);
-    KS_CUDA(h, cudaStreamSynchronize(h->stream));
-    info->ms_decode = ev_ms(ev[0], ev[1]);
-    info->ms_join = ev_ms(ev[1], ev[2]);
-    info->ms_order = ev_ms(ev[2], ev[3]);   // partition by key range + the sample exchange
-    info->ms_reduce = ev_ms(ev[3], ev[4]);  // K2 + K4
-    info->ms_finalize = ev_ms(ev[4], ev[5]);
-    info->ms_total = ev_ms(ev[0], ev[5]);
+    if (flags & KS_TIMING) {  // device time of the five phases, each up to and including its exchange: one more host wait
+      cudaEventRecord(ev[5], h->stream);
+      KS_CUDA(h, cudaStreamSynchronize(h->stream));
+      info->ms_decode = ev_ms(ev[0], ev[1]);
+      info->ms_join = ev_ms(ev[1], ev[2]);
+      info->ms_order = ev_ms(ev[2], ev[3]);   // partition by key range + the sample exchange
+      info->ms_reduce = ev_ms(ev[3], ev[4]);  // K2 + K4
+      info->ms_finalize = ev_ms(ev[4], ev[5]);
+      info->ms_total = ev_ms(ev[0], ev[5]);
+    }
   }
   return (int64_t)rows_total;
 }

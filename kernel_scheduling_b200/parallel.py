@@ -364,14 +364,16 @@ class NativeSession:
         access)."""
         return bool(self.b._lib.ks_mg_peer_memory(self.b._h))
 
-    def build_device(self, records: torch.Tensor, key_type: bool = False) -> int:
+    def build_device(self, records: torch.Tensor, key_type: bool = False, timing: bool = False) -> int:
         """Collective.  ``records``: this rank's window as a uint8 CUDA tensor (48 bytes per record, start order), ready on
-        the builder's stream.  Returns the rows of the whole table, which stays on this rank's device (``builder.fetch``)."""
+        the builder's stream.  Returns the rows of the whole table, which stays on this rank's device (``builder.fetch``).
+        ``timing``: wait for the call to finish and report the device time of its five phases in ``builder.info``."""
         if not records.is_cuda or records.dtype != torch.uint8 or records.numel() % 48:
             raise ValueError("records: a uint8 CUDA tensor of 48-byte records")
         info = _lib.KsTableInfo()
         p = ctypes.c_void_p(records.data_ptr()) if records.numel() else None
-        rows = self.b._check(self.b._lib.ks_mg_build(self.b._h, p, records.numel() // 48, _lib.KEY_TYPE if key_type else 0, ctypes.byref(info)), "ks_mg_build")
+        flags = (_lib.KEY_TYPE if key_type else 0) | (_lib.TIMING if timing else 0)
+        rows = self.b._check(self.b._lib.ks_mg_build(self.b._h, p, records.numel() // 48, flags, ctypes.byref(info)), "ks_mg_build")
         self.b.info = info.as_dict()
         return rows
 
