@@ -29,6 +29,7 @@ import numpy as np  # noqa: E402
 
 METRIC = "trace records/sec to interference table"
 UNIT = "records/s"
+CLOCK_LOAD_STEPS = 200  # at most this many untimed steps in front of the warm-up while the clock sampler runs (about 0.2-0.3 s of load)
 CPU_SAMPLE_RECORDS = 10_000_000  # the CPU arm runs the whole c2 workload: about 10-20 s of one host core per step
 
 
@@ -71,6 +72,12 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+
+    def wait_first(self, timeout: float):
+        """Returns once nvidia-smi has delivered its first sample (its start-up is over), or after ``timeout`` seconds."""
+        t0 = time.perf_counter()
+        while self.proc and not self.rows and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
 
     def stop(self):
         if not self.proc:
@@ -199,15 +206,20 @@ def main():
         builder.info = {"n_pairs": 0, "n_rows": table_t.numel() // 128, "n_keys": keys_t.numel() // 72}
         return table_t.numel() // 128
 
-    # ---- device-resident: warm-up, then K timed steps
-    for _ in range(max(args.warmup, 3)):
+    # ---- device-resident: warm-up, then K timed steps.  The clock sampler (nvidia-smi, rank 0) is started first and given
+    # a stretch of the same load to sample (CLOCK_LOAD_STEPS untimed steps, the same number on every rank): its start-up
+    # would otherwise fall into the timed region, which lasts only a few milliseconds.
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        sampler.wait_first(5.0)
+    barrier()
+    clock_steps = int(max(10, min(CLOCK_LOAD_STEPS, 2_000_000_000 // max(n_rec, 1))))  # fewer for larger traces; the same on every rank
+    for _ in range(clock_steps + max(args.warmup, 3)):
         step_device()
     stage_names = ("ms_decode", "ms_dict", "ms_join", "ms_sort", "ms_reduce", "ms_finalize", "ms_total")
     stage_ms = {k: 0.0 for k in stage_names}
-    sampler = ClockSampler(local_rank)
     barrier()
-    if rank == 0:
-        sampler.start()
     launches0 = builder.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):

@@ -137,15 +137,17 @@ __global__ void __launch_bounds__(256) k_solo_ns(const RowStats* __restrict__ st
 // First 256 bytes of every exchanged block: the sender's control words and the counts the other ranks need.
 struct MgHeader {
   Control ctl;
-  uint32_t n_tail;                 // launches in the sender's tail (block 1)
-  uint32_t reserved0;
+  uint32_t n_tail;                 // launches in the sender's tail
+  uint32_t n_halo;                 // launches of earlier windows that reach into the sender's window (from block 2 on)
   unsigned long long capacity;     // sample capacity of the sender (block 2): n_pairs above it means "grow and repeat"
   unsigned long long first_start;  // start_ns of the sender's first record
   // peer-memory mode: the buffer the other ranks store into next (block 2: the sample receive buffer, block 4: the table)
   unsigned char ipc[64];           // cudaIpcMemHandle_t
   unsigned long long buf_gen;      // changes whenever the sender replaced the buffer
   unsigned long long buf_cap;      // its size in bytes
-  unsigned char pad[256 - sizeof(Control) - 24 - 64 - 16];
+  uint32_t n_local_keys;           // distinct keys of the sender's own window
+  uint32_t reserved0;
+  unsigned char pad[256 - sizeof(Control) - 24 - 64 - 16 - 8];
 };
 struct MgIpc {
   unsigned char handle[64];
@@ -153,14 +155,17 @@ struct MgIpc {
 };
 static_assert(sizeof(MgHeader) == 256, "exchange header is 256 bytes");
 
-__global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n_tail, const unsigned char* records, uint64_t n_owned, uint64_t capacity,
+// counts: {tail, halo, keys of the own window} on the device, or null
+__global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* counts, const unsigned char* records, uint64_t n_owned, uint64_t capacity,
                             const MgIpc ipc) {
   const uint32_t t = threadIdx.x;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(ctl);
   uint32_t* dst = reinterpret_cast<uint32_t*>(&out->ctl);
   if (t < sizeof(Control) / 4) dst[t] = src[t];
   if (t == 0) {
-    out->n_tail = n_tail ? *n_tail : 0u;
+    out->n_tail = counts ? counts[0] : 0u;
+    out->n_halo = counts ? counts[1] : 0u;
+    out->n_local_keys = counts ? counts[2] : 0u;
     out->reserved0 = 0;
     out->capacity = capacity;
     out->first_start = n_owned ? *reinterpret_cast<const unsigned long long*>(records + 32) : 0ull;
@@ -168,6 +173,25 @@ __global__ void k_mg_header(MgHeader* out, const Control* ctl, const uint32_t* n
     out->buf_cap = ipc.cap;
   }
   if (t < 16) reinterpret_cast<uint32_t*>(out->ipc)[t] = reinterpret_cast<const uint32_t*>(ipc.handle)[t];
+}
+
+// every rank's exported keys into this rank's dictionary, counts from the gathered headers (blockIdx.y = source rank)
+__global__ void __launch_bounds__(256) k_dict_insert_gathered(const unsigned char* __restrict__ gathered, size_t stride, size_t off_keys, size_t off_words, uint32_t capacity,
+                                                              unsigned long long* dict_keys, uint4* dict_words, Control* ctl) {
+  const unsigned char* block = gathered + blockIdx.y * stride;
+  const uint32_t n = min(reinterpret_cast<const MgHeader*>(block)->ctl.n_keys, capacity);
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long key = reinterpret_cast<const unsigned long long*>(block + off_keys)[i];
+  if (key == 0ull) return;
+  const uint4* words = reinterpret_cast<const uint4*>(block + off_words);
+  bool inserted;
+  const uint32_t slot = dict_find_or_insert(dict_keys, key, &inserted);
+  if (slot >= kDictSlots) { atomicOr(&ctl->err, kErrTooManyKeys); return; }
+  if (inserted) {
+    dict_words[2 * (size_t)slot] = words[2 * (size_t)i];
+    dict_words[2 * (size_t)slot + 1] = words[2 * (size_t)i + 1];
+  }
 }
 
 // k_gather_records with the count on the device

@@ -4,14 +4,16 @@
 //
 // One process per GPU calls ks_mg_build with its window of the start-ordered trace.  The five exchanges:
 //   1. all-gather  [header | tail launches | distinct keys + launch fields]      -> global key ids, halo
-//   2. all-gather  [header | sample-key histogram | per-key launch counts]       -> splitters, transfer sizes
+//   2. all-gather  [header | sample-key histogram]                               -> splitters, transfer sizes
 //   3. all-to-all  samples to the rank that owns their key range                 (send/recv pairs, exact sizes)
-//   4. all-gather  [header | solo times of the keys reduced here]                -> every key's solo time, shard sizes
+//   4. all-gather  [header | solo times of the keys reduced here | launch counts] -> solo times, totals, shard sizes
 //   5. all-gather  table shards, straight into place in the whole table          (send/recv pairs, exact sizes)
-// Every block starts with a 256-byte header that carries the sender's control words, so after exchanges 1, 2 and 4 every
+// Every block starts with a 256-byte header that carries the sender's control words, so after exchanges 2 and 4 every
 // rank knows every rank's error bits and counts: an error on any rank makes ALL ranks return it from the same point, and
-// decisions that change what is exchanged next (a larger key block, a larger sample stream) are taken alike everywhere.
-// The host waits for the device three times per table (after the header exchanges); everything else is queued.
+// decisions that change what is exchanged next (a larger key block, a larger sample stream, a larger peer buffer) are
+// taken alike everywhere.  The host waits for the device twice per table (behind exchanges 2 and 4: it needs the
+// histograms for the splitters and the shard sizes for the table); everything else is queued, and what exchange 1 feeds
+// (key merge, halo) reads the other ranks' counts from the gathered headers on the device.
 //
 // NCCL is bound at run time (dlopen of libnccl.so.2, or the library named by KS_NCCL_LIBRARY): the library has no link-time
 // dependency on it, and a process that already loaded NCCL (PyTorch) shares that copy.
@@ -366,37 +368,43 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   tr.on = rank == 0 && getenv("KS_MG_TRACE") != nullptr;
   tr.stream = h->stream;
   tr.mark("start");
-  cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only when info is asked for)
-  // ---- phase 1: K1 over the window, its tail, its distinct keys                                 (queued, no wait)
-  cudaEventRecord(ev[0], h->stream);
-  { int64_t r = ks_mg_begin(h, records, n_owned, flags & KS_KEY_TYPE); if (r < 0) return r; }
-  KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
-  uint32_t* tail_idx = as<uint32_t>(h->tmp[0]);
-  KS_CUDA(h, cudaMemsetAsync(h->mg_counts, 0, 16, h->stream));
-  if (n_owned) {
-    k_tail_select<<<1, 1024, 0, h->stream>>>(as<unsigned long long>(h->tl_start[0]) + kHaloMax, as<unsigned long long>(h->tl_dm[0]) + kHaloMax, (uint32_t)n_owned,
-                                             tail_idx, kHaloMax, h->mg_counts, h->d_ctl);
-    ++h->launches;
-  }
-  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
-  DictArgs d{};
-  d.dict_keys = h->dict_keys; d.dkeys = h->dkeys; d.dslot = h->dslot; d.drank = h->drank; d.kid_of_slot = h->kid_of_slot;
-  d.slot_of_kid = h->slot_of_kid; d.keys_sorted = h->keys_sorted; d.ctl = h->d_ctl;
-  k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
-  ++h->launches;
-  tr.mark("decode+tail+compact");
-
+  cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only with KS_TIMING)
+  const bool p2p = h->mg_p2p && world > 1;
+  const uint64_t n_tl = n_owned + kHaloMax;  // the join always sees all halo slots (unused ones are inert)
+  const size_t width2 = H + kMgHistBytes, block2 = width2;
   // blocks 2 and 4 at their largest, so that the exchange buffers are sized once per key capacity
-  const size_t block_other = std::max(H + kMgHistBytes + (size_t)kMaxKeys * 16, H + (size_t)kMaxKeys * 8);
-  size_t block1 = 0, off_keys = 0, off_words = 0;
-  uint64_t key_sum = 0;
-  for (;;) {
+  const size_t block_other = std::max(width2, H + (size_t)kMaxKeys * 24);
+  size_t block1 = 0;
+  unsigned char* gathered = nullptr;
+  uint64_t cap_s = 0;
+  cudaEventRecord(ev[0], h->stream);
+  for (int round = 0;; ++round) {
+    // ---- phase 1: K1 over the window, its tail, its distinct keys; exchange 1                   (queued, no wait)
+    { int64_t r = ks_mg_begin(h, records, n_owned, flags & KS_KEY_TYPE); if (r < 0) return r; }
+    KS_ENSURE(h, h->tmp[0], (size_t)kHaloMax * 4 + 16);
+    uint32_t* tail_idx = as<uint32_t>(h->tmp[0]);
+    KS_CUDA(h, cudaMemsetAsync(h->mg_counts, 0, 16, h->stream));
+    if (n_owned) {
+      k_tail_select<<<1, 1024, 0, h->stream>>>(as<unsigned long long>(h->tl_start[0]) + kHaloMax, as<unsigned long long>(h->tl_dm[0]) + kHaloMax, (uint32_t)n_owned,
+                                               tail_idx, kHaloMax, h->mg_counts, h->d_ctl);
+      ++h->launches;
+    }
+    { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+    DictArgs d{};
+    d.dict_keys = h->dict_keys; d.dkeys = h->dkeys; d.dslot = h->dslot; d.drank = h->drank; d.kid_of_slot = h->kid_of_slot;
+    d.slot_of_kid = h->slot_of_kid; d.keys_sorted = h->keys_sorted; d.ctl = h->d_ctl;
+    k_dict_compact<<<kDictSlots / 256, 256, 0, h->stream>>>(d);
+    ++h->launches;
+    // the number of keys of the own window: the global count replaces it in the control words further down
+    KS_CUDA(h, cudaMemcpyAsync(h->mg_counts + 2, &h->d_ctl->n_keys, 4, cudaMemcpyDeviceToDevice, h->stream));
+    tr.mark("decode+tail+compact");
+
     const uint32_t cap = h->mg_key_cap;
-    off_keys = H + kMgTailBytes;
-    off_words = off_keys + (size_t)cap * 8;
+    const size_t off_keys = H + kMgTailBytes, off_words = off_keys + (size_t)cap * 8;
     block1 = off_words + (size_t)cap * 32;
     KS_ENSURE(h, h->mg_block, std::max(block1, block_other));
     KS_ENSURE(h, h->mg_gathered, std::max(block1, block_other) * (size_t)world);
+    gathered = as<unsigned char>(h->mg_gathered);
     unsigned char* blk = as<unsigned char>(h->mg_block);
     k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, 0, MgIpc{});
     if (n_owned)
@@ -409,110 +417,97 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     tr.mark("pack1");
     KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block1, kNcclUint8, h->mg_comm, h->stream));
     tr.mark("allgather1");
-    { int r = mg_fetch_heads(h, block1, H); if (r) return r; }                                         // ---- wait 1
-    { int r = mg_any_error(h, H, "decode"); if (r) return r; }
-    uint32_t need = 0;
-    key_sum = 0;
-    for (int q = 0; q < world; ++q) {
-      const MgHeader& hd = mg_head(h, H, q);
-      if (hd.n_tail > kHaloMax)
-        return fail(h, KS_ERR_CAPACITY, "ks_mg_build: rank " + std::to_string(q) + " has more launches reaching into the next window than the halo can hold");
-      need = std::max(need, hd.ctl.n_keys);
-      key_sum += hd.ctl.n_keys;
-    }
-    if (need <= cap) break;
-    uint32_t grown = cap;
-    while (grown < need) grown <<= 1;
-    h->mg_key_cap = grown;  // every rank saw the same headers and grows alike
-  }
 
-  // ---- phase 2: global key ids, halo, samples, histogram + launch counts                        (queued, no wait)
-  cudaEventRecord(ev[1], h->stream);
-  unsigned char* gathered = as<unsigned char>(h->mg_gathered);
-  for (int q = 0; q < world; ++q) {
-    const uint32_t nq = mg_head(h, H, q).ctl.n_keys;
-    if (!nq) continue;
-    k_dict_insert<<<(nq + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<const unsigned long long*>(gathered + q * block1 + off_keys),
-                                                           reinterpret_cast<const uint4*>(gathered + q * block1 + off_words), nq, h->dict_keys, h->dict_words, h->d_ctl);
+    // ---- phase 2: global key ids, halo, samples, histogram; exchange 2                          (queued, then wait 1)
+    // Nothing here needs the host to have seen exchange 1: the kernels read the other ranks' counts from the gathered
+    // headers.  What the host would have checked (tails and keys that fit) is checked behind exchange 2 instead.
+    if (round == 0) cudaEventRecord(ev[1], h->stream);
+    k_dict_insert_gathered<<<dim3((cap + 255) / 256, (unsigned)world), 256, 0, h->stream>>>(gathered, block1, off_keys, off_words, cap, h->dict_keys, h->dict_words,
+                                                                                            h->d_ctl);
     ++h->launches;
-  }
-  { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
-  KS_CUDA(h, cudaMemsetAsync(h->drank, 0, (size_t)(kMaxKeys + 1) * 4, h->stream));
-  { int r = run_dict(h); if (r) return r; }
-  {
-    HaloArgs ha{};
-    ha.gathered = gathered;
-    ha.stride = block1;
-    ha.rank = (uint32_t)rank;
-    ha.own_records = rec;
-    ha.n_owned = n_owned;
-    ha.dict_keys = h->dict_keys;
-    ha.type_mode = (flags & KS_KEY_TYPE) ? 1 : 0;
-    ha.tl_start = as<unsigned long long>(h->tl_start[0]);
-    ha.tl_dm = as<unsigned long long>(h->tl_dm[0]);
-    ha.n_halo = h->mg_counts + 1;
-    ha.ctl = h->d_ctl;
-    k_halo_place<<<1, 1024, 0, h->stream>>>(ha);
-    ++h->launches;
-  }
-  tr.mark("wait1+dict+halo");
-  h->mg_n_halo = kHaloMax;  // the join always sees all halo slots (unused ones are inert)
-  const uint32_t cap2 = (uint32_t)std::min<uint64_t>(key_sum, kMaxKeys);  // the global key count is at most the sum
-  const size_t off_launches = H + kMgHistBytes, off_solo = off_launches + (size_t)cap2 * 8;
-  const size_t block2 = (off_solo + (size_t)cap2 * 8 + 15) & ~(size_t)15;
-  const uint64_t n_tl = n_owned + kHaloMax;
-  uint64_t cap_s = sample_capacity(h);
-  if (cap_s < std::max<uint64_t>(2 * n_tl, 1u << 16)) {
-    cap_s = std::max<uint64_t>(2 * n_tl, 1u << 16);
-    int r = ensure_samples(h, cap_s);
-    if (r) return r;
-  }
-  const bool p2p = h->mg_p2p && world > 1;
-  if (p2p) { int r = mg_export_ensure(h, h->mg_recv_x, cap_s * 16); if (r) return r; }
-  const size_t width2 = H + kMgHistBytes;
-  for (int attempt = 0;; ++attempt) {
-    unsigned char* blk = as<unsigned char>(h->mg_block);
-    KS_CUDA(h, cudaMemsetAsync(blk + H, 0, block2 - H, h->stream));
-    if (cap2)
-      k_counts_export_dev<<<(cap2 + 255) / 256, 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, h->d_ctl, cap2,
-                                                                     reinterpret_cast<unsigned long long*>(blk + off_launches),
-                                                                     reinterpret_cast<unsigned long long*>(blk + off_solo));
-    SoloArgs s{};
-    s.solo_stream = as<unsigned long long>(h->solo_stream);
-    s.kid_of_slot = h->kid_of_slot;
-    s.samples = as<uint4>(h->samples[0]);
-    s.capacity = cap_s;
-    s.ctl = h->d_ctl;
-    k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
-    { int r = run_join(h, 0, n_tl, cap_s, nullptr, nullptr, 0, kHaloMax); if (r) return r; }
-    tr.mark("samples+join");
-    k_key_hist_dev<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
-    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
-    h->launches += cap2 ? 4 : 3;
-    KS_CUDA(h, cudaGetLastError());
-    tr.mark("hist+pack2");
-    KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block2, kNcclUint8, h->mg_comm, h->stream));
-    tr.mark("allgather2");
-    { int r = mg_fetch_heads(h, block2, width2); if (r) return r; }                                    // ---- wait 2
-    { int r = mg_any_error(h, width2, "join"); if (r) return r; }
-    bool any_over = false;
-    for (int q = 0; q < world; ++q) {
-      const MgHeader& hd = mg_head(h, width2, q);
-      if (hd.n_tail > kHaloMax)  // here: the launches of earlier windows that reach into window q
-        return fail(h, KS_ERR_CAPACITY, "ks_mg_build: " + std::to_string(hd.n_tail) + " launches of earlier windows reach into window " + std::to_string(q) +
-                                            "; the halo holds " + std::to_string(kHaloMax));
-      if (hd.ctl.n_keys != mg_head(h, width2, 0).ctl.n_keys) return fail(h, KS_ERR_COMM, "ks_mg_build: the ranks disagree on the number of keys");
-      if (hd.ctl.n_pairs >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more on rank " + std::to_string(q));
-      if (hd.ctl.n_pairs > hd.capacity) any_over = true;
+    { int r = mg_zero_u32(h, &h->d_ctl->n_keys); if (r) return r; }
+    KS_CUDA(h, cudaMemsetAsync(h->drank, 0, (size_t)(kMaxKeys + 1) * 4, h->stream));
+    { int r = run_dict(h); if (r) return r; }
+    {
+      HaloArgs ha{};
+      ha.gathered = gathered;
+      ha.stride = block1;
+      ha.rank = (uint32_t)rank;
+      ha.own_records = rec;
+      ha.n_owned = n_owned;
+      ha.dict_keys = h->dict_keys;
+      ha.type_mode = (flags & KS_KEY_TYPE) ? 1 : 0;
+      ha.tl_start = as<unsigned long long>(h->tl_start[0]);
+      ha.tl_dm = as<unsigned long long>(h->tl_dm[0]);
+      ha.n_halo = h->mg_counts + 1;
+      ha.ctl = h->d_ctl;
+      k_halo_place<<<1, 1024, 0, h->stream>>>(ha);
+      ++h->launches;
     }
-    if (!any_over) break;
-    if (attempt == 1) return fail(h, KS_ERR_CAPACITY, "ks_mg_build: sample stream still too small");
-    const uint64_t mine = mg_head(h, width2, rank).ctl.n_pairs;
-    if (mine > cap_s) {  // only the ranks that ran over grow; all of them repeat the step
-      cap_s = mine + mine / 16;
+    tr.mark("dict+halo");
+    h->mg_n_halo = kHaloMax;
+    cap_s = sample_capacity(h);
+    if (cap_s < std::max<uint64_t>(2 * n_tl, 1u << 16)) {
+      cap_s = std::max<uint64_t>(2 * n_tl, 1u << 16);
       int r = ensure_samples(h, cap_s);
       if (r) return r;
     }
+    if (p2p) { int r = mg_export_ensure(h, h->mg_recv_x, cap_s * 16); if (r) return r; }
+    bool keys_fit = true;
+    for (int attempt = 0;; ++attempt) {
+      KS_CUDA(h, cudaMemsetAsync(blk + H, 0, kMgHistBytes, h->stream));
+      SoloArgs s{};
+      s.solo_stream = as<unsigned long long>(h->solo_stream);
+      s.kid_of_slot = h->kid_of_slot;
+      s.samples = as<uint4>(h->samples[0]);
+      s.capacity = cap_s;
+      s.ctl = h->d_ctl;
+      k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
+      { int r = run_join(h, 0, n_tl, cap_s, nullptr, nullptr, 0, kHaloMax); if (r) return r; }
+      tr.mark("samples+join");
+      k_key_hist_dev<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
+      k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
+      h->launches += 3;
+      KS_CUDA(h, cudaGetLastError());
+      tr.mark("hist+pack2");
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block2, kNcclUint8, h->mg_comm, h->stream));
+      tr.mark("allgather2");
+      { int r = mg_fetch_heads(h, block2, width2); if (r) return r; }                                  // ---- wait 1
+      // did every rank's keys fit exchange 1?  If not, nothing computed since means anything: grow (alike everywhere,
+      // every rank sees the same headers) and start over
+      uint32_t need = 0;
+      for (int q = 0; q < world; ++q) need = std::max(need, mg_head(h, width2, q).n_local_keys);
+      if (need > cap) {
+        uint32_t grown = cap;
+        while (grown < need) grown <<= 1;
+        h->mg_key_cap = grown;
+        keys_fit = false;
+        break;
+      }
+      { int r = mg_any_error(h, width2, "decode and join"); if (r) return r; }
+      bool any_over = false;
+      for (int q = 0; q < world; ++q) {
+        const MgHeader& hd = mg_head(h, width2, q);
+        if (hd.n_tail > kHaloMax)
+          return fail(h, KS_ERR_CAPACITY, "ks_mg_build: rank " + std::to_string(q) + " has more launches reaching into the next window than the halo can hold");
+        if (hd.n_halo > kHaloMax)
+          return fail(h, KS_ERR_CAPACITY, "ks_mg_build: " + std::to_string(hd.n_halo) + " launches of earlier windows reach into window " + std::to_string(q) +
+                                              "; the halo holds " + std::to_string(kHaloMax));
+        if (hd.ctl.n_keys != mg_head(h, width2, 0).ctl.n_keys) return fail(h, KS_ERR_COMM, "ks_mg_build: the ranks disagree on the number of keys");
+        if (hd.ctl.n_pairs >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more on rank " + std::to_string(q));
+        if (hd.ctl.n_pairs > hd.capacity) any_over = true;
+      }
+      if (!any_over) break;
+      if (attempt == 1) return fail(h, KS_ERR_CAPACITY, "ks_mg_build: sample stream still too small");
+      const uint64_t mine = mg_head(h, width2, rank).ctl.n_pairs;
+      if (mine > cap_s) {  // only the ranks that ran over grow; all of them repeat the step
+        cap_s = mine + mine / 16;
+        int r = ensure_samples(h, cap_s);
+        if (r) return r;
+      }
+    }
+    if (keys_fit) break;
+    if (round == 2) return fail(h, KS_ERR_COMM, "ks_mg_build: the key exchange keeps overflowing");
   }
   const Control ctl2 = mg_head(h, width2, rank).ctl;  // a copy: the pinned area is reused by the next exchange
   const uint64_t nk = ctl2.n_keys;
@@ -553,11 +548,6 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     for (int q = 0; q < world; ++q) in += range_sum(q, r);
     if (in >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more in the key range of rank " + std::to_string(r));
   }
-  if (nk) {
-    k_counts_sum_import<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block2, (uint32_t)world, off_launches, off_solo, h->slot_of_kid, (uint32_t)nk,
-                                                                             h->dict_launches, h->dict_solo);
-    ++h->launches;
-  }
   const int key_bits = bit_length(nk + nk * nk);
   const uint32_t shift = key_bits > 12 ? (uint32_t)(key_bits - 12) : 0u;
   uint32_t splitters[16] = {0};
@@ -582,9 +572,9 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     if (grow) {
       if (n_recv * 16 > h->mg_recv_x.cap) { int r = mg_export_ensure(h, h->mg_recv_x, n_recv * 16 + n_recv * 4); if (r) return r; }
       unsigned char* blk = as<unsigned char>(h->mg_block);
-      k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts + 1, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
+      k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
       ++h->launches;
-      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));  // behind k_counts_sum_import, which read the old blocks
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));
       { int r = mg_fetch_heads(h, H, H); if (r) return r; }
     }
     const size_t wh = grow ? H : width2;  // layout of the pinned header copies
@@ -600,7 +590,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
       dest[d] = reinterpret_cast<uint4*>(base + my_off_at[d] * 16);
     }
     { int r = mg_partition_to_peers(h, splitters, shift, (uint32_t)world, dest); if (r) return r; }
-    tr.mark("wait2+partition to peers");
+    tr.mark("wait1+partition to peers");
     { int r = mg_barrier(h); if (r) return r; }
     tr.mark("barrier");
     sort_input = reinterpret_cast<const uint4*>(h->mg_recv_x.p);
@@ -608,7 +598,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   } else {
     // -- NCCL: partition into sample set 1, one send/recv pair per peer with exact sizes, own part by a local copy
     { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
-    tr.mark("wait2+partition");
+    tr.mark("wait1+partition");
     const bool in_place = n_recv <= sample_capacity(h);
     if (!in_place) KS_ENSURE(h, h->mg_recv, n_recv * 16);
     unsigned char* recv_base = in_place ? as<unsigned char>(h->samples[0]) : as<unsigned char>(h->mg_recv);
@@ -631,21 +621,29 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     }
   }
 
-  // ---- phase 4: K2 + K4 over the received key range; solo times                                 (queued, then wait 3)
+  // ---- phase 4: K2 + K4 over the received key range; solo times                                 (queued, then wait 2)
   cudaEventRecord(ev[3], h->stream);
   { int r = mg_reduce_queue(h, n_recv, sort_input); if (r) return r; }
   tr.mark("sort+stats");
   if (p2p) { int r = mg_export_ensure(h, h->mg_table_x, std::max<size_t>(h->mg_table_x.cap, (size_t)8 << 20)); if (r) return r; }
-  const size_t block4 = (H + (size_t)nk * 8 + 15) & ~(size_t)15;
+  // block 4: [header | solo times | launches per key | solo launches per key], all by dense key id
+  const size_t off_launches = H + (size_t)nk * 8, off_solo = off_launches + (size_t)nk * 8;
+  const size_t block4 = (off_solo + (size_t)nk * 8 + 15) & ~(size_t)15;
   {
     unsigned char* blk = as<unsigned char>(h->mg_block);
     k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
     ++h->launches;
-    if (nk) KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+    if (nk) {
+      KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+      k_counts_export_dev<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, h->d_ctl, (uint32_t)nk,
+                                                                               reinterpret_cast<unsigned long long*>(blk + off_launches),
+                                                                               reinterpret_cast<unsigned long long*>(blk + off_solo));
+      ++h->launches;
+    }
     KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block4, kNcclUint8, h->mg_comm, h->stream));
   }
   tr.mark("allgather4");
-  { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 3
+  { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 2
   { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
   std::vector<uint64_t> row_off(world + 1, 0);
   for (int q = 0; q < world; ++q) {
@@ -659,7 +657,9 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   cudaEventRecord(ev[4], h->stream);
   if (nk) {
     k_solo_merge<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, H, (uint32_t)nk, h->solo_ns);
-    ++h->launches;
+    k_counts_sum_import<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, off_launches, off_solo, h->slot_of_kid, (uint32_t)nk,
+                                                                             h->dict_launches, h->dict_solo);
+    h->launches += 2;
   }
   if (p2p) {
     // -- peer memory: the finalize kernel stores this rank's rows into every rank's copy of the table
@@ -683,7 +683,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     }
     ks_pair_row* table = reinterpret_cast<ks_pair_row*>(h->mg_table_x.p);
     { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine, n_peers, peers); if (r) return r; }
-    tr.mark("wait3+finalize to peers");
+    tr.mark("wait2+finalize to peers");
     { int r = mg_barrier(h); if (r) return r; }
     tr.mark("barrier");
     h->pair_rows_src = table;
@@ -691,7 +691,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
     ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
     { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine); if (r) return r; }
-    tr.mark("wait3+finalize");
+    tr.mark("wait2+finalize");
     if (world > 1) {
       KS_NCCL(h, api->GroupStart());
       for (int q = 0; q < world; ++q) {
