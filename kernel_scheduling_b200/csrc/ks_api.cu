@@ -52,7 +52,7 @@ struct ks_handle {
   DevBuf records, tl_start[2], tl_dm[2], solo_stream, keys_tmp;
   DevBuf samples[2];  // the sample stream, 16-byte items {sort key, lane 0, lane 1, lane 2}; two sets for the sort
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
-  DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows;
+  DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows, cta_rows;
   DevBuf tmp[6];
   DevBuf tsv_text, tsv_lines, tsv_parsed, tsv_valid, tsv_cnt, tsv_vcnt, tsv_dict, tsv_maps;
   uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0;
@@ -307,11 +307,20 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
     h->attr_decode = true;
   }
   const uint64_t ntiles = (n + kDecodeTile - 1) / kDecodeTile;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 3);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * kDecodeCtasPerSm);
   k_decode_hash<<<grid, kDecodeThreads, decode_smem_bytes(), h->stream>>>(a);
   ++h->launches;
   KS_CUDA(h, cudaGetLastError());
   return 0;
+}
+
+// The decode kernel records only the first and the last start in Control::min_start / max_start: the range of an ordered
+// trace.  For an unordered one this pass over the timeline extends them to the real range (and reads the control words back).
+int start_range_of_unordered(ks_handle* h, const unsigned long long* tl_start, uint64_t n) {
+  k_minmax_u64<<<h->sm_count * 2, 256, 0, h->stream>>>(tl_start, n, h->d_ctl);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  return read_ctl(h);
 }
 
 // sorts timeline set 0 by start_ns if the decode found it unordered; returns the set that holds the ordered timeline
@@ -322,6 +331,7 @@ int order_timeline(ks_handle* h, uint64_t n, bool* was_ordered) {
   KS_ENSURE(h, h->tl_dm[1], n * 8);
   unsigned long long* keys[2] = {as<unsigned long long>(h->tl_start[0]), as<unsigned long long>(h->tl_start[1])};
   unsigned long long* vals[2][1] = {{as<unsigned long long>(h->tl_dm[0])}, {as<unsigned long long>(h->tl_dm[1])}};
+  { int r = start_range_of_unordered(h, keys[0], n); if (r) return r; }
   const int end_bit = bit_length(h->h_ctl->min_start ^ h->h_ctl->max_start);
   return radix_sort<unsigned long long, unsigned long long, 1, 8>(h, keys, vals, n, nullptr, 0, end_bit);
 }
@@ -378,12 +388,13 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
 
 // K4 core: integer statistics of every row (three size classes, see ks_segstats.cuh)
 int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, uint64_t n_values, uint32_t max_rows) {
-  const uint32_t max_large = (uint32_t)(n_values / kMidMax) + 1;
+  const uint32_t max_large = (uint32_t)(n_values / kBigMax) + 1;
   const uint32_t max_chunks = (uint32_t)(n_values / kLargeChunk) + max_large + 1;
   KS_ENSURE(h, h->stats, ((size_t)max_rows + 257) * sizeof(RowStats));
   KS_ENSURE(h, h->big_rows, ((size_t)max_rows + 1) * 4);
   KS_ENSURE(h, h->small_rows, ((size_t)max_rows + 1) * 4);
   KS_ENSURE(h, h->small8_rows, ((size_t)max_rows + 1) * 4);
+  KS_ENSURE(h, h->cta_rows, ((size_t)(n_values / kMidMax) + 2) * 4);
   KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
   KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
@@ -399,6 +410,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   s.mid_rows = as<uint32_t>(h->big_rows);
   s.small_rows = as<uint32_t>(h->small_rows);
   s.small8_rows = as<uint32_t>(h->small8_rows);
+  s.big_rows = as<uint32_t>(h->cta_rows);
   s.large = as<LargeRow>(h->large_rows);
   s.chunk_row = as<uint32_t>(h->chunk_row);
   s.chunk_idx = as<uint32_t>(h->chunk_idx);
@@ -414,6 +426,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->fork_ev, 0));
   k_seg_small<8><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
   k_seg_small<32><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
+  k_seg_big<<<h->sm_count * 2, 256, 0, h->aux[0]>>>(s);
   k_seg_mid<<<h->sm_count * 4, 256, 0, h->aux[1]>>>(s);
   KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
   KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
@@ -428,7 +441,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[1], 0));
-  h->launches += 7 + 2 * kLargeRounds;
+  h->launches += 8 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -569,7 +582,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
@@ -852,6 +865,7 @@ int64_t ks_sort_launches(ks_handle* h, const void* records, uint64_t n, uint32_t
   unsigned long long* b[2][1] = {{as<unsigned long long>(h->keys_tmp)}, {as<unsigned long long>(h->tmp[4])}};
   int cur = 0;
   if ((h->h_ctl->err & kErrUnordered) && n > 1) {
+    { int r = start_range_of_unordered(h, a[0], n); if (r) return r; }
     cur = radix_sort<unsigned long long, unsigned long long, 1, 8>(h, a, b, n, nullptr, 0, bit_length(h->h_ctl->min_start ^ h->h_ctl->max_start));
     if (cur < 0) return cur;
   }
@@ -1042,6 +1056,7 @@ int mg_reduce_queue(ks_handle* h, uint64_t n, const uint4* first_in = nullptr) {
   { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
   KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->scratch0, 0, 8, h->stream));
   KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad2[1], 0, 8, h->stream));
   KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
   const uint64_t nk = h->mg_nk;
   const int cur = radix_sort16(h, n, bit_length(nk + nk * nk), nullptr, first_in);

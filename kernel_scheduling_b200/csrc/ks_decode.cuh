@@ -22,7 +22,9 @@ constexpr int kDecodeStages = 2;
 constexpr int kDecodePerThread = 2;  // two records per thread: two dictionary probes in flight
 constexpr int kDecodeTile = kDecodeThreads * kDecodePerThread;
 constexpr int kDecodeTileBytes = kDecodeTile * 48;
-constexpr uint32_t kCtaCountSlots = 1024;  // per-CTA launch-count cache (open addressing on the dictionary slot)
+constexpr int kCtaCountBits = 10;
+constexpr int kDecodeCtasPerSm = 3;  // 61 KB of shared memory per CTA; four CTAs with a 512-slot count cache measured the same
+constexpr uint32_t kCtaCountSlots = 1u << kCtaCountBits;  // per-CTA launch-count cache (open addressing on the dictionary slot)
 
 struct DecodeArgs {
   const unsigned char* records;
@@ -89,7 +91,7 @@ __device__ __forceinline__ uint32_t dict_find_or_insert(unsigned long long* dict
   return kDictSlots;
 }
 
-__global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs a) {
+__global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm) k_decode_hash(const DecodeArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* tiles = smem;                                                           // [stages][tile bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecodeStages * kDecodeTileBytes);  // [stages]
@@ -123,7 +125,6 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
   }
 
   uint32_t err = 0, max_dur = 0;
-  unsigned long long min_start = ~0ull, max_start = 0ull;
   uint32_t it = 0;
   for (uint64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
     const int stage = it % kDecodeStages;
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
         if (!a.halo) {
           // launch counts: CTA-local cache first (a plain load finds the key's entry once it exists), global atomics
           // when the cache is crowded
-          uint32_t h = (slot * 2654435761u) >> (32 - 10);
+          uint32_t h = (slot * 2654435761u) >> (32 - kCtaCountBits);
           bool cached = false;
           for (int probe = 0; probe < 8; ++probe) {
             uint32_t cur = cc_slot[h];
@@ -205,8 +206,10 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
         a.tl_dm[r[u]] = (unsigned long long)dur | ((unsigned long long)meta << 32);
         if (a.keys_out) a.keys_out[r[u]] = key[u];
         max_dur = max(max_dur, dur);
-        min_start = min(min_start, start[u]);
-        max_start = max(max_start, start[u]);
+        // Control::min_start / max_start: of an ordered trace they are the first and the last start.  An unordered one
+        // gets them from a pass of its own (the host runs it when the order flag comes back set).
+        if (r[u] == 0) atomicMin(&a.ctl->min_start, start[u]);
+        if (r[u] == a.n - 1) atomicMax(&a.ctl->max_start, start[u]);
       }
       // solo stream: one counter update per warp
       if (solo_ballot) {
@@ -231,18 +234,9 @@ __global__ void __launch_bounds__(kDecodeThreads) k_decode_hash(const DecodeArgs
   // flush per-thread reductions and the CTA's launch counts
   err = __reduce_or_sync(0xFFFFFFFFu, err);
   max_dur = warp_max(max_dur);
-#pragma unroll
-  for (int o = 16; o; o >>= 1) {
-    min_start = min(min_start, __shfl_xor_sync(0xFFFFFFFFu, min_start, o));
-    max_start = max(max_start, __shfl_xor_sync(0xFFFFFFFFu, max_start, o));
-  }
   if (lane == 0) {
     if (err) atomicOr(&a.ctl->err, err);
     if (max_dur) atomicMax(&a.ctl->max_dur, max_dur);
-    if (min_start != ~0ull) {
-      atomicMin(&a.ctl->min_start, min_start);
-      atomicMax(&a.ctl->max_start, max_start);
-    }
   }
   __syncthreads();
   for (uint32_t i = tid; i < kCtaCountSlots; i += kDecodeThreads) {

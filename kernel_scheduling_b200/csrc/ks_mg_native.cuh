@@ -536,7 +536,17 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     }
   }
   std::vector<uint64_t> send_cnt(world, 0), recv_cnt(world, 0);
-  auto range_sum = [&](int q, int r) { uint64_t s = 0; for (uint32_t b = edge[r]; b < edge[r + 1]; ++b) s += hist_of(q)[b]; return s; };
+  // cnt[q][r]: samples rank q holds for rank r's key range -- one walk over every rank's histogram
+  uint64_t cnt[16][16] = {{0}};
+  for (int q = 0; q < world; ++q) {
+    const uint64_t* hq = hist_of(q);
+    for (int r = 0; r < world; ++r) {
+      uint64_t sum = 0;
+      for (uint32_t b = edge[r]; b < edge[r + 1]; ++b) sum += hq[b];
+      cnt[q][r] = sum;
+    }
+  }
+  auto range_sum = [&](int q, int r) { return cnt[q][r]; };
   uint64_t n_recv = 0;
   for (int q = 0; q < world; ++q) {
     send_cnt[q] = range_sum(rank, q);

@@ -213,8 +213,13 @@ __global__ void __launch_bounds__(256) k_finalize_pairs(const FinalArgs a) {
       uint32_t* w = reinterpret_cast<uint32_t*>(&st);
 #pragma unroll
       for (int i = 0; i < kInWords; ++i) w[i] = stage[threadIdx.x * kInWords + i];
-      const uint32_t pid = a.row_key[r] - nk;
-      const uint32_t ka = pid / nk, kb = pid % nk;
+      // A row behind the solo rows holds a pair key >= nk.  When a caller's size guess was wrong (the sort covered too
+      // few key bits) rows are out of order and this does not hold: such a table is thrown away by the host, but its
+      // rows must still index inside the key arrays.
+      const uint32_t rk = a.row_key[r];
+      const bool sane = nk != 0 && rk >= nk && (rk - nk) / nk < nk;
+      const uint32_t pid = sane ? rk - nk : 0u;
+      const uint32_t ka = sane ? pid / nk : 0u, kb = sane ? pid % nk : 0u;
       const uint32_t cnt = a.row_start[r + 1] - a.row_start[r];
       const double sa = a.solo_ns[ka], sb = a.solo_ns[kb];
       const bool va = sa > 0.0, vb = sb > 0.0;  // false for NaN

@@ -5,7 +5,7 @@
 // feeds all three lanes from it.  The stage entry point ks_segment_stats hands in a plain u32 array instead (one lane).
 //
 // Rows differ in size by six orders of magnitude (most key pairs meet a few times, the hottest pair owns percent of
-// all samples), so four size classes share the work:
+// all samples), so five size classes share the work:
 //
 //   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
 //                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
@@ -13,7 +13,9 @@
 //   mid    (n <= 1024)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
 //                         only the bits in which the row's values can differ are walked, 8 per round, with 256-bin
 //                         histograms in the warp's own shared memory -- no block-wide barrier anywhere.
-//   large  (n > 1024)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
+//   big    (n <= 8192)    k_seg_big: one CTA per row, the same selection with block-wide histograms; a row of this size
+//                         is worth a CTA but not the separate launches of the large class.
+//   large  (n > 8192)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
 //                         chunk's sum/min/max into the row's accumulators, then up to four rounds of
 //                         k_segL_hist (chunk histograms of the current digit into the row's global histogram) and
 //                         k_segL_resolve (pick the digit that holds the wanted rank) narrow lo and hi separately.
@@ -29,6 +31,7 @@ namespace ks {
 
 constexpr int kLanes = 3;
 constexpr uint32_t kMidMax = 1024;     // largest row the warp-per-row kernel takes
+constexpr uint32_t kBigMax = 8192;     // largest row the CTA-per-row kernel takes
 constexpr uint32_t kLargeChunk = 4096; // samples per work item of a large row
 constexpr int kLargeRounds = 4;        // 8 bits per round: any 32-bit range
 
@@ -58,15 +61,18 @@ struct SegArgs {
   uint32_t* small_rows;    // [max_rows] rows of 9..32 samples
   uint32_t* small8_rows;   // [max_rows] rows of 5..8 samples
   uint32_t* mid_rows;      // [max_rows]
+  uint32_t* big_rows;      // [max_rows] rows of kMidMax+1 .. kBigMax samples
   LargeRow* large;         // [max_large]
   uint32_t* chunk_row;     // [max_chunks] index into large[]
   uint32_t* chunk_idx;     // [max_chunks] chunk number inside the row
   uint32_t* large_hist;    // [max_large][2 * kLanes][256]
   uint32_t max_large, max_chunks;
   int round;
-  Control* ctl;            // pad32 / n_small / n_big = rows of 5..8 / 9..32 / mid rows, ticket = large rows, scratch0 = chunks,
-                           // pad[0..3] = unresolved selection states per round
+  Control* ctl;            // pad32 / n_small / n_big = rows of 5..8 / 9..32 / mid rows, low word of pad2[1] = big rows,
+                           // ticket = large rows, scratch0 = chunks, pad[0..3] = unresolved selection states per round
 };
+
+__device__ __forceinline__ uint32_t* big_row_counter(Control* ctl) { return reinterpret_cast<uint32_t*>(&ctl->pad2[1]); }
 
 struct Val3 {
   uint32_t v[kLanes];
@@ -154,6 +160,7 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
     push_row(a.small8_rows, &a.ctl->pad32, valid && cnt > 4 && cnt <= 8, row);
     push_row(a.small_rows, &a.ctl->n_small, valid && cnt > 8 && cnt <= kSmallSegment, row);
     push_row(a.mid_rows, &a.ctl->n_big, valid && cnt > kSmallSegment && cnt <= kMidMax, row);
+    push_row(a.big_rows, big_row_counter(a.ctl), valid && cnt > kMidMax && cnt <= kBigMax, row);
     RowStats st;
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) { st.sum[l] = 0; st.mn[l] = 0; st.mx[l] = 0; st.lo[l] = 0; st.hi[l] = 0; }
@@ -181,7 +188,7 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
         st.lo[l] = pick(i_lo);
         st.hi[l] = pick(i_hi);
       }
-    } else if (valid && cnt > kMidMax) {
+    } else if (valid && cnt > kBigMax) {
       const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
       const uint32_t l = atomicAdd(&a.ctl->ticket, 1u);
       const uint32_t cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
@@ -367,6 +374,140 @@ __global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
       }
     }
     if (lane == 0) {
+      RowStats* st = a.stats + row;
+      for (int l = 0; l < nl; ++l) { st->sum[l] = sum[l]; st->mn[l] = mn[l]; st->mx[l] = mx[l]; st->lo[l] = lo[l]; st->hi[l] = hi[l]; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// one CTA per row of kMidMax+1 .. kBigMax samples: k_seg_mid's scheme with block-wide reductions and histograms.  The
+// selection state (prefix, rank, highest open bit per lane) is computed redundantly by every thread from shared results,
+// so it stays in registers.
+__global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
+  __shared__ uint32_t hist[kLanes][256];
+  __shared__ unsigned long long sh_sum[8][kLanes];
+  __shared__ uint32_t sh_a[8][kLanes], sh_b[8][kLanes];
+  __shared__ uint32_t sh_pick[kLanes][2];
+  const uint32_t tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
+  const uint32_t n_big = min(*big_row_counter(a.ctl), a.max_rows);
+  const int nl = a.n_lanes;
+  for (uint32_t t = blockIdx.x; t < n_big; t += gridDim.x) {
+    const uint32_t row = a.big_rows[t];
+    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+    unsigned long long sum[kLanes] = {0, 0, 0};
+    uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
+    for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
+      Val3 xs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) if (i0 + 256 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 256 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + 256 * u >= cnt) break;
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) { sum[l] += xs[u].v[l]; mn[l] = min(mn[l], xs[u].v[l]); mx[l] = max(mx[l], xs[u].v[l]); }
+      }
+    }
+    __syncthreads();  // the previous row's readers of the shared arrays are done
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      const unsigned long long s2 = warp_sum64(sum[l]);
+      const uint32_t n2 = warp_min(mn[l]), x2 = warp_max(mx[l]);
+      if (lane == 0) { sh_sum[warp][l] = s2; sh_a[warp][l] = n2; sh_b[warp][l] = x2; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      sum[l] = 0; mn[l] = 0xFFFFFFFFu; mx[l] = 0;
+      for (int w = 0; w < 8; ++w) { sum[l] += sh_sum[w][l]; mn[l] = min(mn[l], sh_a[w][l]); mx[l] = max(mx[l], sh_b[w][l]); }
+    }
+    const uint32_t k_lo = (cnt - 1) >> 1, k_hi = cnt >> 1;
+    uint32_t prefix[kLanes] = {0, 0, 0}, k[kLanes] = {k_lo, k_lo, k_lo};
+    int hi_bit[kLanes];
+    bool open = false;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      hi_bit[l] = (l < nl && mn[l] != mx[l]) ? bit_length32(mx[l] - mn[l]) - 1 : -1;
+      open = open || hi_bit[l] >= 0;
+    }
+    while (open) {
+      int nb[kLanes], shift[kLanes];
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        nb[l] = min(8, hi_bit[l] + 1);
+        shift[l] = hi_bit[l] + 1 - nb[l];
+        hist[l][tid] = 0;
+      }
+      __syncthreads();
+      for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
+        Val3 xs[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (i0 + 256 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 256 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (i0 + 256 * u >= cnt) break;
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) {
+            if (hi_bit[l] < 0) continue;
+            const uint32_t v = xs[u].v[l] - mn[l];
+            if (matches_prefix(v, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(v >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
+          }
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {  // warp l resolves lane l
+        if (warp != (uint32_t)l || hi_bit[l] < 0) continue;
+        uint32_t d, below;
+        warp_pick_bin(hist[l], k[l], &d, &below);
+        if (lane == 0) { sh_pick[l][0] = d; sh_pick[l][1] = below; }
+      }
+      __syncthreads();
+      open = false;
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        if (hi_bit[l] < 0) continue;
+        prefix[l] |= sh_pick[l][0] << shift[l];
+        k[l] -= sh_pick[l][1];
+        hi_bit[l] = shift[l] - 1;
+        open = open || hi_bit[l] >= 0;
+      }
+      __syncthreads();  // sh_pick and hist are free again
+    }
+    uint32_t lo[kLanes], hi[kLanes];
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) { lo[l] = mn[l] + prefix[l]; hi[l] = lo[l]; }
+    if (k_hi != k_lo) {
+      // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
+      uint32_t le[kLanes] = {0, 0, 0}, next[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
+      for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
+        Val3 xs[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (i0 + 256 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 256 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (i0 + 256 * u >= cnt) break;
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) {
+            le[l] += xs[u].v[l] <= lo[l];
+            if (xs[u].v[l] > lo[l]) next[l] = min(next[l], xs[u].v[l]);
+          }
+        }
+      }
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        const uint32_t le_w = warp_sum(le[l]), nx_w = warp_min(next[l]);
+        if (lane == 0) { sh_a[warp][l] = le_w; sh_b[warp][l] = nx_w; }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        uint32_t le_t = 0, nx = 0xFFFFFFFFu;
+        for (int w = 0; w < 8; ++w) { le_t += sh_a[w][l]; nx = min(nx, sh_b[w][l]); }
+        hi[l] = (le_t > k_hi) ? lo[l] : nx;
+      }
+    }
+    if (tid == 0) {
       RowStats* st = a.stats + row;
       for (int l = 0; l < nl; ++l) { st->sum[l] = sum[l]; st->mn[l] = mn[l]; st->mx[l] = mx[l]; st->lo[l] = lo[l]; st->hi[l] = hi[l]; }
     }

@@ -7,7 +7,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from kernel_scheduling_b200 import parallel, trace
+from kernel_scheduling_b200 import _lib, parallel, trace
 from kernel_scheduling_b200.pair_table import PairTableBuilder
 from kernel_scheduling_b200.records import pack_records
 
@@ -39,6 +39,20 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     torch.cuda.synchronize()
     skeys, spairs = session.build(window2, key_type=True)
     peer_memory = session.peer_memory
+    # a bad record in the LAST rank's window: every rank gets the same status from the same call, nobody is left waiting,
+    # and the session works afterwards
+    bad = rec[lo:hi].copy()
+    if rank == world - 1:
+        bad["end_ns"][5] = bad["start_ns"][5] - np.uint64(1)
+    bad_dev = torch.from_numpy(bad.view(np.uint8).reshape(-1).copy()).cuda()
+    torch.cuda.synchronize()
+    try:
+        session.build(bad_dev)
+        status = 0
+    except _lib.KsError as e:
+        status = e.status
+    rkeys, rpairs = session.build(window)
+    assert rkeys.tobytes() == nkeys.tobytes() and rpairs.tobytes() == npairs.tobytes()
     session.close()
     # once more with the bulk exchanges forced onto NCCL send/recv
     os.environ["KS_MG_NO_P2P"] = "1"
@@ -47,5 +61,5 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     ckeys, cpairs = session.build(window)
     session.close()
 np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs, ckeys=ckeys, cpairs=cpairs,
-         peer_memory=peer_memory)
+         peer_memory=peer_memory, bad_status=status)
 dist.destroy_process_group()

@@ -94,6 +94,7 @@ def test_two_nccl_ranks(tmp_path):
         # ... and the one with the bulk exchanges on NCCL instead of peer memory
         assert d["ckeys"].tobytes() == d["keys"].tobytes() and d["cpairs"].tobytes() == d["pairs"].tobytes()
         print("peer memory:", bool(d["peer_memory"]))
+        assert int(d["bad_status"]) == 3  # KS_ERR_RECORD on BOTH ranks, although only the last rank's window held the bad record
 
 
 @pytest.mark.parametrize("cfg,n,key_type", [("c1", 60_000, False), ("c2", 300_000, True), ("c1", 0, False)])
@@ -108,4 +109,57 @@ def test_native_driver_single_rank(cfg, n, key_type):
         for _ in range(2):
             keys, pairs = session.build(window, key_type=key_type)
             assert_tables_match(keys, pairs, okeys, opairs)
+        session.close()
+
+
+def _window(rec):
+    t = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).cuda()
+    torch.cuda.synchronize()
+    return t
+
+
+def test_native_driver_statuses_and_recovery():
+    """Device-detected errors come back as status codes through the exchange headers; the session stays usable."""
+    from kernel_scheduling_b200 import _lib
+
+    rec = trace.generate(trace.config("c1", 5000))
+    with PairTableBuilder(device=0) as b:
+        session = parallel.NativeSession(b)
+        bad = rec.copy()
+        bad["end_ns"][17] = bad["start_ns"][17] - 1
+        with pytest.raises(_lib.KsError) as e:
+            session.build(_window(bad))
+        assert e.value.status == _lib.ERR_RECORD
+        with pytest.raises(_lib.KsError) as e:
+            session.build(_window(trace.shuffled(rec)))
+        assert e.value.status == _lib.ERR_NOT_ORDERED
+        keys, pairs = session.build(_window(rec))
+        assert_tables_match(keys, pairs, *O.build_pair_table(rec))
+        session.close()
+        # without a communicator the call is refused, not run
+        with pytest.raises(_lib.KsError) as e:
+            session.build(_window(rec))
+        assert e.value.status == _lib.ERR_ARG
+
+
+def test_native_driver_grows_key_block_and_sample_stream():
+    # more distinct keys than the first exchange holds by default (4,096): the build starts over with a larger block
+    n = 12_000
+    start = np.arange(n, dtype=np.uint64) * 50 + 1000
+    names = np.arange(n) % 6000
+    tenant = np.arange(n) % 2
+    rec = pack_records(names, np.ones((n, 3)), np.ones((n, 3)) * 64, np.zeros(n), tenant, (np.arange(n) % 5) == 0, start, start + np.uint64(120))
+    # and eight tenants with long launches: far more overlapping pairs than twice the records (the first guess)
+    m = 40_000
+    start2 = np.arange(m, dtype=np.uint64) * 100 + 1000
+    rec2 = pack_records(np.arange(m) % 50, np.ones((m, 3)), np.ones((m, 3)) * 64, np.zeros(m), np.arange(m) % 8, np.zeros(m, bool), start2, start2 + np.uint64(1500))
+    with PairTableBuilder(device=0) as b:
+        session = parallel.NativeSession(b)
+        sizes = []
+        for r in (rec, rec2):
+            okeys, opairs = O.build_pair_table(r)
+            keys, pairs = session.build(_window(r))
+            assert_tables_match(keys, pairs, okeys, opairs)
+            sizes.append((len(keys), int(pairs["count"].sum())))
+        assert sizes[0][0] > 4096 and sizes[1][1] > 2 * (m + 4096)  # the cases are what they claim to be
         session.close()
