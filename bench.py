@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--max-records", type=int, default=10_000_000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--clock-load-steps", type=int, default=CLOCK_LOAD_STEPS,
+                    help="untimed steps in front of the warm-up while the clock sampler starts (0 for profiler runs)")
     ap.add_argument("--mg-driver", default="native", choices=["native", "python"], help="N > 1: who issues the exchanges (the library through NCCL, or torch.distributed)")
     return ap.parse_args()
 
@@ -214,7 +216,7 @@ def main():
         sampler.start()
         sampler.wait_first(5.0)
     barrier()
-    clock_steps = int(max(10, min(CLOCK_LOAD_STEPS, 2_000_000_000 // max(n_rec, 1))))  # fewer for larger traces; the same on every rank
+    clock_steps = int(max(10, min(args.clock_load_steps, 2_000_000_000 // max(n_rec, 1)))) if args.clock_load_steps > 0 else 0  # fewer for larger traces; the same on every rank
     for _ in range(clock_steps + max(args.warmup, 3)):
         step_device()
     stage_names = ("ms_decode", "ms_dict", "ms_join", "ms_sort", "ms_reduce", "ms_finalize", "ms_total")
@@ -344,6 +346,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, min(CPU_SAMPLE_RECORDS, n_rec), rec)
         print(json.dumps(line), flush=True)
+    if session is not None:
+        session.close()  # collective: every rank unmaps the others' buffers before any rank frees its own
     builder.close()
     if world > 1:
         dist.destroy_process_group()

@@ -485,7 +485,7 @@ __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start,
   out[6 * (size_t)r + 5] = st.hi[0];
 }
 
-void mg_native_release(ks_handle* h);  // ks_mg_native.cuh
+void mg_native_release(ks_handle* h, bool orderly);  // ks_mg_native.cuh
 
 float ev_ms(cudaEvent_t a, cudaEvent_t b) {
   float ms = 0.f;
@@ -575,7 +575,7 @@ void ks_destroy(ks_handle* h) {
   if (!h) return;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
-  mg_native_release(h);
+  mg_native_release(h, false);
   auto fr = [](void* p) { if (p) cudaFree(p); };
   fr(h->d_ctl); fr(h->dict_keys); fr(h->dict_words); fr(h->dict_launches); fr(h->dict_solo); fr(h->kid_of_slot);
   fr(h->dkeys); fr(h->dslot); fr(h->drank); fr(h->slot_of_kid); fr(h->row_of_kid); fr(h->keys_sorted); fr(h->solo_ns); fr(h->key_rows);

@@ -82,15 +82,24 @@ NcclApi* nccl_api() {
 void mg_close_imports(ks_handle* h);
 void mg_free_exports(ks_handle* h);
 
-// not collective (ks_destroy must never wait for another rank): mappings of the other ranks' buffers are closed, then the
-// own buffers are freed.  ks_mg_comm_destroy is the orderly, collective way (all mappings closed before any buffer goes).
-void mg_native_release(ks_handle* h) {
+// ks_destroy calls this with orderly = false: it must never wait for another rank, so it closes its mappings of the other
+// ranks' buffers and, in peer-memory mode, leaves its own exported buffers to the end of the process.
+// ks_mg_comm_destroy is the orderly, collective way (all mappings closed everywhere, then every buffer freed).
+void mg_native_release(ks_handle* h, bool orderly) {
   if (h->pair_rows_src && h->pair_rows_src != h->pair_rows.p) {  // the last table lives in an exported buffer
     h->pair_rows_src = nullptr;
     h->n_pair_rows = 0;
   }
   mg_close_imports(h);
-  mg_free_exports(h);
+  if (orderly || !h->mg_p2p) {
+    mg_free_exports(h);
+  } else {
+    // Other ranks may still map these buffers and nobody told them to let go: exported memory must outlive its mappings,
+    // so it is left to the end of the process instead of freed under them.
+    h->mg_recv_x = ks_handle::Exported{};
+    h->mg_table_x = ks_handle::Exported{};
+    h->mg_retired.clear();
+  }
   if (h->mg_bar) cudaFree(h->mg_bar);
   h->mg_bar = nullptr;
   h->mg_p2p = false;
@@ -348,11 +357,12 @@ int ks_mg_comm_destroy(ks_handle* h) {
   if (!h) return -KS_ERR_ARG;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
+  bool orderly = true;
   if (h->mg_comm && h->mg_p2p && h->mg_world > 1) {  // collective: all mappings are closed before any exported buffer is freed
     mg_close_imports(h);
-    if (mg_barrier(h) == 0) cudaStreamSynchronize(h->stream);
+    orderly = mg_barrier(h) == 0 && cudaStreamSynchronize(h->stream) == cudaSuccess;
   }
-  mg_native_release(h);
+  mg_native_release(h, orderly);
   return KS_OK;
 }
 
