@@ -86,13 +86,13 @@ struct ks_handle {
   size_t mg_host_cap = 0;
 
   // what the last ks_build_table saw: lets the next call queue every stage without reading counts back in between
-  bool attr_sort16 = false, attr_decode = false;  // kernel attributes set on this handle's device
+  bool attr_sort16 = false, attr_decode = false, attr_seg = false;  // kernel attributes set on this handle's device
   bool hint_valid = false;
   uint64_t hint_samples = 0, hint_nk = 0, hint_rows = 0;
   cudaEvent_t ev[12]{};
   // the three size classes of K4 are independent of one another: they run side by side on two helper streams
   cudaStream_t aux[2]{};
-  cudaEvent_t fork_ev{}, join_ev[2]{};
+  cudaEvent_t fork_ev{}, classify_ev{}, join_ev[2]{};
 };
 
 namespace {
@@ -419,18 +419,28 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   s.max_chunks = max_chunks;
   s.ctl = h->d_ctl;
   const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 255) / 256, (uint32_t)h->sm_count * 8));
-  k_seg_classify<<<cgrid, 256, 0, h->stream>>>(s);
-  // fork: small rows on aux[0], mid rows on aux[1], the large-row rounds stay on the main stream
+  if (!h->attr_seg) {  // per device, so remembered per handle
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_mid, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_mid_smem_bytes()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes()));
+    h->attr_seg = true;
+  }
+  // Three streams.  The chain of launches of the large rows is the longest path, so it starts first and stays on the main
+  // stream; the classification and the other classes run beside it: aux[0] classify, rows of 5..32, big rows; aux[1]
+  // (behind the classification) mid rows.  k_segL_final also waits for the classification, which writes zeros into the
+  // statistics of every row it does not finish itself.
   KS_CUDA(h, cudaEventRecord(h->fork_ev, h->stream));
   KS_CUDA(h, cudaStreamWaitEvent(h->aux[0], h->fork_ev, 0));
-  KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->fork_ev, 0));
+  k_seg_classify<<<cgrid, 256, 0, h->aux[0]>>>(s);
+  KS_CUDA(h, cudaEventRecord(h->classify_ev, h->aux[0]));
+  KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->classify_ev, 0));
+  k_seg_mid<<<h->sm_count * 3, kMidWarps * 32, seg_mid_smem_bytes(), h->aux[1]>>>(s);
   k_seg_small<8><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
   k_seg_small<32><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
-  k_seg_big<<<h->sm_count * 2, 256, 0, h->aux[0]>>>(s);
-  k_seg_mid<<<h->sm_count * 4, 256, 0, h->aux[1]>>>(s);
+  k_seg_big<<<h->sm_count * 2, 256, seg_big_smem_bytes(), h->aux[0]>>>(s);
   KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
   KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
   const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 4));
+  k_seg_find_large<<<cgrid, 256, 0, h->stream>>>(s);
   k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
   k_segL_init<<<(max_large * 2 * kLanes + 255) / 256, 256, 0, h->stream>>>(s);
   for (int r = 0; r < kLargeRounds; ++r) {
@@ -438,10 +448,11 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
     k_segL_hist<<<lgrid, 256, 0, h->stream>>>(s);
     k_segL_resolve<<<(int)std::min<uint32_t>(max_large, (uint32_t)h->sm_count * 8), 2 * kLanes * 32, 0, h->stream>>>(s);
   }
+  KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->classify_ev, 0));
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[1], 0));
-  h->launches += 8 + 2 * kLargeRounds;
+  h->launches += 9 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }
@@ -557,6 +568,7 @@ ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
   for (auto& e : h->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
   for (auto& st : h->aux) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&h->fork_ev, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->classify_ev, cudaEventDisableTiming) == cudaSuccess;
   for (auto& e : h->join_ev) ok = ok && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess;
   if (ok && h->cfg.max_records) {
     const size_t n = h->cfg.max_records;
@@ -587,6 +599,7 @@ void ks_destroy(ks_handle* h) {
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
   if (h->fork_ev) cudaEventDestroy(h->fork_ev);
+  if (h->classify_ev) cudaEventDestroy(h->classify_ev);
   for (auto& e : h->join_ev) if (e) cudaEventDestroy(e);
   if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
   delete h;

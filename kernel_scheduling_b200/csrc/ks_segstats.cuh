@@ -10,11 +10,13 @@
 //   tiny   (n <= 4)       k_seg_classify, one thread per row, finishes them in registers (85 % of the rows of a
 //                         Zipf-distributed trace) and pushes the other rows onto the work list of their class.
 //   small  (n <= 32)      k_seg_small<W>: W = 8 or 32 lanes per row, shuffle reductions and a W-wide bitonic network.
-//   mid    (n <= 1024)    k_seg_mid: one warp per row.  Reductions, then a radix select over (value - min) per lane:
-//                         only the bits in which the row's values can differ are walked, 8 per round, with 256-bin
-//                         histograms in the warp's own shared memory -- no block-wide barrier anywhere.
-//   big    (n <= 8192)    k_seg_big: one CTA per row, the same selection with block-wide histograms; a row of this size
-//                         is worth a CTA but not the separate launches of the large class.
+//   mid    (n <= 512)     k_seg_mid: one warp per row.  The row is read once: its value lanes are staged in the warp's own
+//                         shared memory while sum/min/max are taken; then a radix select over (value - min) per lane,
+//                         only the bits in which the row's values can differ, 8 per round, with 256-bin histograms in
+//                         shared memory -- no block-wide barrier anywhere.
+//   big    (n <= 8192)    k_seg_big: one CTA per row, the same scheme with the row staged in 96 KB of shared memory and
+//                         block-wide histograms; a row of this size is worth a CTA but not the separate launches of the
+//                         large class.
 //   large  (n > 8192)     the row is cut into chunks of 4096 samples that any CTA may take; k_segL_reduce adds the
 //                         chunk's sum/min/max into the row's accumulators, then up to four rounds of
 //                         k_segL_hist (chunk histograms of the current digit into the row's global histogram) and
@@ -30,7 +32,7 @@
 namespace ks {
 
 constexpr int kLanes = 3;
-constexpr uint32_t kMidMax = 1024;     // largest row the warp-per-row kernel takes
+constexpr uint32_t kMidMax = 512;      // largest row the warp-per-row kernel takes
 constexpr uint32_t kBigMax = 8192;     // largest row the CTA-per-row kernel takes
 constexpr uint32_t kLargeChunk = 4096; // samples per work item of a large row
 constexpr int kLargeRounds = 4;        // 8 bits per round: any 32-bit range
@@ -147,6 +149,28 @@ __device__ __forceinline__ void push_row(uint32_t* list, uint32_t* counter, bool
   list[base + __popc(ballot & lanemask_lt())] = row;
 }
 
+// The large rows (more than kBigMax samples) are found by a kernel of their own, so that their chain of launches can
+// start while k_seg_classify and the other classes are still at work on other streams: one thread per row registers the
+// row and its chunks.
+__global__ void __launch_bounds__(256) k_seg_find_large(const SegArgs a) {
+  const uint32_t n_rows = min(*a.n_rows_dev, a.max_rows);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n_rows; row += gridDim.x * blockDim.x) {
+    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+    if (cnt <= kBigMax) continue;
+    const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
+    const uint32_t l = atomicAdd(&a.ctl->ticket, 1u);
+    const uint32_t cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
+    if (l >= a.max_large || cbase + nch > a.max_chunks) {
+      atomicOr(&a.ctl->err, kErrTooLarge);
+    } else {
+      LargeRow* L = a.large + l;
+      L->row = row; L->start = s; L->cnt = cnt;
+      for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
+      for (uint32_t c = 0; c < nch; ++c) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
   // the statistics of 256 consecutive rows are 18 KB of consecutive memory: staged here, written with coalesced stores
   constexpr int kWords = sizeof(RowStats) / 4;
@@ -187,18 +211,6 @@ __global__ void __launch_bounds__(256) k_seg_classify(const SegArgs a) {
         st.mx[l] = pick(i_max);
         st.lo[l] = pick(i_lo);
         st.hi[l] = pick(i_hi);
-      }
-    } else if (valid && cnt > kBigMax) {
-      const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
-      const uint32_t l = atomicAdd(&a.ctl->ticket, 1u);
-      const uint32_t cbase = (uint32_t)atomicAdd(&a.ctl->scratch0, (unsigned long long)nch);
-      if (l >= a.max_large || cbase + nch > a.max_chunks) {
-        atomicOr(&a.ctl->err, kErrTooLarge);
-      } else {
-        LargeRow* L = a.large + l;
-        L->row = row; L->start = s; L->cnt = cnt;
-        for (int i = 0; i < kLanes; ++i) { L->sum[i] = 0; L->mn[i] = 0xFFFFFFFFu; L->mx[i] = 0; }
-        for (uint32_t c = 0; c < nch; ++c) { a.chunk_row[cbase + c] = l; a.chunk_idx[cbase + c] = c; }
       }
     }
     // rows of the other classes get zeros now and their statistics from the class kernels, which run after this one
@@ -267,33 +279,44 @@ __global__ void __launch_bounds__(256) k_seg_small(const SegArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// one warp per row of 33..2048 samples; the three lanes are selected together, every sample is loaded once per round
-__global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
-  __shared__ uint32_t hist_all[8][kLanes][256];
-  uint32_t (*hist)[256] = hist_all[threadIdx.x >> 5];
-  const uint32_t lane = lane_id();
+// One warp per row of 33..kMidMax samples.  The row is read from global memory ONCE: its three value lanes are staged in
+// the warp's own shared memory while sum/min/max are taken, and the selection rounds (and the pass for the upper middle
+// value) run over shared memory.  No block-wide barrier anywhere.
+constexpr int kMidWarps = 8;
+constexpr size_t seg_mid_smem_bytes() { return (size_t)kMidWarps * kLanes * (kMidMax + 256) * sizeof(uint32_t); }
+
+__global__ void __launch_bounds__(kMidWarps * 32, 3) k_seg_mid(const SegArgs a) {
+  extern __shared__ __align__(16) uint32_t mid_smem[];
+  const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+  uint32_t* vals = mid_smem + (size_t)warp * kLanes * (kMidMax + 256);  // [kLanes][kMidMax]
+  uint32_t* hist = vals + kLanes * kMidMax;                              // [kLanes][256]
   const uint32_t n_mid = min(a.ctl->n_big, a.max_rows);
-  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+  const uint32_t warps = gridDim.x * kMidWarps;
   const int nl = a.n_lanes;
-  for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_mid; t += warps) {
+  for (uint32_t t = blockIdx.x * kMidWarps + warp; t < n_mid; t += warps) {
     const uint32_t row = a.mid_rows[t];
-    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+    const uint32_t s = a.row_start[row], cnt = min(a.row_start[row + 1] - s, kMidMax);
     unsigned long long sum[kLanes] = {0, 0, 0};
     uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
+    __syncwarp();  // the previous row's readers of the staging area are done
     for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
       Val3 xs[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-      if (i0 + 32 * u >= cnt) break;
-      const Val3 x = xs[u];
+        if (i0 + 32 * u >= cnt) break;
 #pragma unroll
-      for (int l = 0; l < kLanes; ++l) { sum[l] += x.v[l]; mn[l] = min(mn[l], x.v[l]); mx[l] = max(mx[l], x.v[l]); }
+        for (int l = 0; l < kLanes; ++l) {
+          const uint32_t v = xs[u].v[l];
+          vals[l * kMidMax + i0 + 32 * u] = v;
+          sum[l] += v; mn[l] = min(mn[l], v); mx[l] = max(mx[l], v);
+        }
       }
     }
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) { sum[l] = warp_sum64(sum[l]); mn[l] = warp_min(mn[l]); mx[l] = warp_max(mx[l]); }
+    __syncwarp();
 
     const uint32_t k_lo = (cnt - 1) >> 1, k_hi = cnt >> 1;
     uint32_t prefix[kLanes] = {0, 0, 0}, k[kLanes] = {k_lo, k_lo, k_lo};
@@ -312,24 +335,16 @@ __global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
         shift[l] = hi_bit[l] + 1 - nb[l];
         if (hi_bit[l] >= 0) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) hist[l][lane * 8 + i] = 0;
+          for (int i = 0; i < 8; ++i) hist[l * 256 + lane * 8 + i] = 0;
         }
       }
       __syncwarp();
-      for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
-        Val3 xs[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-        if (i0 + 32 * u >= cnt) break;
-        const Val3 x = xs[u];
-#pragma unroll
-        for (int l = 0; l < kLanes; ++l) {
-          if (hi_bit[l] < 0) continue;
-          const uint32_t u = x.v[l] - mn[l];
-          if (matches_prefix(u, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(u >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
-        }
+      for (int l = 0; l < kLanes; ++l) {
+        if (hi_bit[l] < 0) continue;
+        for (uint32_t i = lane; i < cnt; i += 32) {
+          const uint32_t u = vals[l * kMidMax + i] - mn[l];
+          if (matches_prefix(u, prefix[l], hi_bit[l])) atomicAdd(&hist[l * 256 + ((u >> shift[l]) & ((1u << nb[l]) - 1u))], 1u);
         }
       }
       __syncwarp();
@@ -338,7 +353,7 @@ __global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
       for (int l = 0; l < kLanes; ++l) {
         if (hi_bit[l] < 0) continue;
         uint32_t d, below;
-        warp_pick_bin(hist[l], k[l], &d, &below);
+        warp_pick_bin(hist + l * 256, k[l], &d, &below);
         prefix[l] |= d << shift[l];
         k[l] -= below;
         hi_bit[l] = shift[l] - 1;
@@ -351,25 +366,16 @@ __global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
     for (int l = 0; l < kLanes; ++l) { lo[l] = mn[l] + prefix[l]; hi[l] = lo[l]; }
     if (k_hi != k_lo) {
       // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
-      uint32_t le[kLanes] = {0, 0, 0}, next[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-      for (uint32_t i0 = lane; i0 < cnt; i0 += 128) {
-        Val3 xs[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) if (i0 + 32 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 32 * u);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-        if (i0 + 32 * u >= cnt) break;
-        const Val3 x = xs[u];
-#pragma unroll
-        for (int l = 0; l < kLanes; ++l) {
-          le[l] += x.v[l] <= lo[l];
-          if (x.v[l] > lo[l]) next[l] = min(next[l], x.v[l]);
-        }
-        }
-      }
 #pragma unroll
       for (int l = 0; l < kLanes; ++l) {
-        const uint32_t le_t = warp_sum(le[l]), nx = warp_min(next[l]);
+        if (l >= nl) continue;
+        uint32_t le = 0, next = 0xFFFFFFFFu;
+        for (uint32_t i = lane; i < cnt; i += 32) {
+          const uint32_t v = vals[l * kMidMax + i];
+          le += v <= lo[l];
+          if (v > lo[l]) next = min(next, v);
+        }
+        const uint32_t le_t = warp_sum(le), nx = warp_min(next);
         hi[l] = (le_t > k_hi) ? lo[l] : nx;
       }
     }
@@ -381,10 +387,13 @@ __global__ void __launch_bounds__(256, 4) k_seg_mid(const SegArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// one CTA per row of kMidMax+1 .. kBigMax samples: k_seg_mid's scheme with block-wide reductions and histograms.  The
-// selection state (prefix, rank, highest open bit per lane) is computed redundantly by every thread from shared results,
-// so it stays in registers.
+// One CTA per row of kMidMax+1 .. kBigMax samples: the same scheme with block-wide reductions and histograms and the
+// row's three value lanes staged in the CTA's shared memory (96 KB).  The selection state (prefix, rank, highest open
+// bit per lane) is computed redundantly by every thread from shared results, so it stays in registers.
+constexpr size_t seg_big_smem_bytes() { return (size_t)kLanes * kBigMax * sizeof(uint32_t); }
+
 __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
+  extern __shared__ __align__(16) uint32_t big_vals[];  // [kLanes][kBigMax]
   __shared__ uint32_t hist[kLanes][256];
   __shared__ unsigned long long sh_sum[8][kLanes];
   __shared__ uint32_t sh_a[8][kLanes], sh_b[8][kLanes];
@@ -394,9 +403,10 @@ __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
   const int nl = a.n_lanes;
   for (uint32_t t = blockIdx.x; t < n_big; t += gridDim.x) {
     const uint32_t row = a.big_rows[t];
-    const uint32_t s = a.row_start[row], cnt = a.row_start[row + 1] - s;
+    const uint32_t s = a.row_start[row], cnt = min(a.row_start[row + 1] - s, kBigMax);
     unsigned long long sum[kLanes] = {0, 0, 0};
     uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};
+    __syncthreads();  // the previous row's readers of the shared arrays are done
     for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
       Val3 xs[4];
 #pragma unroll
@@ -405,10 +415,13 @@ __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
       for (int u = 0; u < 4; ++u) {
         if (i0 + 256 * u >= cnt) break;
 #pragma unroll
-        for (int l = 0; l < kLanes; ++l) { sum[l] += xs[u].v[l]; mn[l] = min(mn[l], xs[u].v[l]); mx[l] = max(mx[l], xs[u].v[l]); }
+        for (int l = 0; l < kLanes; ++l) {
+          const uint32_t v = xs[u].v[l];
+          big_vals[l * kBigMax + i0 + 256 * u] = v;
+          sum[l] += v; mn[l] = min(mn[l], v); mx[l] = max(mx[l], v);
+        }
       }
     }
-    __syncthreads();  // the previous row's readers of the shared arrays are done
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) {
       const unsigned long long s2 = warp_sum64(sum[l]);
@@ -439,19 +452,12 @@ __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
         hist[l][tid] = 0;
       }
       __syncthreads();
-      for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
-        Val3 xs[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (i0 + 256 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 256 * u);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (i0 + 256 * u >= cnt) break;
-#pragma unroll
-          for (int l = 0; l < kLanes; ++l) {
-            if (hi_bit[l] < 0) continue;
-            const uint32_t v = xs[u].v[l] - mn[l];
-            if (matches_prefix(v, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(v >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
-          }
+      for (int l = 0; l < kLanes; ++l) {
+        if (hi_bit[l] < 0) continue;
+        for (uint32_t i = tid; i < cnt; i += 256) {
+          const uint32_t v = big_vals[l * kBigMax + i] - mn[l];
+          if (matches_prefix(v, prefix[l], hi_bit[l])) atomicAdd(&hist[l][(v >> shift[l]) & ((1u << nb[l]) - 1u)], 1u);
         }
       }
       __syncthreads();
@@ -480,18 +486,12 @@ __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
     if (k_hi != k_lo) {
       // hi = x[k_lo + 1]: lo again if more than k_hi values are <= lo, else the smallest value above lo
       uint32_t le[kLanes] = {0, 0, 0}, next[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-      for (uint32_t i0 = tid; i0 < cnt; i0 += 1024) {
-        Val3 xs[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (i0 + 256 * u < cnt) xs[u] = seg_fetch(a, (size_t)s + i0 + 256 * u);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (i0 + 256 * u >= cnt) break;
-#pragma unroll
-          for (int l = 0; l < kLanes; ++l) {
-            le[l] += xs[u].v[l] <= lo[l];
-            if (xs[u].v[l] > lo[l]) next[l] = min(next[l], xs[u].v[l]);
-          }
+      for (int l = 0; l < kLanes; ++l) {
+        for (uint32_t i = tid; i < cnt; i += 256) {
+          const uint32_t v = big_vals[l * kBigMax + i];
+          le[l] += v <= lo[l];
+          if (v > lo[l]) next[l] = min(next[l], v);
         }
       }
 #pragma unroll
