@@ -232,6 +232,12 @@ int ks_mg_peer_memory(ks_handle* h);
 #define KS_TSV_MODEL_SLOTS 256
 int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t flags);
 int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* where);
+/* Optional, between ks_tsv_parse and ks_tsv_finish: the profiling daemon's log of the same run (one row per released
+ * kernel: batch_id, kind, pid, kernel_id, ...; profiling/pairprof_daemon.cpp:266, :317-318), parsed on the device.  The
+ * rows of process `pid` label the parsed launches by kernel_id (column 0 of the agent log): kind alone* -> a solo sample,
+ * gang* -> a co-run launch; launches the log does not mention (warm-up) are dropped.  ks_tsv_finish then ignores its
+ * `solo` argument.  Returns the rows that remain. */
+int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags);
 int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags);
 
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).

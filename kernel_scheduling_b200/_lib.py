@@ -87,6 +87,7 @@ KS_API = [
     ("ks_mg_peer_memory", [c_void_p], c_int),
     ("ks_tsv_parse", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_tsv_dictionary", [c_void_p, c_int, c_void_p, c_void_p], c_int64),
+    ("ks_tsv_label", [c_void_p, c_void_p, c_uint64, c_uint64, c_uint32], c_int64),
     ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),
 ]

@@ -55,7 +55,9 @@ struct ks_handle {
   DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows, cta_rows;
   DevBuf tmp[6];
   DevBuf tsv_text, tsv_lines, tsv_parsed, tsv_valid, tsv_cnt, tsv_vcnt, tsv_dict, tsv_maps;
-  uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0;
+  DevBuf tsv_kid, tsv_rowsolo, tsv_label, tsv_logtext, tsv_loglines, tsv_logcnt;
+  uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0, tsv_max_kid = 0;
+  bool tsv_labelled = false;  // ks_tsv_label ran on the parsed text: the solo flag is per row
   const unsigned char* tsv_dev_text = nullptr;
 
   // results of the last ks_build_table
@@ -594,7 +596,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
@@ -1373,6 +1375,8 @@ TsvArgs tsv_args(ks_handle* h) {
   a.name_where = d + kTsvNameSlots;
   a.model_hash = d + 2 * (size_t)kTsvNameSlots;
   a.model_where = a.model_hash + kTsvModelSlots;
+  a.kernel_id = as<uint32_t>(h->tsv_kid);
+  a.row_solo = h->tsv_labelled ? as<unsigned char>(h->tsv_rowsolo) : nullptr;
   a.ctl = h->d_ctl;
   return a;
 }
@@ -1389,7 +1393,8 @@ int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t 
   { int r = stage_in<unsigned char>(h, h->tsv_text, reinterpret_cast<const unsigned char*>(text), n_bytes, (flags & KS_ON_DEVICE) != 0, &d_text); if (r) return r; }
   h->tsv_dev_text = d_text;
   h->tsv_n_bytes = n_bytes;
-  h->tsv_n_lines = h->tsv_n_valid = 0;
+  h->tsv_n_lines = h->tsv_n_valid = h->tsv_max_kid = 0;
+  h->tsv_labelled = false;
   const uint64_t ntiles = (n_bytes + kTsvTile - 1) / kTsvTile;
   KS_ENSURE(h, h->tsv_cnt, (ntiles + 1) * 4);
   KS_ENSURE(h, h->tsv_dict, (2 * (size_t)kTsvNameSlots + 2 * kTsvModelSlots) * 8);
@@ -1411,6 +1416,7 @@ int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t 
   KS_ENSURE(h, h->tsv_lines, (n_lines + 2) * 8);
   KS_ENSURE(h, h->tsv_parsed, std::max<uint64_t>(n_lines, 1) * sizeof(ks_record));
   KS_ENSURE(h, h->tsv_valid, std::max<uint64_t>(n_lines, 1));
+  KS_ENSURE(h, h->tsv_kid, std::max<uint64_t>(n_lines, 1) * 4);
   const uint64_t vtiles = (n_lines + 255) / 256;
   KS_ENSURE(h, h->tsv_vcnt, (vtiles + 1) * 4);
   a = tsv_args(h);
@@ -1424,6 +1430,66 @@ int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t 
   { int r = read_ctl(h); if (r) return r; }
   if (h->h_ctl->err & kErrTooManyKeys) return fail(h, KS_ERR_TOO_MANY_KEYS, "ks_tsv_parse: more than 65,536 distinct kernel symbols or 256 models in one file");
   h->tsv_n_valid = h->h_ctl->n_pairs;
+  h->tsv_max_kid = h->h_ctl->max_start;
+  return (int64_t)h->tsv_n_valid;
+}
+
+// The profiling daemon's log of the same run: which launches of process `pid` ran alone (solo samples) and which in a
+// gang.  Applies to the text parsed last; rows the log does not mention are dropped.  Returns the rows that remain.
+int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags) {
+  if (!h || (!log_text && n_bytes) || (flags & ~KS_ON_DEVICE)) return -KS_ERR_ARG;
+  if (n_bytes >= (1ull << 40)) return fail(h, KS_ERR_TOO_LARGE, "ks_tsv_label: text of 2^40 bytes or more");
+  if (!h->tsv_dict.p) return fail(h, KS_ERR_ARG, "ks_tsv_label: no parsed text (ks_tsv_parse first)");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  const uint64_t n_lines = h->tsv_n_lines;
+  if (n_lines == 0) return 0;
+  const unsigned char* d_text = nullptr;
+  { int r = stage_in<unsigned char>(h, h->tsv_logtext, reinterpret_cast<const unsigned char*>(log_text), n_bytes, (flags & KS_ON_DEVICE) != 0, &d_text); if (r) return r; }
+  const uint64_t label_cap = h->tsv_max_kid + 1;
+  KS_ENSURE(h, h->tsv_label, label_cap);
+  KS_ENSURE(h, h->tsv_rowsolo, n_lines);
+  KS_CUDA(h, cudaMemsetAsync(h->tsv_label.p, 0, label_cap, h->stream));
+  if (n_bytes) {
+    // line starts of the log: the same three kernels, with buffers of their own and the line count in a free control word
+    const uint64_t ntiles = (n_bytes + kTsvTile - 1) / kTsvTile;
+    KS_ENSURE(h, h->tsv_logcnt, (ntiles + 1) * 4);
+    TsvArgs la{};
+    la.text = d_text;
+    la.n_bytes = n_bytes;
+    la.tile_cnt = as<uint32_t>(h->tsv_logcnt);
+    la.ctl = h->d_ctl;
+    const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 8);
+    k_tsv_nl_count<<<grid, 256, 0, h->stream>>>(la);
+    k_tsv_scan<<<1, 1024, 0, h->stream>>>(la.tile_cnt, ntiles, &h->d_ctl->batches_both, d_text, n_bytes);
+    { int r = read_ctl(h); if (r) return r; }
+    const uint64_t log_lines = h->h_ctl->batches_both;
+    KS_ENSURE(h, h->tsv_loglines, (log_lines + 2) * 8);
+    la.line_start = as<unsigned long long>(h->tsv_loglines);
+    la.max_lines = log_lines;
+    k_tsv_nl_fill<<<grid, 256, 0, h->stream>>>(la);
+    TsvLabelArgs lb{};
+    lb.text = d_text;
+    lb.n_bytes = n_bytes;
+    lb.line_start = la.line_start;
+    lb.n_lines = log_lines;
+    lb.pid = pid;
+    lb.label = as<unsigned char>(h->tsv_label);
+    lb.label_cap = label_cap;
+    const int pgrid = (int)std::max<uint64_t>(1, std::min<uint64_t>((log_lines + 255) / 256, (uint64_t)h->sm_count * 16));
+    k_pplog_parse<<<pgrid, 256, 0, h->stream>>>(lb);
+    h->launches += 4;
+  }
+  TsvArgs a = tsv_args(h);
+  const int lgrid = (int)std::max<uint64_t>(1, std::min<uint64_t>((n_lines + 255) / 256, (uint64_t)h->sm_count * 16));
+  const uint64_t vtiles = (n_lines + 255) / 256;
+  k_tsv_apply_labels<<<lgrid, 256, 0, h->stream>>>(a, as<unsigned char>(h->tsv_label), label_cap, as<unsigned char>(h->tsv_rowsolo));
+  k_tsv_valid_count<<<lgrid, 256, 0, h->stream>>>(a);
+  k_tsv_scan<<<1, 1024, 0, h->stream>>>(a.vtile_cnt, vtiles, &h->d_ctl->n_pairs, nullptr, 0);
+  h->launches += 3;
+  KS_CUDA(h, cudaGetLastError());
+  { int r = read_ctl(h); if (r) return r; }
+  h->tsv_n_valid = h->h_ctl->n_pairs;
+  h->tsv_labelled = true;
   return (int64_t)h->tsv_n_valid;
 }
 

@@ -42,7 +42,9 @@ struct TsvArgs {
   const uint32_t* name_map;      // k_tsv_finish: slot -> name id
   const uint32_t* model_map;     // slot -> tenant
   uint32_t solo;
-  Control* ctl;                  // scratch0 = lines, n_pairs = valid records
+  uint32_t* kernel_id;           // [lines] column 0 (the agent's running launch number), 0xFFFFFFFF if absent
+  const unsigned char* row_solo; // [lines] per-row solo flag from a pairprof log (ks_tsv_label), or null: `solo` for all
+  Control* ctl;                  // scratch0 = lines, n_pairs = valid records, max_start = largest kernel_id
 };
 
 __device__ __forceinline__ uint64_t fnv1a(const unsigned char* p, uint32_t n) {
@@ -197,13 +199,14 @@ __global__ void __launch_bounds__(256) k_tsv_parse(const TsvArgs a) {
     uint64_t fs = b;
     int col = 0;
     uint64_t name_off = 0;
-    uint32_t name_len = 0, model_slot = 0;
+    uint32_t name_len = 0, model_slot = 0, kid = 0xFFFFFFFFu;
     bool have_name = false, have_model = false, have_start = false, have_end = false, have_block = false, have_grid = false;
     for (uint64_t i = b; ok && i <= e; ++i) {
       if (i == e || a.text[i] == '\t') {
         const unsigned char* f = a.text + fs;
         const uint32_t fl = (uint32_t)(i - fs);
-        if (col == 8) { name_off = fs; name_len = fl; have_name = fl > 0; }
+        if (col == 0) { unsigned long long v; if (tsv_u64(f, fl, &v) && v < 0xFFFFFFFFull) kid = (uint32_t)v; }
+        else if (col == 8) { name_off = fs; name_len = fl; have_name = fl > 0; }
         else if (col == 9) have_start = tsv_u64(f, fl, reinterpret_cast<unsigned long long*>(&r.start_ns));
         else if (col == 10) have_end = tsv_u64(f, fl, reinterpret_cast<unsigned long long*>(&r.end_ns));
         else if (col == 14) have_block = tsv_dims(f, fl, r.block);
@@ -220,6 +223,59 @@ __global__ void __launch_bounds__(256) k_tsv_parse(const TsvArgs a) {
     }
     a.parsed[line] = r;
     a.valid[line] = ok ? 1 : 0;
+    a.kernel_id[line] = kid;
+    if (ok && kid != 0xFFFFFFFFu) atomicMax(&a.ctl->max_start, (unsigned long long)kid);
+  }
+}
+
+// ---- labels from the profiling daemon's log (profiling/pairprof_daemon.cpp:266 header, :317-318 rows):
+// batch_id, kind, pid, kernel_id, model, kernel, block, rep, grid -- one row per released kernel; kernel_id is the agent
+// log's kernel_id of process pid.  kind "alone" / "alone_other_waits" = the kernel had the GPU to itself (a solo sample),
+// "gang_profile" / "gang_filler" = released together with a kernel of the other model.
+struct TsvLabelArgs {
+  const unsigned char* text;
+  uint64_t n_bytes;
+  const unsigned long long* line_start;
+  uint64_t n_lines;
+  unsigned long long pid;
+  unsigned char* label;  // [label_cap] by kernel_id: 0 = not in the log, 1 = alone, 2 = gang
+  uint64_t label_cap;
+};
+
+__global__ void __launch_bounds__(256) k_pplog_parse(const TsvLabelArgs a) {
+  for (uint64_t line = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x + 1; line < a.n_lines; line += (uint64_t)gridDim.x * blockDim.x) {  // line 0: header
+    const uint64_t b = a.line_start[line];
+    uint64_t e = (line + 1 < a.n_lines || (a.n_bytes && a.text[a.n_bytes - 1] == '\n')) ? a.line_start[line + 1] - 1 : a.n_bytes;
+    if (e > b && a.text[e - 1] == '\r') --e;
+    uint64_t fs = b;
+    int col = 0;
+    unsigned char kind = 0;
+    unsigned long long pid = ~0ull, kid = ~0ull;
+    for (uint64_t i = b; i <= e && col <= 3; ++i) {
+      if (i == e || a.text[i] == '\t') {
+        const unsigned char* f = a.text + fs;
+        const uint32_t fl = (uint32_t)(i - fs);
+        if (col == 1) kind = (fl >= 5 && f[0] == 'a' && f[1] == 'l' && f[2] == 'o' && f[3] == 'n' && f[4] == 'e') ? 1 : (fl >= 4 && f[0] == 'g' && f[1] == 'a' && f[2] == 'n' && f[3] == 'g') ? 2 : 0;
+        else if (col == 2) { if (!tsv_u64(f, fl, &pid)) pid = ~0ull; }
+        else if (col == 3) { if (!tsv_u64(f, fl, &kid)) kid = ~0ull; }
+        fs = i + 1;
+        ++col;
+      }
+    }
+    if (kind && pid == a.pid && kid < a.label_cap) a.label[kid] = kind;
+  }
+}
+
+// rows the log does not mention are dropped (launches of the warm-up, which the profiler does not register); the others
+// get their own solo flag
+__global__ void __launch_bounds__(256) k_tsv_apply_labels(const TsvArgs a, const unsigned char* __restrict__ label, uint64_t label_cap, unsigned char* __restrict__ row_solo) {
+  const uint64_t n_lines = min(a.ctl->scratch0, (unsigned long long)a.max_lines);
+  for (uint64_t line = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; line < n_lines; line += (uint64_t)gridDim.x * blockDim.x) {
+    if (!a.valid[line]) continue;
+    const uint32_t kid = a.kernel_id[line];
+    const unsigned char lab = kid < label_cap ? label[kid] : 0;
+    if (!lab) a.valid[line] = 0;
+    row_solo[line] = lab == 1;
   }
 }
 
@@ -259,7 +315,8 @@ __global__ void __launch_bounds__(256) k_tsv_compact(const TsvArgs a) {
     if (v && pos < a.out_capacity) {
       ks_record r = a.parsed[i];
       r.name_id = a.name_map[r.name_id];
-      r.smem_word = (a.model_map[r.smem_word >> 24] << 24) | (a.solo ? kMetaSoloBit : 0u);
+      const bool solo = a.row_solo ? a.row_solo[i] != 0 : a.solo != 0;
+      r.smem_word = (a.model_map[r.smem_word >> 24] << 24) | (solo ? kMetaSoloBit : 0u);
       a.out[pos] = r;
     }
   }

@@ -2,10 +2,13 @@
 ``make_pair_eff.py`` (scheduler/scheduler_daemon.cpp:5, :193, :848) but does not ship.
 
     python -m kernel_scheduling_b200.make_pair_eff --corun a.tsv b.tsv [...] --solo sa.tsv sb.tsv [...] --out-dir DIR
+    python -m kernel_scheduling_b200.make_pair_eff --corun agent_<pid>_timing.tsv [...] --pairprof-log pairprof_log_<pid>.tsv --out-dir DIR
 
 Input: the 17-column logs the agent writes (scheduler/agent.cpp:692-705), one file per process; ``--solo`` files
 come from a one-kernel-at-a-time run (profiling/pairprof_daemon.cpp:46).  Rows without ``end_ns`` (no completion
-callback, agent.cpp:702) are dropped.  The logs are parsed on the GPU (``records_from_log``); ``TraceIngest.records``
+callback, agent.cpp:702) are dropped.  With ``--pairprof-log`` (the profiling daemon's own log of the run,
+pairprof_daemon.cpp:266, :317-318) every launch is labelled by it instead: kind ``alone*`` = a solo sample, ``gang*`` =
+a co-run launch, not mentioned (warm-up) = dropped; the process id comes from the agent log's file name.  The logs are parsed on the GPU (``records_from_log``); ``TraceIngest.records``
 is the same ingest from a pandas frame.  Kernel symbols are reduced to their short names (kernel_key.hpp) and
 numbered; the ``model`` column is the tenant.
 
@@ -66,23 +69,53 @@ class TraceIngest:
         ids = {sym: self.name_id(sym) for sym in symbols.unique()}
         return symbols.map(ids).to_numpy(dtype=np.uint32)
 
-    def records(self, frame: pd.DataFrame, solo: bool) -> np.ndarray:
+    def records(self, frame: pd.DataFrame, solo: bool, pairprof: pd.DataFrame | None = None, pid: int | None = None) -> np.ndarray:
+        """``pairprof`` (the profiling daemon's log as a frame) with ``pid``: the solo flag is per launch, from the log's
+        ``kind`` of (pid, kernel_id); launches the log does not mention are dropped.  Names and models are numbered over
+        all launches with an ``end_ns``, dropped or not (as the device route does)."""
         f = frame[frame["end_ns"].notna()]
-        tenants = [self.tenant_id(m) for m in f["model"].astype(str)]
+        tenants = np.array([self.tenant_id(m) for m in f["model"].astype(str)], dtype=np.uint32)
+        name_ids = self._name_ids(f["kernel_name"])
+        solo_col = np.full(len(f), solo)
+        keep = np.ones(len(f), dtype=bool)
+        if pairprof is not None:
+            mine = pairprof[pairprof["pid"] == pid]
+            kind = dict(zip(mine["kernel_id"].astype(np.int64), mine["kind"].astype(str)))
+            kinds = [kind.get(int(k), "") for k in f["kernel_id"]]
+            keep = np.array([k.startswith(("alone", "gang")) for k in kinds], dtype=bool)
+            solo_col = np.array([k.startswith("alone") for k in kinds], dtype=bool)
+        f = f[keep]
         n = len(f)
         return pack_records(
-            self._name_ids(f["kernel_name"]), _dims(f["grid"]), _dims(f["block"]), np.zeros(n, np.uint32), np.array(tenants, dtype=np.uint32),
-            np.full(n, solo), f["start_ns"].to_numpy(dtype=np.uint64), f["end_ns"].to_numpy(dtype=np.uint64))
+            name_ids[keep], _dims(f["grid"]), _dims(f["block"]), np.zeros(n, np.uint32), tenants[keep],
+            solo_col[keep], f["start_ns"].to_numpy(dtype=np.uint64), f["end_ns"].to_numpy(dtype=np.uint64))
 
 
-def records_from_log(ing: "TraceIngest", builder: PairTableBuilder, path_or_bytes, solo: bool) -> np.ndarray:
+def agent_pid(path) -> int | None:
+    """The process id in an agent log's file name (``agent_<pid>_timing.tsv``, scheduler/agent.cpp:692), or None."""
+    m = re.search(r"agent_(\d+)_timing", os.path.basename(str(path)))
+    return int(m.group(1)) if m else None
+
+
+def _text_of(path_or_bytes) -> np.ndarray:
+    return np.fromfile(path_or_bytes, dtype=np.uint8) if isinstance(path_or_bytes, (str, os.PathLike)) else np.frombuffer(path_or_bytes, dtype=np.uint8)
+
+
+def records_from_log(ing: "TraceIngest", builder: PairTableBuilder, path_or_bytes, solo: bool, pairprof_log=None, pid: int | None = None) -> np.ndarray:
     """One agent timing log -> launch records, parsed on the GPU (``ks_tsv_parse``): line splitting, tab walking, number
     and dimension parsing and the string dictionaries run on the device; the host only canonicalises each DISTINCT kernel
     symbol (``ks_function_base``) and numbers names and models in their order of first appearance -- the same ids the
-    pandas route (``TraceIngest.records``) assigns."""
-    text = np.fromfile(path_or_bytes, dtype=np.uint8) if isinstance(path_or_bytes, (str, os.PathLike)) else np.frombuffer(path_or_bytes, dtype=np.uint8)
+    pandas route (``TraceIngest.records``) assigns.  ``pairprof_log`` (path or bytes of the profiling daemon's log) with
+    ``pid``: that log, parsed on the device too (``ks_tsv_label``), decides per launch between solo sample, co-run launch
+    and dropped."""
+    text = _text_of(path_or_bytes)
     lib, h = builder._lib, builder._h
     n = builder._check(lib.ks_tsv_parse(h, _lib.ptr(text), len(text), 0), "ks_tsv_parse")
+    if pairprof_log is not None:
+        if pid is None:
+            raise ValueError("pid is required with a pairprof log")
+        log = _text_of(pairprof_log)
+        n = builder._check(lib.ks_tsv_label(h, _lib.ptr(log), len(log), int(pid), 0), "ks_tsv_label")
     maps = []
     for which, slots in ((0, 65536), (1, 256)):
         hashes, where = np.zeros(slots, dtype=np.uint64), np.zeros(slots, dtype=np.uint64)
@@ -142,11 +175,18 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--corun", nargs="+", required=True)
     ap.add_argument("--solo", nargs="*", default=[])
+    ap.add_argument("--pairprof-log", default=None, help="pairprof_log_<pid>.tsv of the run that wrote the --corun logs: labels every launch")
     ap.add_argument("--out-dir", default=".")
     args = ap.parse_args(argv)
     ing = TraceIngest()
     with PairTableBuilder() as b:
-        parts = [records_from_log(ing, b, p, solo=False) for p in args.corun]
+        if args.pairprof_log:
+            pids = [agent_pid(p) for p in args.corun]
+            if None in pids:
+                ap.error("--pairprof-log needs agent logs named agent_<pid>_timing.tsv")
+            parts = [records_from_log(ing, b, p, solo=False, pairprof_log=args.pairprof_log, pid=pid) for p, pid in zip(args.corun, pids)]
+        else:
+            parts = [records_from_log(ing, b, p, solo=False) for p in args.corun]
         parts += [records_from_log(ing, b, p, solo=True) for p in args.solo]
         rec = np.concatenate(parts)
         us, eff = write_tables(args.out_dir, build_tables(rec, b), ing.names, ing.models)

@@ -93,3 +93,69 @@ def test_device_tsv_parse_equals_pandas_ingest(builder, tmp_path):
     assert M.records_from_log(ing_b, builder, raw.rstrip(b"\n"), False).tobytes() == want.tobytes()
     assert M.records_from_log(ing_b, builder, raw.replace(b"\n", b"\r\n"), False).tobytes() == want.tobytes()
     assert len(M.records_from_log(ing_b, builder, raw.split(b"\n")[0] + b"\n", False)) == 0
+
+
+def _one_run_with_pairprof_log(n, tmp_path):
+    """One profiling run as the reference leaves it on disk: an agent log per process holding ALL its launches (solo and
+    gang, numbered by kernel_id) and the daemon's log that says which was which (pairprof_daemon.cpp:266, :317-318)."""
+    rec, frames = synthetic_timing_frames(n)
+    pids = {"qwen": 4101, "whisper": 4102}
+    rng = np.random.default_rng(11)
+    agent_paths, log_rows = {}, []
+    for model, pid in pids.items():
+        both = pd.concat([frames[(model, False)].assign(_solo=False), frames[(model, True)].assign(_solo=True)]).sort_values("start_ns", kind="stable").reset_index(drop=True)
+        both["kernel_id"] = np.arange(len(both)) + 7  # the agent's running number does not start at 0 after the warm-up
+        unlisted = rng.random(len(both)) < 0.05        # launches the profiler never registered (warm-up): dropped
+        for i, row in both.iterrows():
+            if unlisted[i]:
+                continue
+            kind = ("alone" if i % 3 else "alone_other_waits") if row["_solo"] else ("gang_profile" if i % 2 else "gang_filler")
+            block = row["block"].strip("()").replace(" ", "")
+            log_rows.append((i + 1, kind, pid, int(row["kernel_id"]), model, "k", block, "1" if kind == "gang_profile" else "", "1,1,1"))
+            # a row of ANOTHER process with the same kernel_id and the opposite kind must not label this launch
+            if i % 50 == 0:
+                log_rows.append((i + 1, "gang_filler" if row["_solo"] else "alone", 9999, int(row["kernel_id"]), model, "k", block, "", "1,1,1"))
+        p = str(tmp_path / f"agent_{pid}_timing.tsv")
+        both.drop(columns="_solo").to_csv(p, sep="\t", index=False)
+        agent_paths[model] = p
+    log = pd.DataFrame(log_rows, columns=["batch_id", "kind", "pid", "kernel_id", "model", "kernel", "block", "rep", "grid"])
+    log_path = str(tmp_path / "pairprof_log_77.tsv")
+    log.to_csv(log_path, sep="\t", index=False)
+    return pids, agent_paths, log_path
+
+
+def test_pairprof_log_labels_on_the_device_equal_the_pandas_route(builder, tmp_path):
+    pids, agent_paths, log_path = _one_run_with_pairprof_log(6000, tmp_path)
+    log = pd.read_csv(log_path, sep="\t")
+    ing_a, ing_b = M.TraceIngest(), M.TraceIngest()
+    total = 0
+    for model, pid in pids.items():
+        want = ing_a.records(pd.read_csv(agent_paths[model], sep="\t"), False, pairprof=log, pid=pid)
+        got = M.records_from_log(ing_b, builder, agent_paths[model], False, pairprof_log=log_path, pid=pid)
+        assert len(got) == len(want) and got.tobytes() == want.tobytes(), model
+        solo = (want["smem_word"] >> 23) & 1
+        assert 0 < solo.sum() < len(want)  # both kinds present
+        total += len(want)
+    assert ing_a.names == ing_b.names and ing_a.models == ing_b.models
+    assert M.agent_pid(agent_paths["qwen"]) == 4101
+    # CRLF log, and a log that mentions nothing of this process: every launch is dropped
+    raw = open(log_path, "rb").read()
+    again = M.records_from_log(M.TraceIngest(), builder, agent_paths["qwen"], False, pairprof_log=raw.replace(b"\n", b"\r\n"), pid=4101)
+    assert len(again) == len(ing_a.records(pd.read_csv(agent_paths["qwen"], sep="\t"), False, pairprof=log, pid=4101))
+    assert len(M.records_from_log(M.TraceIngest(), builder, agent_paths["qwen"], False, pairprof_log=raw, pid=1)) == 0
+
+
+def test_make_pair_eff_cli_with_pairprof_log(tmp_path):
+    pids, agent_paths, log_path = _one_run_with_pairprof_log(5000, tmp_path)
+    out = str(tmp_path / "out")
+    assert M.main(["--corun", agent_paths["qwen"], agent_paths["whisper"], "--pairprof-log", log_path, "--out-dir", out]) == 0
+    log = pd.read_csv(log_path, sep="\t")
+    ing = M.TraceIngest()
+    r2 = np.concatenate([ing.records(pd.read_csv(agent_paths[m], sep="\t"), False, pairprof=log, pid=pids[m]) for m in ("qwen", "whisper")])
+    tables = [(*oracle_tables_as_rows(r2, O.KEY_SHAPE), False), (*oracle_tables_as_rows(r2, O.KEY_TYPE), True)]
+    want = str(tmp_path / "want")
+    M.write_tables(want, tables, ing.names, ing.models)
+    assert open(os.path.join(out, "kernel_us.tsv")).read() == open(os.path.join(want, "kernel_us.tsv")).read()
+    got_eff, want_eff = pd.read_csv(os.path.join(out, "pair_eff.tsv"), sep="\t"), pd.read_csv(os.path.join(want, "pair_eff.tsv"), sep="\t")
+    exact = [c for c in got_eff.columns if "mean" not in c]
+    assert got_eff[exact].equals(want_eff[exact])

@@ -113,3 +113,19 @@ def test_reference_daemon_loads_the_emitted_tables(tmp_path):
     n_us = int(np.isfinite(tables[0][0]["solo_ns"]).sum()) + int(np.isfinite(tables[1][0]["solo_ns"]).sum())
     assert (int(m.group(1)), int(m.group(2)), int(m.group(3))) == (n_type, n_shape, n_us)
     assert "WARNING" not in line
+
+
+def test_pairprof_labels_in_the_pandas_ingest():
+    """The host-side meaning of a pairprof log: alone* = solo sample, gang* = co-run launch, not mentioned = dropped."""
+    from kernel_scheduling_b200 import make_pair_eff as M
+
+    _, frames = synthetic_timing_frames(600)
+    f = frames[("qwen", False)].copy().reset_index(drop=True)
+    f["kernel_id"] = np.arange(len(f)) + 3
+    log = pd.DataFrame({"batch_id": 1, "kind": ["alone", "gang_profile", "alone_other_waits", "gang_filler", "alone"], "pid": [5, 5, 5, 5, 6],
+                        "kernel_id": [3, 4, 5, 6, 7], "model": "qwen", "kernel": "k", "block": "1,1,1", "rep": "", "grid": "1,1,1"})
+    rec = M.TraceIngest().records(f, False, pairprof=log, pid=5)
+    assert len(rec) == 4  # kernel_id 7 belongs to another process, the rest of the file is not mentioned
+    assert list((rec["smem_word"] >> 23) & 1) == [1, 0, 1, 0]
+    assert list(rec["start_ns"]) == list(f["start_ns"][:4])
+    assert M.agent_pid("/x/agent_123_timing.tsv") == 123 and M.agent_pid("a.tsv") is None
