@@ -173,6 +173,13 @@ int64_t ks_count_batches(ks_handle* h, const uint64_t* start1, uint64_t n1, cons
 int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double* launches, const double* values, uint64_t rows, uint32_t cols,
                               uint32_t n_groups, uint32_t flags, double* out_total, double* out_means);
 
+/* profiling/ncu-bench/ncu_summary.py:185-245, the pooling of per-launch profiler metrics: per group (the host maps
+ * (kernel name, block) to dense ids) the number of launches, and per column the mean and the SAMPLE standard deviation
+ * (:239-240: statistics.mean, statistics.stdev, 0 for a single value) over the launches that have the metric (NaN =
+ * absent; a column no launch of the group has gives NaN, the script's None).  values: rows x cols, row major. */
+int64_t ks_pool_launches(ks_handle* h, const uint32_t* group, const double* values, uint64_t rows, uint32_t cols, uint32_t n_groups, uint32_t flags,
+                         uint64_t* out_launches, double* out_mean, double* out_std);
+
 /* ---- multi-GPU session: one process and one handle per GPU, each owning one window of the start-ordered trace.
  * The reference has no multi-GPU path; these phases are what kernel_scheduling_b200/parallel.py runs between its
  * collectives (all-gather of keys, sum of counts, all-to-all of samples, all-gather of solo times and table shards).

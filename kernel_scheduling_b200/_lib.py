@@ -67,6 +67,7 @@ KS_API = [
     ("ks_segment_stats", [c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p], c_int64),
     ("ks_count_batches", [c_void_p, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(c_uint64)], c_int64),
     ("ks_combine_duplicates", [c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p], c_int64),
+    ("ks_pool_launches", [c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p], c_int64),
     ("ks_mg_begin", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_mg_tail", [c_void_p, c_void_p, c_uint64], c_int64),
     ("ks_mg_halo", [c_void_p, c_void_p, c_uint64], c_int64),

@@ -1045,6 +1045,54 @@ int64_t ks_combine_duplicates(ks_handle* h, const uint32_t* group, const double*
   return (int64_t)n_groups;
 }
 
+int64_t ks_pool_launches(ks_handle* h, const uint32_t* group, const double* values, uint64_t rows, uint32_t cols, uint32_t n_groups, uint32_t flags,
+                         uint64_t* out_launches, double* out_mean, double* out_std) {
+  if (!h || (!group && rows) || (!values && rows && cols) || (n_groups && (!out_launches || ((!out_mean || !out_std) && cols)))) return -KS_ERR_ARG;
+  if (rows >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_pool_launches: too many rows");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n_groups == 0) return 0;
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  { int r = reset_run(h); if (r) return r; }
+  // sort row indices by group (stable) -> order[]
+  const size_t rb = std::max<size_t>(rows * 4, 16);
+  DevBuf* t = h->tmp;
+  KS_ENSURE(h, t[0], rb); KS_ENSURE(h, t[1], rb); KS_ENSURE(h, t[2], rb); KS_ENSURE(h, t[3], rb);
+  uint32_t* k[2] = {as<uint32_t>(t[0]), as<uint32_t>(t[1])};
+  uint32_t* v[2][1] = {{as<uint32_t>(t[2])}, {as<uint32_t>(t[3])}};
+  if (rows) {
+    KS_CUDA(h, cudaMemcpyAsync(k[0], group, rows * 4, dev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    k_iota<<<(unsigned)((rows + 255) / 256), 256, 0, h->stream>>>(v[0][0], (uint32_t)rows);
+  }
+  const int cur = radix_sort<uint32_t, uint32_t, 1, 16>(h, k, v, rows, nullptr, 0, bit_length(n_groups ? n_groups - 1 : 0));
+  if (cur < 0) return cur;
+  KS_ENSURE(h, t[4], ((size_t)n_groups + 2) * 4);
+  uint32_t* seg = as<uint32_t>(t[4]);
+  k_group_offsets<<<(unsigned)((rows + 1 + 255) / 256), 256, 0, h->stream>>>(k[cur], (uint32_t)rows, n_groups, seg);
+  const double* d_v = nullptr;
+  { int r = stage_in<double>(h, h->tl_start[1], values, rows * cols, dev, &d_v); if (r) return r; }
+  unsigned long long* d_cnt = reinterpret_cast<unsigned long long*>(out_launches);
+  double *d_mean = out_mean, *d_std = out_std;
+  if (!dev) {
+    KS_ENSURE(h, t[5], ((size_t)n_groups * (2 * (size_t)cols + 1)) * 8 + 16);
+    d_cnt = as<unsigned long long>(t[5]);
+    d_mean = reinterpret_cast<double*>(d_cnt + n_groups);
+    d_std = d_mean + (size_t)n_groups * cols;
+  }
+  const uint64_t threads = (uint64_t)n_groups * (cols + 1);
+  k_pool_launches<<<(unsigned)((threads + 255) / 256), 256, 0, h->stream>>>(v[cur][0], seg, d_v, cols, n_groups, d_cnt, d_mean, d_std);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  if (!dev) {
+    { int r = copy_out(h, out_launches, d_cnt, (size_t)n_groups * 8, false); if (r) return r; }
+    { int r = copy_out(h, out_mean, d_mean, (size_t)n_groups * cols * 8, false); if (r) return r; }
+    { int r = copy_out(h, out_std, d_std, (size_t)n_groups * cols * 8, false); if (r) return r; }
+  }
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, false);
+  if (st) return fail(h, st, std::string("ks_pool_launches: ") + ks_status_string(st));
+  return (int64_t)n_groups;
+}
+
 }  // extern "C"
 
 // =========================================================================================================

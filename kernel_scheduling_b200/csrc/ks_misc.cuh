@@ -102,6 +102,47 @@ __global__ void __launch_bounds__(256) k_combine_duplicates(const uint32_t* __re
   out_means[(uint64_t)g * cols + c] = any ? ws / wt : __longlong_as_double(0x7FF8000000000000ll);
 }
 
+// Pooling of per-launch profiler metrics (profiling/ncu-bench/ncu_summary.py:185-245): per group and column the mean and
+// the SAMPLE standard deviation (n - 1; 0 for a single value) over the cells that hold a value (NaN = the launch has no
+// such metric), and the number of launches of the group.  One thread per (group, column); two passes (mean, then
+// squared deviations from it), both compensated.
+__global__ void __launch_bounds__(256) k_pool_launches(const uint32_t* __restrict__ order, const uint32_t* __restrict__ seg, const double* __restrict__ values,
+                                                       uint32_t cols, uint32_t n_groups, unsigned long long* __restrict__ out_launches,
+                                                       double* __restrict__ out_mean, double* __restrict__ out_std) {
+  const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (uint64_t)n_groups * (cols + 1)) return;
+  const uint32_t g = (uint32_t)(t / (cols + 1)), c = (uint32_t)(t % (cols + 1));
+  const uint32_t r0 = seg[g], r1 = seg[g + 1];
+  if (c == cols) { out_launches[g] = r1 - r0; return; }
+  const double nan = __longlong_as_double(0x7FF8000000000000ll);
+  double s = 0.0, comp = 0.0;
+  uint32_t n = 0;
+  for (uint32_t r = r0; r < r1; ++r) {
+    const double v = values[(uint64_t)order[r] * cols + c];
+    if (v != v) continue;
+    ++n;
+    const double y = v - comp, tt = s + y;
+    comp = (tt - s) - y;
+    s = tt;
+  }
+  if (n == 0) { out_mean[(uint64_t)g * cols + c] = nan; out_std[(uint64_t)g * cols + c] = nan; return; }
+  const double mean = s / (double)n;
+  double ss = 0.0, d1 = 0.0;
+  comp = 0.0;
+  for (uint32_t r = r0; r < r1; ++r) {
+    const double v = values[(uint64_t)order[r] * cols + c];
+    if (v != v) continue;
+    const double d = v - mean;
+    d1 += d;  // the residual of the rounded mean, for the correction below
+    const double y = d * d - comp, tt = ss + y;
+    comp = (tt - ss) - y;
+    ss = tt;
+  }
+  ss -= d1 * d1 / (double)n;
+  out_mean[(uint64_t)g * cols + c] = mean;
+  out_std[(uint64_t)g * cols + c] = n > 1 ? sqrt(fmax(ss, 0.0) / (double)(n - 1)) : 0.0;
+}
+
 __global__ void __launch_bounds__(256) k_iota(uint32_t* v, uint32_t n) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) v[i] = i;

@@ -180,3 +180,17 @@ class PairTableBuilder:
             "ks_combine_duplicates",
         )
         return total, means
+
+    def pool_launches(self, group: np.ndarray, values: np.ndarray, n_groups: int):
+        """-> (launches [n_groups] uint64, mean [n_groups, cols], sample std [n_groups, cols]); NaN cells are absent values."""
+        group = np.ascontiguousarray(group, dtype=np.uint32)
+        values = np.ascontiguousarray(values, dtype=np.float64).reshape(len(group), -1)
+        cols = values.shape[1]
+        launches = np.zeros(n_groups, dtype=np.uint64)
+        mean = np.zeros((n_groups, cols), dtype=np.float64)
+        std = np.zeros((n_groups, cols), dtype=np.float64)
+        self._check(
+            self._lib.ks_pool_launches(self._h, _lib.ptr(group), _lib.ptr(values), len(group), cols, n_groups, 0, _lib.ptr(launches), _lib.ptr(mean), _lib.ptr(std)),
+            "ks_pool_launches",
+        )
+        return launches, mean, std

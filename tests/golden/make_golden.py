@@ -110,7 +110,53 @@ def function_base_cases():
     print("function_base", len(r.stdout.splitlines()), "symbols")
 
 
+def ncu_pool_case():
+    """Per-launch label values of real Nsight Compute reports, extracted with the reference script's own helpers, and the
+    summary CSV the reference script writes for the same reports (profiling/ncu-bench/ncu_summary.py).  The reports are
+    named in KS_NCU_REPORTS (os.pathsep separated); without it the committed fixtures are left alone."""
+    reports = [p for p in os.environ.get("KS_NCU_REPORTS", "").split(os.pathsep) if p]
+    if not reports:
+        print("ncu_pool_case: KS_NCU_REPORTS not set, fixtures unchanged")
+        return
+    import importlib.util
+    import math
+
+    script = REF / "profiling" / "ncu-bench" / "ncu_summary.py"
+    spec = importlib.util.spec_from_file_location("ref_ncu_summary", script)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    ncu_report = ref.import_ncu_report(None)
+    labels = [ref.RATIO_LABEL, ref.BPW_LABEL] + list(ref.METRICS)
+    rows = []
+    for path in reports:
+        ctx = ncu_report.load_report(path)
+        for i in range(ctx.num_ranges()):
+            rng = ctx.range_by_idx(i)
+            for j in range(rng.num_actions()):
+                action = rng.action_by_idx(j)
+                row = {"Kernel": action.name(), "Block": ref.fmt_dims(ref.get_dims(action, "block"))}
+                dur_us = ref.get_value(action, ref.DURATION_METRIC)
+                grid = ref.get_dims(action, "grid")
+                waves = ref.get_waves(action, grid, None)
+                grid_total = ref.get_value(action, "launch__grid_size")
+                if grid_total is None and grid:
+                    grid_total = math.prod(grid)
+                row["duration_us"], row["waves"], row["grid_total"] = dur_us, waves, grid_total
+                for label, candidates in ref.METRICS.items():
+                    for metric in candidates:
+                        v = ref.get_value(action, metric)
+                        if v is not None:
+                            row[label] = v
+                            break
+                rows.append(row)
+    frame = pd.DataFrame(rows, columns=["Kernel", "Block", "duration_us", "waves", "grid_total"] + list(ref.METRICS))
+    frame.to_csv(HERE / "ncu_launches.csv", index=False, float_format="%.17g")
+    subprocess.run([sys.executable, str(script), *reports, "--csv", str(HERE / "ncu_summary_ref.csv")], check=True, capture_output=True)
+    print(f"ncu_pool_case: {len(frame)} launches, labels {labels}")
+
+
 if __name__ == "__main__":
     postprocess_cases()
     combine_cases()
     function_base_cases()
+    ncu_pool_case()

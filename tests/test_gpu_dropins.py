@@ -159,3 +159,39 @@ def test_make_pair_eff_cli_with_pairprof_log(tmp_path):
     got_eff, want_eff = pd.read_csv(os.path.join(out, "pair_eff.tsv"), sep="\t"), pd.read_csv(os.path.join(want, "pair_eff.tsv"), sep="\t")
     exact = [c for c in got_eff.columns if "mean" not in c]
     assert got_eff[exact].equals(want_eff[exact])
+
+
+def test_ncu_pooling_on_the_device(builder, tmp_path):
+    from kernel_scheduling_b200 import ncu_summary as N
+    from tests.test_oracle_golden import _ncu_pool_inputs
+
+    # real reports: the frame the reference script would pool, against the CSV it wrote
+    frame, ref = _ncu_pool_inputs()
+    got = N.pool_launches(frame, builder)
+    assert list(got.columns) == list(ref.columns)
+    assert list(got["Kernel"]) == list(ref["Kernel"]) and list(got["Block"]) == list(ref["Block"]) and list(got["Launches"]) == list(ref["Launches"])
+    for c in ref.columns[3:]:
+        assert np.allclose(got[c].to_numpy(), ref[c].to_numpy(dtype=np.float64), rtol=1e-12, atol=0, equal_nan=True), c
+    # CLI round trip
+    src, dst = str(tmp_path / "launches.csv"), str(tmp_path / "summary.csv")
+    frame.to_csv(src, index=False, float_format="%.17g")
+    assert N.main([src, dst]) == 0
+    again = pd.read_csv(dst, float_precision="round_trip")
+    assert np.allclose(again[ref.columns[3:]].to_numpy(), ref[ref.columns[3:]].to_numpy(dtype=np.float64), rtol=1e-12, atol=0, equal_nan=True)
+
+    # synthetic: thousands of launches, groups from 1 to 4,000 launches, absent cells, a constant column, a large offset
+    rng = np.random.default_rng(5)
+    rows, cols, groups = 30_000, 6, 200
+    gid = np.minimum((rng.pareto(0.7, rows)).astype(np.int64), groups - 1).astype(np.uint32)
+    gid[:groups] = np.arange(groups)  # every group has at least one launch
+    values = rng.normal(50.0, 10.0, (rows, cols))
+    values[:, 1] = 7.25                                  # constant: std exactly 0
+    values[:, 2] += 1e9                                  # large mean, small spread
+    values[rng.random((rows, cols)) < 0.2] = np.nan      # absent metrics
+    values[gid == 3, 4] = np.nan                         # a label no launch of the group has
+    launches, mean, std = builder.pool_launches(gid, values, groups)
+    ol, om, os_ = O.pool_launches(gid, values, groups)
+    assert list(launches) == list(ol)
+    assert np.allclose(mean, om, rtol=1e-13, atol=0, equal_nan=True)
+    assert np.allclose(std, os_, rtol=1e-9, atol=1e-12, equal_nan=True)  # sample std of n values: conditioning ~ mean / spread
+    assert np.all(std[:, 1][~np.isnan(std[:, 1])] == 0.0) and np.isnan(mean[3, 4]) and np.isnan(std[3, 4])

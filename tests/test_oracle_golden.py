@@ -102,3 +102,34 @@ def test_trace_generator_shapes():
         assert (rec["start_ns"][m][1:] >= rec["end_ns"][m][:-1]).all()
     k, p = O.build_pair_table(rec, check_bijection=False)
     assert len(k["key"]) <= 2000 and 0.3 < p["count"].sum() / len(rec) < 0.7
+
+
+def _ncu_pool_inputs():
+    """Per-launch values of real Nsight Compute reports (extracted with the reference script's helpers) -> the label
+    frame the pooling takes, and the summary CSV the reference script wrote for the same reports."""
+    import pandas as pd
+
+    from kernel_scheduling_b200 import ncu_summary as N
+
+    launches = pd.read_csv(os.path.join(GOLDEN, "ncu_launches.csv"), float_precision="round_trip")
+    ref = pd.read_csv(os.path.join(GOLDEN, "ncu_summary_ref.csv"), float_precision="round_trip")  # the default parser is off by an ulp now and then
+    bpw, ratio = N.per_launch_labels(launches["duration_us"], launches["waves"], launches["grid_total"])
+    frame = launches[["Kernel", "Block"]].copy()
+    frame[N.RATIO_LABEL] = ratio
+    frame[N.BPW_LABEL] = bpw
+    for c in launches.columns[5:]:
+        frame[c] = launches[c]
+    return frame, ref
+
+
+def test_pooling_oracle_equals_the_reference_script_on_real_reports():
+    frame, ref = _ncu_pool_inputs()
+    labels = [c for c in frame.columns if c not in ("Kernel", "Block")]
+    assert [c for c in ref.columns[3:]] == [x for l in labels for x in (l, f"{l} std")]
+    keys = list(zip(ref["Kernel"], ref["Block"]))  # the reference's group order
+    gid = np.array([keys.index(kb) for kb in zip(frame["Kernel"], frame["Block"])])
+    launches, mean, std = O.pool_launches(gid, frame[labels].to_numpy(dtype=np.float64), len(keys))
+    assert list(launches) == list(ref["Launches"])
+    for j, l in enumerate(labels):
+        assert np.array_equal(mean[:, j], ref[l].to_numpy(dtype=np.float64), equal_nan=True), l
+        assert np.array_equal(std[:, j], ref[f"{l} std"].to_numpy(dtype=np.float64), equal_nan=True), l
