@@ -38,6 +38,13 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     window2 = torch.from_numpy(rec2[lo2:hi2].view(np.uint8).reshape(-1).copy()).cuda()
     torch.cuda.synchronize()
     skeys, spairs = session.build(window2, key_type=True)
+    # ragged windows: three launches over two ranks, then one launch (the second rank's window is empty)
+    tiny_tables = []
+    for m in (3, 1):
+        lo3, hi3 = parallel.split_windows(m, world)[rank]
+        w3 = torch.from_numpy(rec[:m][lo3:hi3].view(np.uint8).reshape(-1).copy()).cuda()
+        torch.cuda.synchronize()
+        tiny_tables.append(session.build(w3))
     peer_memory = session.peer_memory
     # a bad record in the LAST rank's window: every rank gets the same status from the same call, nobody is left waiting,
     # and the session works afterwards
@@ -61,5 +68,5 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     ckeys, cpairs = session.build(window)
     session.close()
 np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs, ckeys=ckeys, cpairs=cpairs,
-         peer_memory=peer_memory, bad_status=status)
+         peer_memory=peer_memory, bad_status=status, t3keys=tiny_tables[0][0], t3pairs=tiny_tables[0][1], t1keys=tiny_tables[1][0], t1pairs=tiny_tables[1][1])
 dist.destroy_process_group()

@@ -95,6 +95,8 @@ def test_two_nccl_ranks(tmp_path):
         assert d["ckeys"].tobytes() == d["keys"].tobytes() and d["cpairs"].tobytes() == d["pairs"].tobytes()
         print("peer memory:", bool(d["peer_memory"]))
         assert int(d["bad_status"]) == 3  # KS_ERR_RECORD on BOTH ranks, although only the last rank's window held the bad record
+        assert_tables_match(d["t3keys"], d["t3pairs"], *O.build_pair_table(rec[:3]))  # ragged windows
+        assert_tables_match(d["t1keys"], d["t1pairs"], *O.build_pair_table(rec[:1]))  # an empty window on the second rank
 
 
 @pytest.mark.parametrize("cfg,n,key_type", [("c1", 60_000, False), ("c2", 300_000, True), ("c1", 0, False)])
