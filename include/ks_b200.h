@@ -247,6 +247,21 @@ int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* w
 int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags);
 int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags);
 
+/* The kernel key of one launch shape, on the host: bit for bit what the device computes for a record with these fields
+ * (flags: KS_KEY_TYPE or 0).  For programs that look keys up in a finished table (include/ks_pairtab_shm.h). */
+uint64_t ks_kernel_key(uint32_t name_id, const uint32_t grid[3], const uint32_t block[3], uint32_t smem, uint32_t tenant, uint32_t flags);
+
+/* The pair table in a POSIX shared-memory segment (layout and reader: include/ks_pairtab_shm.h; the reference keeps its
+ * table in a string-keyed map filled from pair_eff.tsv, scheduler_daemon.cpp:230-274).  Host code, HOST arrays: the key
+ * rows and pair rows of a SHAPE table and of a TYPE table as ks_copy_key_rows / ks_copy_pair_rows return them, and the
+ * strings behind name ids and tenants.  Written to "<name>.tmp", then renamed over "<name>".  Returns the bytes of the
+ * image, or -KS_ERR_ARG (ks_pairtab_last_error says why). */
+int64_t ks_pairtab_publish(const char* shm_name, const ks_key_row* shape_keys, uint64_t n_shape_keys, const ks_pair_row* shape_pairs, uint64_t n_shape_rows,
+                           const ks_key_row* type_keys, uint64_t n_type_keys, const ks_pair_row* type_pairs, uint64_t n_type_rows, const char* const* names,
+                           uint64_t n_names, const char* const* models, uint64_t n_models, uint64_t generation);
+int ks_pairtab_unlink(const char* shm_name);
+const char* ks_pairtab_last_error(void);
+
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
  * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */
 int64_t ks_function_base(const char* symbol, char* out, uint64_t capacity);

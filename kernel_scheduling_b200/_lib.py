@@ -91,6 +91,11 @@ KS_API = [
     ("ks_tsv_label", [c_void_p, c_void_p, c_uint64, c_uint64, c_uint32], c_int64),
     ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),
+    ("ks_kernel_key", [c_uint32, POINTER(c_uint32), POINTER(c_uint32), c_uint32, c_uint32, c_uint32], c_uint64),
+    ("ks_pairtab_publish", [c_char_p, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(c_char_p), c_uint64,
+                            POINTER(c_char_p), c_uint64, c_uint64], c_int64),
+    ("ks_pairtab_unlink", [c_char_p], c_int),
+    ("ks_pairtab_last_error", [], c_char_p),
 ]
 
 _lib = None

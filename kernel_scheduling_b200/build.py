@@ -13,7 +13,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libks_b200.so"
-SOURCES = [CSRC / "ks_api.cu", CSRC / "ks_names.cpp"]
+SOURCES = [CSRC / "ks_api.cu", CSRC / "ks_names.cpp", CSRC / "ks_pairtab.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
@@ -21,6 +21,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-shared",
     "--expt-relaxed-constexpr",
     "-ldl",  # NCCL is bound at run time (dlopen)
+    "-lrt",  # shm_open (the shared-memory pair table)
 ]
 
 

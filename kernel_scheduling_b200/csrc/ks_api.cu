@@ -607,6 +607,11 @@ void ks_destroy(ks_handle* h) {
   delete h;
 }
 
+uint64_t ks_kernel_key(uint32_t name_id, const uint32_t grid[3], const uint32_t block[3], uint32_t smem, uint32_t tenant, uint32_t flags) {
+  const uint32_t smem_word = (smem & kSmemMask) | (tenant << 24);
+  return kernel_key(name_id, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem_word, (flags & KS_KEY_TYPE) != 0);
+}
+
 const char* ks_last_error(ks_handle* h) { return h ? h->last_error.c_str() : g_null_error.c_str(); }
 void* ks_stream(ks_handle* h) { return h ? reinterpret_cast<void*>(h->stream) : nullptr; }
 uint64_t ks_launch_count(ks_handle* h) { return h ? h->launches : 0; }

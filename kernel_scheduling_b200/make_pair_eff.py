@@ -177,6 +177,8 @@ def main(argv=None) -> int:
     ap.add_argument("--solo", nargs="*", default=[])
     ap.add_argument("--pairprof-log", default=None, help="pairprof_log_<pid>.tsv of the run that wrote the --corun logs: labels every launch")
     ap.add_argument("--out-dir", default=".")
+    ap.add_argument("--publish-shm", default=None, metavar="NAME",
+                    help="also publish both tables as a shared-memory segment (e.g. /kernel_sched_pairtab_v1; include/ks_pairtab_shm.h reads it)")
     args = ap.parse_args(argv)
     ing = TraceIngest()
     with PairTableBuilder() as b:
@@ -189,7 +191,14 @@ def main(argv=None) -> int:
             parts = [records_from_log(ing, b, p, solo=False) for p in args.corun]
         parts += [records_from_log(ing, b, p, solo=True) for p in args.solo]
         rec = np.concatenate(parts)
-        us, eff = write_tables(args.out_dir, build_tables(rec, b), ing.names, ing.models)
+        tables = build_tables(rec, b)
+        us, eff = write_tables(args.out_dir, tables, ing.names, ing.models)
+        if args.publish_shm:
+            from . import pair_table_shm
+
+            by_type = {is_type: (keys, pairs) for keys, pairs, is_type in tables}
+            nbytes = pair_table_shm.publish(by_type[False], by_type[True], ing.names, ing.models, name=args.publish_shm)
+            print(f"published {nbytes} bytes as {args.publish_shm}")
     print(f"{len(rec)} launches, {len(ing.names)} kernel names, {len(ing.models)} models -> {us}, {eff}")
     return 0
 

@@ -195,3 +195,44 @@ def test_ncu_pooling_on_the_device(builder, tmp_path):
     assert np.allclose(mean, om, rtol=1e-13, atol=0, equal_nan=True)
     assert np.allclose(std, os_, rtol=1e-9, atol=1e-12, equal_nan=True)  # sample std of n values: conditioning ~ mean / spread
     assert np.all(std[:, 1][~np.isnan(std[:, 1])] == 0.0) and np.isnan(mean[3, 4]) and np.isnan(std[3, 4])
+
+
+def test_make_pair_eff_publishes_the_tables_in_shared_memory(tmp_path):
+    """The segment holds what pair_eff.tsv / kernel_us.tsv hold: every pair row of the files is found by key with the same
+    efficiency (as float32) and gangs, every kernel row with the same solo time."""
+    from kernel_scheduling_b200 import pair_table_shm as PT
+
+    rec, frames = synthetic_timing_frames(5000)
+    paths = {}
+    for (model, solo), f in frames.items():
+        paths[(model, solo)] = str(tmp_path / f"{model}_{int(solo)}.tsv")
+        f.to_csv(paths[(model, solo)], sep="\t", index=False)
+    out, name = str(tmp_path / "out"), f"/ks_pairtab_gpu_test_{os.getpid()}"
+    try:
+        assert M.main(["--corun", paths[("qwen", False)], paths[("whisper", False)], "--solo", paths[("qwen", True)], paths[("whisper", True)],
+                       "--out-dir", out, "--publish-shm", name]) == 0
+        eff = pd.read_csv(os.path.join(out, "pair_eff.tsv"), sep="\t")
+        kus = pd.read_csv(os.path.join(out, "kernel_us.tsv"), sep="\t")
+        dims = lambda s: [int(v) for v in str(s).replace("(", "").replace(")", "").split(",")]
+        with PT.Attached(name) as seg:
+            name_id, tenant = {n: i for i, n in enumerate(seg.names)}, {m: i for i, m in enumerate(seg.models)}
+
+            def key(model, kernel, block, grid):
+                is_type = str(grid) == "*"
+                return is_type, PT.kernel_key(name_id[kernel], (0, 0, 0) if is_type else dims(grid), dims(block), tenant[model], type_key=is_type)
+
+            assert 100 < len(eff) <= len(seg.shape.vals) + len(seg.type.vals)  # the file leaves out pairs without an efficiency
+            for _, r in eff.iloc[:: max(1, len(eff) // 400)].iterrows():
+                ta, ka = key(r["model_a"], r["kernel_a"], r["block_a"], r["grid_a"])
+                tb, kb = key(r["model_b"], r["kernel_b"], r["block_b"], r["grid_b"])
+                assert ta == tb
+                v = (seg.type if ta else seg.shape).find_pair(ka, kb)
+                assert v is not None and v[1] == int(r["gangs"])
+                assert v[0] == np.float32(r["efficiency"]) or (np.isnan(v[0]) and np.isnan(r["efficiency"]))
+            for _, r in kus.iloc[:: max(1, len(kus) // 200)].iterrows():
+                is_type, k = key(r["model"], r["kernel"], r["block"], r["grid"])
+                table = seg.type if is_type else seg.shape
+                i = table.find_key(k)
+                assert i >= 0 and np.isclose(table.keys["solo_us"][i], float(r["solo_us"]), rtol=1e-12, atol=0)
+    finally:
+        PT.unlink(name)

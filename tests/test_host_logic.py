@@ -129,3 +129,70 @@ def test_pairprof_labels_in_the_pandas_ingest():
     assert list((rec["smem_word"] >> 23) & 1) == [1, 0, 1, 0]
     assert list(rec["start_ns"]) == list(f["start_ns"][:4])
     assert M.agent_pid("/x/agent_123_timing.tsv") == 123 and M.agent_pid("a.tsv") is None
+
+
+def test_pair_table_in_shared_memory_python_and_c_readers(tmp_path):
+    """Publish the SHAPE and TYPE tables into a POSIX segment; read them back with the Python reader and with a C99 program
+    that uses the header alone; the daemon's fallback rule (scheduler_daemon.cpp:269-274) on both."""
+    import subprocess
+
+    from kernel_scheduling_b200 import pair_table_shm as PT
+
+    rec = trace.generate(trace.config("c1", 4000))
+    shape = oracle_tables_as_rows(rec, O.KEY_SHAPE)
+    typ = oracle_tables_as_rows(rec, O.KEY_TYPE)
+    names = [f"kernel_{i}" for i in range(int(rec["name_id"].max()) + 1)]
+    models = ["qwen", "whisper"]
+    name = f"/ks_pairtab_test_{os.getpid()}"
+    try:
+        nbytes = PT.publish(shape, typ, names, models, name=name, generation=7)
+        assert nbytes == os.path.getsize("/dev/shm" + name) and not os.path.exists("/dev/shm" + name + ".tmp")
+        # the host key function is the oracle's hash
+        k0 = shape[0][0]
+        assert PT.kernel_key(int(k0["name_id"]), k0["grid"], k0["block"], int(k0["tenant"]), smem=int(k0["smem"])) == int(k0["key"])
+        type_of_shape = {int(r["key"]): PT.kernel_key(int(r["name_id"]), (0, 0, 0), r["block"], int(r["tenant"]), type_key=True) for r in shape[0]}
+        assert set(type_of_shape.values()) == {int(k) for k in typ[0]["key"]}
+        with PT.Attached(name) as seg:
+            assert seg.generation == 7 and seg.names == names and seg.models == models
+            assert len(seg.shape.keys) == len(shape[0]) and len(seg.shape.vals) == len(shape[1]) and len(seg.type.vals) == len(typ[1])
+            for table, (keys, pairs) in ((seg.shape, shape), (seg.type, typ)):
+                for p in pairs[:: max(1, len(pairs) // 300)]:
+                    for x, y in ((p["key_a"], p["key_b"]), (p["key_b"], p["key_a"])):  # either order
+                        v = table.find_pair(int(x), int(y))
+                        assert v is not None and v[1] == int(p["count"])
+                        assert (np.isnan(v[0]) and np.isnan(p["efficiency"])) or v[0] == np.float32(p["efficiency"])
+                assert table.find_pair(int(keys["key"][0]), int(keys["key"][0])) is None  # same tenant: no such row
+                assert table.find_key(12345) == -1
+            # the fallback: a shape pair seen fewer than min_gangs times answers with its type row
+            queries, want = [], []
+            min_gangs = 3
+            for p in shape[1][:: max(1, len(shape[1]) // 200)]:
+                ta, tb = type_of_shape[int(p["key_a"])], type_of_shape[int(p["key_b"])]
+                v = seg.lookup_eff(int(p["key_a"]), int(p["key_b"]), ta, tb, min_gangs)
+                trow = seg.type.find_pair(ta, tb)
+                assert trow is not None
+                expect = (np.float32(p["efficiency"]), int(p["count"])) if int(p["count"]) >= min_gangs else trow
+                assert v[1] == expect[1] and (v[0] == expect[0] or (np.isnan(v[0]) and np.isnan(expect[0])))
+                queries.append(f"{int(p['key_a'])} {int(p['key_b'])} {ta} {tb}")
+                kus = seg.kernel_us(int(p["key_a"]), ta)
+                want.append((int(np.float32(v[0]).view(np.uint32)), v[1], int(np.float64(kus).view(np.uint64))))
+            queries.append("1 2 3 4")
+            want.append((-1, -1, int(np.float64(np.nan).view(np.uint64))))
+        exe = str(tmp_path / "pairtab_reader")
+        here = os.path.dirname(os.path.abspath(__file__))
+        subprocess.run(["gcc", "-std=c99", "-O1", "-Wall", "-Werror", "-D_POSIX_C_SOURCE=200809L", "-o", exe, os.path.join(here, "pairtab_reader.c"), "-lrt"], check=True)
+        out = subprocess.run([exe, name, str(min_gangs)], input="\n".join(queries) + "\n", capture_output=True, text=True, check=True).stdout.split("\n")
+        assert out[0].split() == ["7", str(len(shape[0])), str(len(shape[1])), str(len(typ[0])), str(len(typ[1]))]
+        got = [tuple(int(x) for x in line.split()) for line in out[1: 1 + len(want)]]
+        assert got == want
+        # a second publish replaces the segment atomically; rows out of order are refused
+        PT.publish(shape, typ, names, models, name=name, generation=8)
+        with PT.Attached(name) as seg:
+            assert seg.generation == 8
+        from kernel_scheduling_b200 import _lib
+
+        with pytest.raises(_lib.KsError):
+            PT.publish((shape[0], shape[1][::-1]), typ, names, models, name=name)
+    finally:
+        PT.unlink(name)
+    assert not os.path.exists("/dev/shm" + name)
