@@ -37,6 +37,7 @@ extern "C" {
 #define KS_ERR_DUPLICATE 9    /* ks_count_batches: a start_ns occurs twice in one file (the reference asserts) */
 #define KS_ERR_TOO_LARGE 10   /* more items than one call supports (2^30 per sort, 2^32 overlapping pairs) */
 #define KS_ERR_COMM 11        /* NCCL is missing or one of its calls failed (ks_mg_build and its communicator) */
+#define KS_ERR_REBUILD 12     /* ks_update: the resident statistics are no longer exact (or an earlier window failed): begin again, replay */
 
 /* ---- flags */
 #define KS_ON_DEVICE 1u            /* pointer arguments are device pointers */
@@ -246,6 +247,24 @@ int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* w
  * `solo` argument.  Returns the rows that remain. */
 int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags);
 int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags);
+
+/* ---- the resident table: windows of new launches merged into statistics that stay in HBM (BASELINE config 5: "online
+ * incremental mode"; the reference has no such path, its tables are rebuilt offline).  At any time the table read out is
+ * exactly the one ks_build_table gives for all launches so far: counts, sums, minima and maxima are accumulators, and
+ * for the medians every row keeps the 64 values around its median in sorted order plus how many lie below (ks_update.cuh).
+ *   ks_update_begin  an empty table (flags: KS_KEY_TYPE or 0).  At most 2,048 distinct keys; 3.5 GB of HBM for the rows.
+ *                    The handle belongs to the session until ks_update_end (other calls on it clear the dictionary).
+ *   ks_update        one window of launches in start order, not earlier than the previous window (HOST records, or DEVICE
+ *                    with KS_ON_DEVICE).  Launches still running when a window ends are carried into the next (at most
+ *                    4,096).  Returns the samples merged.  If the distribution of a row jumps so far in one window that
+ *                    its median leaves the kept values: -KS_ERR_REBUILD (never a wrong table); after any error the
+ *                    session is over.  info: counts of this window, ms_total = device time of the update.
+ *   ks_update_table  reads the table out (key rows by key, pair rows by (key_a, key_b)); then ks_copy_*_rows.
+ *   ks_update_end    frees the resident rows. */
+int64_t ks_update_begin(ks_handle* h, uint32_t flags);
+int64_t ks_update(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info);
+int64_t ks_update_table(ks_handle* h);
+int64_t ks_update_end(ks_handle* h);
 
 /* The kernel key of one launch shape, on the host: bit for bit what the device computes for a record with these fields
  * (flags: KS_KEY_TYPE or 0).  For programs that look keys up in a finished table (include/ks_pairtab_shm.h). */

@@ -194,3 +194,31 @@ class PairTableBuilder:
             "ks_pool_launches",
         )
         return launches, mean, std
+
+    # -- the resident table: windows of new launches merged into statistics that stay on the device
+    def update_begin(self, key_type: bool = False) -> None:
+        """Starts an empty resident table on this builder (at most 2,048 distinct keys; the builder belongs to the session
+        until ``update_end``)."""
+        self._check(self._lib.ks_update_begin(self._h, _lib.KEY_TYPE if key_type else 0), "ks_update_begin")
+
+    def update(self, records, n=None) -> int:
+        """Merges one window of launches (start order, not earlier than the previous window); returns the samples merged.
+        ``self.update_info`` holds the window's counts and the device time of the update (``ms_total``)."""
+        arg = self._records_arg(records, n)
+        info = _lib.KsTableInfo()
+        r = self._check(self._lib.ks_update(self._h, arg[0], arg[1], arg[2], ctypes.byref(info)), "ks_update")
+        self.update_info = info.as_dict()
+        return r
+
+    def update_table(self):
+        """-> (key_rows, pair_rows): exactly the table ``build`` gives for all launches merged so far."""
+        rows = self._check(self._lib.ks_update_table(self._h), "ks_update_table")
+        keys = np.zeros(2048, dtype=KEY_ROW_DTYPE)  # the most keys a session holds
+        nk = self._check(self._lib.ks_copy_key_rows(self._h, _lib.ptr(keys), len(keys), 0), "ks_copy_key_rows")
+        pairs = np.zeros(rows, dtype=PAIR_ROW_DTYPE)
+        self._check(self._lib.ks_copy_pair_rows(self._h, _lib.ptr(pairs), len(pairs), 0), "ks_copy_pair_rows")
+        self.info = {"n_rows": rows, "n_keys": nk}
+        return keys[:nk].copy(), pairs
+
+    def update_end(self) -> None:
+        self._lib.ks_update_end(self._h)

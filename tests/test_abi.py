@@ -24,7 +24,7 @@ def declared_functions():
 def test_library_exports_every_declared_symbol():
     lib = _lib.load()
     names = declared_functions()
-    assert len(names) >= 49
+    assert len(names) >= 53
     for n in names:
         assert hasattr(lib, n), f"{n} is declared in ks_b200.h but not exported"
     assert sorted(n for n, _, _ in _lib.KS_API) == names, "the ctypes table and the header disagree"
