@@ -5,15 +5,16 @@
 // spans in ns; the division by the solo time happens when the table is read out), so count, sum, min and max are plain
 // accumulators.  For the two middle order statistics a row keeps, per value lane, a WINDOW: the values whose ranks
 // surround the median among all values seen so far, in sorted order, and n_below = how many values lie below the window
-// (those above follow from the count).  A row of up to kUpdWindow (64) samples keeps them all inside its own record; a
-// larger one moves to a block of a pool and keeps all values up to kUpdBigWindow (1,024), then the central 1,024.  A new value below the window's first value (with n_below > 0) only
+// (those above follow from the count).  A row of up to 64 samples keeps them all inside its own record; up to 1,024 it
+// keeps them all in a block of pool 1; a larger one moves to a block of pool 2 and keeps all values up to 16,384, then
+// the central 16,384.  A new value below the window's first value (with n_below > 0) only
 // raises n_below, one above its last only the implied count above; any other value is merged into the window, which is
 // then cut back to its size, centred on the new median rank.  The window is a contiguous range of ranks of the multiset
-// at all times, so the middle values read from it are exact.  Between two re-centrings (which a value inside the window
-// triggers, with probability window / count per sample) the median's rank wanders like a random walk of half a rank per
-// sample, so with w kept values it stays inside as long as w^3 is well above 10 x count: 1,024 values are safe for rows
-// of some 10^8 samples of a stationary distribution.  Values that were dropped cannot come back, so the median CAN leave
-// the window when the distribution of a row moves away from where it was; the kernel then raises kErrEscaped and the host
+// at all times, so the middle values read from it are exact.  Values that were dropped cannot come back: the window
+// follows the median only through the new values that fall inside it.  For a stationary distribution the sample median
+// wanders among the values by a fraction of sqrt(count) ranks over a row's life (measured: 0.3-0.5 sqrt(count)), so 8,192
+// kept values on either side are safe for rows of tens of millions of samples; when the distribution of a row moves
+// away from where it was, the median CAN leave the window; the kernel then raises kErrEscaped and the host
 // reports KS_ERR_REBUILD instead of returning a wrong table.
 //
 // Rows are addressed directly: stable dense key ids (order of first appearance, at most kUpdMaxKeys keys) and
@@ -31,9 +32,9 @@ namespace ks {
 
 constexpr uint32_t kUpdMaxKeys = 2048;
 constexpr uint32_t kUpdWindow = 64;       // values a row keeps inside its own record: rows of up to 64 samples keep them all
-constexpr uint32_t kUpdBigWindow = 1024;  // values a row with more samples keeps, in a block of the pool
-constexpr uint32_t kUpdBlockSlots = kUpdBigWindow + 32;  // per lane: the window plus one chunk being merged
-constexpr uint32_t kUpdChunk = 32;
+constexpr uint32_t kUpdMidWindow = 1024;  // rows of up to 1,024 samples keep them all too, in a block of pool 1
+constexpr uint32_t kUpdBigWindow = 16384; // larger rows keep the 16,384 values around the median, in a block of pool 2
+constexpr uint32_t kUpdBlockSlots = kUpdBigWindow + 1024;  // per lane in pool 2: the window plus one batch being merged
 constexpr uint32_t kErrEscaped = 1u << 7;  // a median left its window: the resident statistics are no longer exact
 constexpr size_t kUpdRows = (size_t)kUpdMaxKeys + (size_t)kUpdMaxKeys * kUpdMaxKeys;
 
@@ -51,15 +52,17 @@ struct UpdState {
   unsigned long long* carry_start;   // [kHaloMax] launches still running at the end of the last window, by start
   unsigned long long* carry_dm;
   uint32_t* scalars;                 // [0] carried launches, [1] key ids handed out, [2..3] start_ns of the last launch seen,
-                                     // [4] pool blocks handed out, [8] scratch counter of the read-out
-  uint32_t* pool;                    // [pool_blocks][kLanes][kUpdBlockSlots]: the windows of rows with more than kUpdWindow samples
-  uint32_t pool_blocks;
+                                     // [4], [5] blocks handed out of pool 1 and 2, [8] scratch counter of the read-out
+  uint32_t* pool1;                   // [pool1_blocks][kLanes][kUpdMidWindow]: rows of 65 .. 1,024 samples
+  uint32_t* pool2;                   // [pool2_blocks][kLanes][kUpdBlockSlots]: rows with more
+  uint32_t pool1_blocks, pool2_blocks;
 };
 
 // A row with more than kUpdWindow samples keeps its windows in a pool block; win[0][0] of its record holds the block index.
 __device__ __forceinline__ const uint32_t* upd_window(const UpdState& st, const UpdRow* R, int l) {
   if (R->cnt <= kUpdWindow) return R->win[l];
-  return st.pool + ((size_t)R->win[0][0] * kLanes + l) * kUpdBlockSlots;
+  if (R->cnt <= kUpdMidWindow) return st.pool1 + ((size_t)R->win[0][0] * kLanes + l) * kUpdMidWindow;
+  return st.pool2 + ((size_t)R->win[0][0] * kLanes + l) * kUpdBlockSlots;
 }
 
 // the control words start a step from zero, except what the session accumulates (longest duration, the id base)
@@ -174,38 +177,72 @@ struct UpdArgs {
   Control* ctl;
 };
 
-// Merges up to 32 new values of one lane (x, valid where have) into a sorted window of wlen values that holds the ranks
-// [n_below, n_below + wlen) of the cnt values seen before; cap = the most values the window keeps.  The window lives in
-// global memory with room for cap + 32 values.  Returns the new n_below; the new length is min(cnt + c, cap) as long as
-// the window was complete or full before, which the callers guarantee.  buf: 64 words of the warp's shared memory.
-__device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uint32_t cap, uint32_t cnt, uint32_t c, uint32_t n_below, bool have, uint32_t x,
-                                              uint32_t* buf, Control* ctl) {
+constexpr uint32_t kUpdBatch = 1024;  // new values of one row merged in one go
+constexpr int kUpdWarps = 4;          // warps per CTA of k_upd_rows: 8 KB of shared memory each
+
+// bitonic sort of the first n words (n a power of two, 32..kUpdBatch) of a warp's shared-memory buffer
+__device__ __forceinline__ void warp_sort_pow2(uint32_t* buf, uint32_t n) {
+  const uint32_t lane = lane_id();
+  for (uint32_t k = 2; k <= n; k <<= 1) {
+    for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+      for (uint32_t t = lane; t < n; t += 32) {
+        const uint32_t o = t ^ j;
+        if (o > t) {
+          const uint32_t x = buf[t], y = buf[o];
+          const bool up = (t & k) == 0;
+          if ((x > y) == up) { buf[t] = y; buf[o] = x; }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Merges mb <= kUpdBatch new values of one lane of a row (items[j].lane, j < mb) into the sorted window vals[0 .. wlen) that
+// holds the ranks [n_below, n_below + wlen) of the cnt values seen before.  trim_to = the most values the window keeps
+// (0: the window keeps everything, its caller makes sure there is room).  The window has room for wlen + mb values.
+// Returns the new n_below.  buf, dest: kUpdBatch words each of the warp's shared memory.
+__device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uint32_t trim_to, uint32_t cnt, const uint4* items, int l, uint32_t mb,
+                                              uint32_t n_below, uint32_t* buf, uint32_t* dest, Control* ctl) {
   const uint32_t lane = lane_id();
   const uint32_t n_above = cnt - n_below - wlen;
   const uint32_t w_first = wlen ? vals[0] : 0u, w_last = wlen ? vals[wlen - 1] : 0u;
-  const bool below = have && wlen && n_below && x < w_first;
-  const bool above = have && wlen && n_above && x > w_last;
-  const bool inside = have && !below && !above;
-  n_below += __popc(__ballot_sync(0xFFFFFFFFu, below));
-  const uint32_t k = __popc(__ballot_sync(0xFFFFFFFFu, inside));
-  // the values that enter the window, ascending, lane j = the j-th smallest; also in shared memory for the searches
-  const uint32_t xs = bitonic_sort32(inside ? x : 0xFFFFFFFFu);
-  __syncwarp();
-  buf[lane] = xs;
-  __syncwarp();
-  uint32_t dest = 0;
-  if (lane < k) {  // old values <= mine stay in front of me
-    uint32_t lo = 0, hi = wlen;
-    while (lo < hi) {
-      const uint32_t mid = (lo + hi) >> 1;
-      if (vals[mid] <= xs) lo = mid + 1; else hi = mid;
-    }
-    dest = lo + lane;
+  // the values that enter the window -> buf
+  uint32_t k = 0;
+  for (uint32_t j0 = 0; j0 < mb; j0 += 32) {
+    const uint32_t j = j0 + lane;
+    const bool have = j < mb;
+    uint32_t x = 0;
+    if (have) { const uint4 it = items[j]; x = l == 0 ? it.y : l == 1 ? it.z : it.w; }
+    const bool below = have && wlen && n_below && x < w_first;
+    const bool above = have && wlen && n_above && x > w_last;
+    const bool inside = have && !below && !above;
+    n_below += __popc(__ballot_sync(0xFFFFFFFFu, below));
+    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, inside);
+    if (inside) buf[k + __popc(ballot & lanemask_lt())] = x;
+    k += __popc(ballot);
   }
-  const uint32_t first_moved = __shfl_sync(0xFFFFFFFFu, dest, 0);  // old values in front of it do not move
+  __syncwarp();
   if (k) {
+    uint32_t p2 = 32;
+    while (p2 < k) p2 <<= 1;
+    for (uint32_t j = k + lane; j < p2; j += 32) buf[j] = 0xFFFFFFFFu;
+    __syncwarp();
+    warp_sort_pow2(buf, p2);
+    // where each entering value goes: old values <= it stay in front of it
+    for (uint32_t j = lane; j < k; j += 32) {
+      const uint32_t x = buf[j];
+      uint32_t lo = 0, hi = wlen;
+      while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (vals[mid] <= x) lo = mid + 1; else hi = mid;
+      }
+      dest[j] = lo + j;
+    }
+    __syncwarp();
     // open the gaps: every old value moves up by the number of entering values smaller than it; tiles from the top down,
-    // so a value is always read before its slot is written
+    // so a value is always read before its slot is written.  Old values in front of the first entering one do not move.
+    const uint32_t first_moved = dest[0];
     const uint32_t tiles = (wlen + 31) / 32;
     for (uint32_t t = tiles; t-- > first_moved / 32;) {
       const uint32_t p = t * 32 + lane;
@@ -223,25 +260,25 @@ __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uin
       if (p < wlen && sh) vals[p + sh] = v;
       __syncwarp();
     }
-    if (lane < k) vals[dest] = xs;
+    for (uint32_t j = lane; j < k; j += 32) vals[dest[j]] = buf[j];
     __syncwarp();
   }
-  const uint32_t L = wlen + k, cnt_new = cnt + c;
+  const uint32_t L = wlen + k, cnt_new = cnt + mb;
   const long long idx_lo = (long long)((cnt_new - 1) >> 1) - (long long)n_below, idx_hi = (long long)(cnt_new >> 1) - (long long)n_below;
   if (idx_lo < 0 || idx_hi >= (long long)L) {
     if (lane == 0) atomicOr(&ctl->err, kErrEscaped);
   }
-  if (L > cap) {  // cut back to cap values centred on the median: drop `start` from the bottom, the rest from the top
-    long long want = idx_lo - (long long)(cap / 2 - 1);
+  if (trim_to && L > trim_to) {  // cut back to trim_to values centred on the median: `start` go at the bottom, the rest at the top
+    long long want = idx_lo - (long long)(trim_to / 2 - 1);
     want = max(want, 0ll);
-    want = min(want, (long long)(L - cap));
+    want = min(want, (long long)(L - trim_to));
     const uint32_t start = (uint32_t)want;
     if (start) {
-      for (uint32_t t = 0; t < (cap + 31) / 32; ++t) {
+      for (uint32_t t = 0; t < (trim_to + 31) / 32; ++t) {
         const uint32_t p = t * 32 + lane;
-        const uint32_t v = p < cap ? vals[p + start] : 0u;
+        const uint32_t v = p < trim_to ? vals[p + start] : 0u;
         __syncwarp();
-        if (p < cap) vals[p] = v;
+        if (p < trim_to) vals[p] = v;
         __syncwarp();
       }
     }
@@ -250,47 +287,71 @@ __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uin
   return n_below;
 }
 
+// where a row of cnt samples keeps its windows: 0 = inside its record, 1 = a block of pool 1, 2 = a block of pool 2
+__device__ __forceinline__ int upd_tier(uint32_t cnt) { return cnt <= kUpdWindow ? 0 : cnt <= kUpdMidWindow ? 1 : 2; }
+
+__device__ __forceinline__ uint32_t* upd_block(const UpdState& st, int tier, uint32_t block, int l) {
+  return tier == 1 ? st.pool1 + ((size_t)block * kLanes + l) * kUpdMidWindow : st.pool2 + ((size_t)block * kLanes + l) * kUpdBlockSlots;
+}
+
 // one warp per row touched by the step
-__global__ void __launch_bounds__(256) k_upd_rows(const UpdArgs a) {
-  __shared__ uint32_t bufs[8][64];
+__global__ void __launch_bounds__(kUpdWarps * 32) k_upd_rows(const UpdArgs a) {
+  __shared__ uint32_t bufs[kUpdWarps][2 * kUpdBatch];
   const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
   uint32_t* buf = bufs[warp];
+  uint32_t* dest = buf + kUpdBatch;
   const uint32_t n_rows = min(*a.n_rows_dev, a.max_rows);
-  const uint32_t warps = gridDim.x * 8;
-  for (uint32_t t = blockIdx.x * 8 + warp; t < n_rows; t += warps) {
+  const uint32_t warps = gridDim.x * kUpdWarps;
+  for (uint32_t t = blockIdx.x * kUpdWarps + warp; t < n_rows; t += warps) {
     const uint32_t key = a.row_key[t];
     if ((size_t)key >= kUpdRows) { if (lane == 0) atomicOr(&a.ctl->err, kErrTooManyKeys); continue; }
     UpdRow* R = a.st.rows + key;
     const uint32_t s = a.row_start[t], m = a.row_start[t + 1] - s;
     const int nl = key < kUpdMaxKeys ? 1 : kLanes;  // a solo row has one lane: the duration
     uint32_t cnt = R->cnt;
-    uint32_t nb[kLanes];  // values below the window, per lane (kept in registers over the chunks)
+    uint32_t nb[kLanes];  // values below the window, per lane (kept in registers over the batches)
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) nb[l] = R->n_below[l];
-    uint32_t block = cnt > kUpdWindow ? R->win[0][0] : 0xFFFFFFFFu;
-    bool dead = false;  // the pool ran out: the row cannot be kept exact
-    for (uint32_t c0 = 0; c0 < m && !dead; c0 += kUpdChunk) {
-      const uint32_t c = min(kUpdChunk, m - c0);
-      const bool have = lane < c;
-      uint4 it = make_uint4(0, 0, 0, 0);
-      if (have) it = a.items[(size_t)s + c0 + lane];
-      const uint32_t xs[kLanes] = {it.y, it.z, it.w};
-      if (block == 0xFFFFFFFFu && cnt + c > kUpdWindow) {
-        // the row outgrows its record: its values (all of them, it is still complete) move into a block of the pool
+    int tier = upd_tier(cnt);
+    uint32_t block = tier ? R->win[0][0] : 0u;
+    bool dead = false;  // a pool ran out: the row cannot be kept exact
+    // accumulators
+    for (int l = 0; l < nl; ++l) {
+      unsigned long long add = 0;
+      uint32_t lo_new = 0xFFFFFFFFu, hi_new = 0;
+      for (uint32_t j = lane; j < m; j += 32) {
+        const uint4 it = a.items[(size_t)s + j];
+        const uint32_t x = l == 0 ? it.y : l == 1 ? it.z : it.w;
+        add += x; lo_new = min(lo_new, x); hi_new = max(hi_new, x);
+      }
+      add = warp_sum64(add); lo_new = warp_min(lo_new); hi_new = warp_max(hi_new);
+      if (lane == 0) {
+        R->sum[l] += add;
+        R->mn[l] = cnt ? min(R->mn[l], lo_new) : lo_new;
+        R->mx[l] = cnt ? max(R->mx[l], hi_new) : hi_new;
+      }
+    }
+    for (uint32_t c0 = 0; c0 < m && !dead; c0 += kUpdBatch) {
+      const uint32_t mb = min(kUpdBatch, m - c0);
+      const int want = upd_tier(cnt + mb);
+      if (want != tier) {
+        // the row outgrows where it lives: its values (all of them: it is complete up to kUpdMidWindow) move to a block
+        // of the next pool
         uint32_t got = 0;
-        if (lane == 0) got = atomicAdd(a.st.scalars + 4, 1u);
+        if (lane == 0) got = atomicAdd(a.st.scalars + (want == 1 ? 4 : 5), 1u);
         got = __shfl_sync(0xFFFFFFFFu, got, 0);
-        if (got >= a.st.pool_blocks) {
+        if (got >= (want == 1 ? a.st.pool1_blocks : a.st.pool2_blocks)) {
           if (lane == 0) atomicOr(&a.ctl->err, kErrPairTableFull);
           dead = true;
           break;
         }
         for (int l = 0; l < kLanes; ++l) {
-          uint32_t* dst = a.st.pool + ((size_t)got * kLanes + l) * kUpdBlockSlots;
-          if (lane < cnt) dst[lane] = R->win[l][lane];
-          if (32 + lane < cnt) dst[32 + lane] = R->win[l][32 + lane];
+          const uint32_t* src = tier == 0 ? R->win[l] : upd_block(a.st, tier, block, l);
+          uint32_t* dst = upd_block(a.st, want, got, l);
+          for (uint32_t i = lane; i < cnt; i += 32) dst[i] = src[i];
         }
         __syncwarp();
+        tier = want;
         block = got;
         if (lane == 0) R->win[0][0] = got;
         __syncwarp();
@@ -298,20 +359,11 @@ __global__ void __launch_bounds__(256) k_upd_rows(const UpdArgs a) {
 #pragma unroll
       for (int l = 0; l < kLanes; ++l) {
         if (l >= nl) continue;
-        const uint32_t x = xs[l];
-        const unsigned long long add = warp_sum64(have ? (unsigned long long)x : 0ull);
-        const uint32_t lo_new = warp_min(have ? x : 0xFFFFFFFFu), hi_new = warp_max(have ? x : 0u);
-        if (lane == 0) {
-          R->sum[l] += add;
-          R->mn[l] = cnt ? min(R->mn[l], lo_new) : lo_new;
-          R->mx[l] = cnt ? max(R->mx[l], hi_new) : hi_new;
-        }
-        const bool big = block != 0xFFFFFFFFu;
-        uint32_t* vals = big ? a.st.pool + ((size_t)block * kLanes + l) * kUpdBlockSlots : R->win[l];
-        const uint32_t cap = big ? kUpdBigWindow : kUpdWindow;
-        nb[l] = upd_merge(vals, min(cnt, cap), cap, cnt, c, nb[l], have, x, buf, a.ctl);
+        uint32_t* vals = tier == 0 ? R->win[l] : upd_block(a.st, tier, block, l);
+        const uint32_t cap = tier == 0 ? kUpdWindow : tier == 1 ? kUpdMidWindow : kUpdBigWindow;
+        nb[l] = upd_merge(vals, min(cnt, cap), tier == 2 ? kUpdBigWindow : 0u, cnt, a.items + s + c0, l, mb, nb[l], buf, dest, a.ctl);
       }
-      cnt += c;
+      cnt += mb;
     }
     if (lane == 0 && !dead) {
       R->cnt = cnt;

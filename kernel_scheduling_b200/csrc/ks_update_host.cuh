@@ -20,8 +20,10 @@ UpdState upd_state(ks_handle* h) {
   st.carry_start = as<unsigned long long>(h->upd_carry);
   st.carry_dm = st.carry_start + kHaloMax;
   st.scalars = as<uint32_t>(h->upd_scalars);
-  st.pool = as<uint32_t>(h->upd_pool);
-  st.pool_blocks = h->upd_pool_blocks;
+  st.pool1 = as<uint32_t>(h->upd_pool);
+  st.pool2 = as<uint32_t>(h->upd_pool2);
+  st.pool1_blocks = h->upd_pool_blocks;
+  st.pool2_blocks = h->upd_pool2_blocks;
   return st;
 }
 
@@ -49,9 +51,13 @@ int64_t ks_update_begin(ks_handle* h, uint32_t flags) {
   KS_ENSURE(h, h->upd_rows, kUpdRows * sizeof(UpdRow));
   KS_ENSURE(h, h->upd_carry, 2 * (size_t)kHaloMax * 8);
   KS_ENSURE(h, h->upd_scalars, 64);
-  // windows of the rows with more than 64 samples: 12.4 KB each; 131,072 of them unless the handle was sized otherwise
-  h->upd_pool_blocks = h->cfg.max_pair_rows && !h->rows_auto ? h->cfg.max_pair_rows : (1u << 17);
-  KS_ENSURE(h, h->upd_pool, (size_t)h->upd_pool_blocks * kLanes * kUpdBlockSlots * 4);
+  // the windows of the rows with more than 64 samples: pool 1 (rows of up to 1,024 samples, 12 KB each) and pool 2 (larger
+  // rows, 204 KB each).  Sized for the full-length run of the online configuration (a 1,200 x 800 pair table after
+  // 10,000 windows of 65,536 launches: about 290,000 rows above 64 samples, 33,000 above 1,024): 4.8 GB + 8.6 GB.
+  h->upd_pool_blocks = 393216;
+  h->upd_pool2_blocks = 40960;
+  KS_ENSURE(h, h->upd_pool, (size_t)h->upd_pool_blocks * kLanes * kUpdMidWindow * 4);
+  KS_ENSURE(h, h->upd_pool2, (size_t)h->upd_pool2_blocks * kLanes * kUpdBlockSlots * 4);
   KS_CUDA(h, cudaMemsetAsync(h->upd_rows.p, 0, kUpdRows * sizeof(UpdRow), h->stream));
   KS_CUDA(h, cudaMemsetAsync(h->upd_scalars.p, 0, 64, h->stream));
   KS_CUDA(h, cudaMemsetAsync(h->kid_of_slot, 0xFF, (size_t)kDictSlots * 4, h->stream));
@@ -69,7 +75,7 @@ int64_t ks_update_end(ks_handle* h) {
   if (!h) return -KS_ERR_ARG;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
-  for (DevBuf* b : {&h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool}) {
+  for (DevBuf* b : {&h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2}) {
     if (b->p) cudaFree(b->p);
     b->p = nullptr;
     b->cap = 0;
@@ -170,7 +176,7 @@ int64_t ks_update(ks_handle* h, const void* records, uint64_t n, uint32_t flags,
     u.n_rows_dev = &h->d_ctl->n_rows;
     u.max_rows = max_rows;
     u.ctl = h->d_ctl;
-    k_upd_rows<<<(int)std::min<uint64_t>((n_samples + 7) / 8, (uint64_t)h->sm_count * 8), 256, 0, h->stream>>>(u);
+    k_upd_rows<<<(int)std::min<uint64_t>((n_samples + kUpdWarps - 1) / kUpdWarps, (uint64_t)h->sm_count * 16), kUpdWarps * 32, 0, h->stream>>>(u);
     h->launches += 4;
     KS_CUDA(h, cudaGetLastError());
   }

@@ -92,17 +92,17 @@ def test_session_errors():
 
 
 def test_a_jump_of_a_rows_distribution_is_reported_not_hidden():
-    # 3,000 solo launches of one kernel around 1,000 ns (the row keeps the central 1,024 values), then 3,000 in ONE window
+    # 40,000 solo launches of one kernel around 1,000 ns (the row keeps the central 16,384 values), then 40,000 in ONE window
     # around 50,000 ns: the median moves to a value the row no longer keeps.  The library must say so.
-    n1, n2 = 3000, 3000
+    n1, n2 = 40_000, 40_000
     dur = np.concatenate([np.full(n1, 1000) + np.arange(n1) % 7, np.full(n2, 50_000) + np.arange(n2) % 11]).astype(np.uint64)
     n = n1 + n2
     start = np.arange(n, dtype=np.uint64) * 100_000 + 1000
     rec = pack_records(np.zeros(n), np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), np.zeros(n), np.ones(n, bool), start, start + dur)
     with PairTableBuilder(device=0) as b:
         b.update_begin()
-        for lo in range(0, n1, 500):
-            b.update(rec[lo: lo + 500])
+        for lo in range(0, n1, 8000):
+            b.update(rec[lo: lo + 8000])
         keys, _ = b.update_table()
         assert keys["solo_ns"][0] == O.build_pair_table(rec[:n1])[0]["solo_ns"][0]
         with pytest.raises(_lib.KsError) as e:
