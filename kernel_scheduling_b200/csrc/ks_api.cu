@@ -61,7 +61,7 @@ struct ks_handle {
   bool tsv_labelled = false;  // ks_tsv_label ran on the parsed text: the solo flag is per row
 
   // resident table (ks_update_*)
-  DevBuf upd_rows, upd_carry, upd_scalars, upd_list[4], upd_ranks, upd_pool, upd_pool2;
+  DevBuf upd_rows, upd_carry, upd_scalars, upd_list[4], upd_ranks, upd_pool, upd_pool2, upd_big;
   uint32_t upd_pool_blocks = 0, upd_pool2_blocks = 0;
   bool upd_active = false, upd_broken = false;
   uint32_t upd_flags = 0;
@@ -605,7 +605,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->upd_big, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }

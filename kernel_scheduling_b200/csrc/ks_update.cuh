@@ -174,18 +174,27 @@ struct UpdArgs {
   const uint32_t* row_key;
   const uint32_t* n_rows_dev;
   uint32_t max_rows;
+  uint32_t* big_list;          // [max_rows] rows left to k_upd_big_rows
   Control* ctl;
 };
 
 constexpr uint32_t kUpdBatch = 1024;  // new values of one row merged in one go
 constexpr int kUpdWarps = 4;          // warps per CTA of k_upd_rows: 8 KB of shared memory each
+constexpr int kUpdBigThreads = 256;   // threads of the CTA that merges into one row of the largest kind
 
-// bitonic sort of the first n words (n a power of two, 32..kUpdBatch) of a warp's shared-memory buffer
-__device__ __forceinline__ void warp_sort_pow2(uint32_t* buf, uint32_t n) {
-  const uint32_t lane = lane_id();
+// The merge is written for a GROUP of G threads that own the row: a warp (G = 32) for rows that keep all their values,
+// a whole CTA (G = 256) for rows with a 16,384-value window.
+template <int G>
+__device__ __forceinline__ void grp_sync() {
+  if (G == 32) __syncwarp(); else __syncthreads();
+}
+
+// bitonic sort of the first n words (n a power of two, 32..kUpdBatch) of the group's shared-memory buffer
+template <int G>
+__device__ __forceinline__ void grp_sort_pow2(uint32_t* buf, uint32_t n, uint32_t tid) {
   for (uint32_t k = 2; k <= n; k <<= 1) {
     for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-      for (uint32_t t = lane; t < n; t += 32) {
+      for (uint32_t t = tid; t < n; t += G) {
         const uint32_t o = t ^ j;
         if (o > t) {
           const uint32_t x = buf[t], y = buf[o];
@@ -193,7 +202,7 @@ __device__ __forceinline__ void warp_sort_pow2(uint32_t* buf, uint32_t n) {
           if ((x > y) == up) { buf[t] = y; buf[o] = x; }
         }
       }
-      __syncwarp();
+      grp_sync<G>();
     }
   }
 }
@@ -201,36 +210,34 @@ __device__ __forceinline__ void warp_sort_pow2(uint32_t* buf, uint32_t n) {
 // Merges mb <= kUpdBatch new values of one lane of a row (items[j].lane, j < mb) into the sorted window vals[0 .. wlen) that
 // holds the ranks [n_below, n_below + wlen) of the cnt values seen before.  trim_to = the most values the window keeps
 // (0: the window keeps everything, its caller makes sure there is room).  The window has room for wlen + mb values.
-// Returns the new n_below.  buf, dest: kUpdBatch words each of the warp's shared memory.
+// Returns the new n_below.  Shared memory of the group: buf, dest (kUpdBatch words each), ctr (2 words).
+template <int G>
 __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uint32_t trim_to, uint32_t cnt, const uint4* items, int l, uint32_t mb,
-                                              uint32_t n_below, uint32_t* buf, uint32_t* dest, Control* ctl) {
-  const uint32_t lane = lane_id();
+                                              uint32_t n_below, uint32_t* buf, uint32_t* dest, uint32_t* ctr, Control* ctl, uint32_t tid) {
   const uint32_t n_above = cnt - n_below - wlen;
   const uint32_t w_first = wlen ? vals[0] : 0u, w_last = wlen ? vals[wlen - 1] : 0u;
-  // the values that enter the window -> buf
-  uint32_t k = 0;
-  for (uint32_t j0 = 0; j0 < mb; j0 += 32) {
-    const uint32_t j = j0 + lane;
-    const bool have = j < mb;
-    uint32_t x = 0;
-    if (have) { const uint4 it = items[j]; x = l == 0 ? it.y : l == 1 ? it.z : it.w; }
-    const bool below = have && wlen && n_below && x < w_first;
-    const bool above = have && wlen && n_above && x > w_last;
-    const bool inside = have && !below && !above;
-    n_below += __popc(__ballot_sync(0xFFFFFFFFu, below));
-    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, inside);
-    if (inside) buf[k + __popc(ballot & lanemask_lt())] = x;
-    k += __popc(ballot);
+  grp_sync<G>();
+  if (tid == 0) { ctr[0] = 0; ctr[1] = 0; }
+  grp_sync<G>();
+  // the values that enter the window -> buf (in any order: they are sorted next)
+  for (uint32_t j = tid; j < mb; j += G) {
+    const uint4 it = items[j];
+    const uint32_t x = l == 0 ? it.y : l == 1 ? it.z : it.w;
+    if (wlen && n_below && x < w_first) atomicAdd(&ctr[1], 1u);
+    else if (wlen && n_above && x > w_last) { }
+    else buf[atomicAdd(&ctr[0], 1u)] = x;
   }
-  __syncwarp();
+  grp_sync<G>();
+  const uint32_t k = ctr[0];
+  n_below += ctr[1];
   if (k) {
     uint32_t p2 = 32;
     while (p2 < k) p2 <<= 1;
-    for (uint32_t j = k + lane; j < p2; j += 32) buf[j] = 0xFFFFFFFFu;
-    __syncwarp();
-    warp_sort_pow2(buf, p2);
+    for (uint32_t j = k + tid; j < p2; j += G) buf[j] = 0xFFFFFFFFu;
+    grp_sync<G>();
+    grp_sort_pow2<G>(buf, p2, tid);
     // where each entering value goes: old values <= it stay in front of it
-    for (uint32_t j = lane; j < k; j += 32) {
+    for (uint32_t j = tid; j < k; j += G) {
       const uint32_t x = buf[j];
       uint32_t lo = 0, hi = wlen;
       while (lo < hi) {
@@ -239,13 +246,13 @@ __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uin
       }
       dest[j] = lo + j;
     }
-    __syncwarp();
+    grp_sync<G>();
     // open the gaps: every old value moves up by the number of entering values smaller than it; tiles from the top down,
     // so a value is always read before its slot is written.  Old values in front of the first entering one do not move.
     const uint32_t first_moved = dest[0];
-    const uint32_t tiles = (wlen + 31) / 32;
-    for (uint32_t t = tiles; t-- > first_moved / 32;) {
-      const uint32_t p = t * 32 + lane;
+    const uint32_t tiles = (wlen + G - 1) / G;
+    for (uint32_t t = tiles; t-- > first_moved / G;) {
+      const uint32_t p = t * G + tid;
       uint32_t v = 0, sh = 0;
       if (p < wlen) {
         v = vals[p];
@@ -256,17 +263,17 @@ __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uin
         }
         sh = lo;
       }
-      __syncwarp();
+      grp_sync<G>();
       if (p < wlen && sh) vals[p + sh] = v;
-      __syncwarp();
+      grp_sync<G>();
     }
-    for (uint32_t j = lane; j < k; j += 32) vals[dest[j]] = buf[j];
-    __syncwarp();
+    for (uint32_t j = tid; j < k; j += G) vals[dest[j]] = buf[j];
+    grp_sync<G>();
   }
   const uint32_t L = wlen + k, cnt_new = cnt + mb;
   const long long idx_lo = (long long)((cnt_new - 1) >> 1) - (long long)n_below, idx_hi = (long long)(cnt_new >> 1) - (long long)n_below;
   if (idx_lo < 0 || idx_hi >= (long long)L) {
-    if (lane == 0) atomicOr(&ctl->err, kErrEscaped);
+    if (tid == 0) atomicOr(&ctl->err, kErrEscaped);
   }
   if (trim_to && L > trim_to) {  // cut back to trim_to values centred on the median: `start` go at the bottom, the rest at the top
     long long want = idx_lo - (long long)(trim_to / 2 - 1);
@@ -274,12 +281,12 @@ __device__ __forceinline__ uint32_t upd_merge(uint32_t* vals, uint32_t wlen, uin
     want = min(want, (long long)(L - trim_to));
     const uint32_t start = (uint32_t)want;
     if (start) {
-      for (uint32_t t = 0; t < (trim_to + 31) / 32; ++t) {
-        const uint32_t p = t * 32 + lane;
+      for (uint32_t t = 0; t < (trim_to + G - 1) / G; ++t) {
+        const uint32_t p = t * G + tid;
         const uint32_t v = p < trim_to ? vals[p + start] : 0u;
-        __syncwarp();
+        grp_sync<G>();
         if (p < trim_to) vals[p] = v;
-        __syncwarp();
+        grp_sync<G>();
       }
     }
     n_below += start;
@@ -294,12 +301,90 @@ __device__ __forceinline__ uint32_t* upd_block(const UpdState& st, int tier, uin
   return tier == 1 ? st.pool1 + ((size_t)block * kLanes + l) * kUpdMidWindow : st.pool2 + ((size_t)block * kLanes + l) * kUpdBlockSlots;
 }
 
-// one warp per row touched by the step
+// The step's samples of one row (items[0 .. m), all of one row) merged into the row by a group of G threads.
+// Shared memory of the group: buf, dest (kUpdBatch words each), ctr (2 words), red (3 * G / 32 64-bit words for G > 32).
+template <int G>
+__device__ __forceinline__ void upd_row(const UpdState& st, UpdRow* R, int nl, const uint4* items, uint32_t m, uint32_t* buf, uint32_t* dest, uint32_t* ctr,
+                                        unsigned long long* red, Control* ctl, uint32_t tid) {
+  uint32_t cnt = R->cnt;
+  uint32_t nb[kLanes];  // values below the window, per lane (kept in registers over the batches)
+#pragma unroll
+  for (int l = 0; l < kLanes; ++l) nb[l] = R->n_below[l];
+  int tier = upd_tier(cnt);
+  uint32_t block = tier ? R->win[0][0] : 0u;
+  // accumulators
+  for (int l = 0; l < nl; ++l) {
+    unsigned long long add = 0;
+    uint32_t lo_new = 0xFFFFFFFFu, hi_new = 0;
+    for (uint32_t j = tid; j < m; j += G) {
+      const uint4 it = items[j];
+      const uint32_t x = l == 0 ? it.y : l == 1 ? it.z : it.w;
+      add += x; lo_new = min(lo_new, x); hi_new = max(hi_new, x);
+    }
+    add = warp_sum64(add); lo_new = warp_min(lo_new); hi_new = warp_max(hi_new);
+    if (G > 32) {
+      grp_sync<G>();
+      if ((tid & 31u) == 0) { red[3 * (tid >> 5)] = add; red[3 * (tid >> 5) + 1] = lo_new; red[3 * (tid >> 5) + 2] = hi_new; }
+      grp_sync<G>();
+      if (tid == 0) {
+        add = 0; lo_new = 0xFFFFFFFFu; hi_new = 0;
+        for (int w = 0; w < G / 32; ++w) { add += red[3 * w]; lo_new = min(lo_new, (uint32_t)red[3 * w + 1]); hi_new = max(hi_new, (uint32_t)red[3 * w + 2]); }
+      }
+    }
+    if (tid == 0) {
+      R->sum[l] += add;
+      R->mn[l] = cnt ? min(R->mn[l], lo_new) : lo_new;
+      R->mx[l] = cnt ? max(R->mx[l], hi_new) : hi_new;
+    }
+  }
+  for (uint32_t c0 = 0; c0 < m; c0 += kUpdBatch) {
+    const uint32_t mb = min(kUpdBatch, m - c0);
+    const int want = upd_tier(cnt + mb);
+    if (want != tier) {
+      // the row outgrows where it lives: its values (all of them: it is complete up to kUpdMidWindow) move to a block of
+      // the next pool
+      grp_sync<G>();
+      if (tid == 0) ctr[0] = atomicAdd(st.scalars + (want == 1 ? 4 : 5), 1u);
+      grp_sync<G>();
+      const uint32_t got = ctr[0];
+      if (got >= (want == 1 ? st.pool1_blocks : st.pool2_blocks)) {  // a pool ran out: the row cannot be kept exact
+        if (tid == 0) atomicOr(&ctl->err, kErrPairTableFull);
+        return;
+      }
+      for (int l = 0; l < kLanes; ++l) {
+        const uint32_t* src = tier == 0 ? R->win[l] : upd_block(st, tier, block, l);
+        uint32_t* dst = upd_block(st, want, got, l);
+        for (uint32_t i = tid; i < cnt; i += G) dst[i] = src[i];
+      }
+      grp_sync<G>();
+      tier = want;
+      block = got;
+      if (tid == 0) R->win[0][0] = got;
+      grp_sync<G>();
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      if (l >= nl) continue;
+      uint32_t* vals = tier == 0 ? R->win[l] : upd_block(st, tier, block, l);
+      const uint32_t cap = tier == 0 ? kUpdWindow : tier == 1 ? kUpdMidWindow : kUpdBigWindow;
+      nb[l] = upd_merge<G>(vals, min(cnt, cap), tier == 2 ? kUpdBigWindow : 0u, cnt, items + c0, l, mb, nb[l], buf, dest, ctr, ctl, tid);
+    }
+    cnt += mb;
+  }
+  if (tid == 0) {
+    R->cnt = cnt;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) R->n_below[l] = nb[l];
+  }
+  grp_sync<G>();
+}
+
+// One warp per row touched by the step.  Rows that have or will get a 16,384-value window are left to k_upd_big_rows
+// (one CTA per row): their list goes to big_list, its length to scalars[6].
 __global__ void __launch_bounds__(kUpdWarps * 32) k_upd_rows(const UpdArgs a) {
   __shared__ uint32_t bufs[kUpdWarps][2 * kUpdBatch];
+  __shared__ uint32_t ctrs[kUpdWarps][2];
   const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
-  uint32_t* buf = bufs[warp];
-  uint32_t* dest = buf + kUpdBatch;
   const uint32_t n_rows = min(*a.n_rows_dev, a.max_rows);
   const uint32_t warps = gridDim.x * kUpdWarps;
   for (uint32_t t = blockIdx.x * kUpdWarps + warp; t < n_rows; t += warps) {
@@ -307,70 +392,27 @@ __global__ void __launch_bounds__(kUpdWarps * 32) k_upd_rows(const UpdArgs a) {
     if ((size_t)key >= kUpdRows) { if (lane == 0) atomicOr(&a.ctl->err, kErrTooManyKeys); continue; }
     UpdRow* R = a.st.rows + key;
     const uint32_t s = a.row_start[t], m = a.row_start[t + 1] - s;
-    const int nl = key < kUpdMaxKeys ? 1 : kLanes;  // a solo row has one lane: the duration
-    uint32_t cnt = R->cnt;
-    uint32_t nb[kLanes];  // values below the window, per lane (kept in registers over the batches)
-#pragma unroll
-    for (int l = 0; l < kLanes; ++l) nb[l] = R->n_below[l];
-    int tier = upd_tier(cnt);
-    uint32_t block = tier ? R->win[0][0] : 0u;
-    bool dead = false;  // a pool ran out: the row cannot be kept exact
-    // accumulators
-    for (int l = 0; l < nl; ++l) {
-      unsigned long long add = 0;
-      uint32_t lo_new = 0xFFFFFFFFu, hi_new = 0;
-      for (uint32_t j = lane; j < m; j += 32) {
-        const uint4 it = a.items[(size_t)s + j];
-        const uint32_t x = l == 0 ? it.y : l == 1 ? it.z : it.w;
-        add += x; lo_new = min(lo_new, x); hi_new = max(hi_new, x);
-      }
-      add = warp_sum64(add); lo_new = warp_min(lo_new); hi_new = warp_max(hi_new);
-      if (lane == 0) {
-        R->sum[l] += add;
-        R->mn[l] = cnt ? min(R->mn[l], lo_new) : lo_new;
-        R->mx[l] = cnt ? max(R->mx[l], hi_new) : hi_new;
-      }
+    if (upd_tier(R->cnt + m) == 2) {
+      if (lane == 0) a.big_list[atomicAdd(a.st.scalars + 6, 1u)] = t;
+      continue;
     }
-    for (uint32_t c0 = 0; c0 < m && !dead; c0 += kUpdBatch) {
-      const uint32_t mb = min(kUpdBatch, m - c0);
-      const int want = upd_tier(cnt + mb);
-      if (want != tier) {
-        // the row outgrows where it lives: its values (all of them: it is complete up to kUpdMidWindow) move to a block
-        // of the next pool
-        uint32_t got = 0;
-        if (lane == 0) got = atomicAdd(a.st.scalars + (want == 1 ? 4 : 5), 1u);
-        got = __shfl_sync(0xFFFFFFFFu, got, 0);
-        if (got >= (want == 1 ? a.st.pool1_blocks : a.st.pool2_blocks)) {
-          if (lane == 0) atomicOr(&a.ctl->err, kErrPairTableFull);
-          dead = true;
-          break;
-        }
-        for (int l = 0; l < kLanes; ++l) {
-          const uint32_t* src = tier == 0 ? R->win[l] : upd_block(a.st, tier, block, l);
-          uint32_t* dst = upd_block(a.st, want, got, l);
-          for (uint32_t i = lane; i < cnt; i += 32) dst[i] = src[i];
-        }
-        __syncwarp();
-        tier = want;
-        block = got;
-        if (lane == 0) R->win[0][0] = got;
-        __syncwarp();
-      }
-#pragma unroll
-      for (int l = 0; l < kLanes; ++l) {
-        if (l >= nl) continue;
-        uint32_t* vals = tier == 0 ? R->win[l] : upd_block(a.st, tier, block, l);
-        const uint32_t cap = tier == 0 ? kUpdWindow : tier == 1 ? kUpdMidWindow : kUpdBigWindow;
-        nb[l] = upd_merge(vals, min(cnt, cap), tier == 2 ? kUpdBigWindow : 0u, cnt, a.items + s + c0, l, mb, nb[l], buf, dest, a.ctl);
-      }
-      cnt += mb;
-    }
-    if (lane == 0 && !dead) {
-      R->cnt = cnt;
-#pragma unroll
-      for (int l = 0; l < kLanes; ++l) R->n_below[l] = nb[l];
-    }
-    __syncwarp();
+    upd_row<32>(a.st, R, key < kUpdMaxKeys ? 1 : kLanes, a.items + s, m, bufs[warp], bufs[warp] + kUpdBatch, ctrs[warp], nullptr, a.ctl, lane);
+  }
+}
+
+// one CTA per row of the largest kind
+__global__ void __launch_bounds__(kUpdBigThreads) k_upd_big_rows(const UpdArgs a) {
+  __shared__ uint32_t buf[2 * kUpdBatch];
+  __shared__ uint32_t ctr[2];
+  __shared__ unsigned long long red[3 * kUpdBigThreads / 32];
+  const uint32_t n_big = min(a.st.scalars[6], a.max_rows);
+  for (uint32_t i = blockIdx.x; i < n_big; i += gridDim.x) {
+    const uint32_t t = a.big_list[i];
+    const uint32_t key = a.row_key[t];
+    UpdRow* R = a.st.rows + key;
+    const uint32_t s = a.row_start[t], m = a.row_start[t + 1] - s;
+    upd_row<kUpdBigThreads>(a.st, R, key < kUpdMaxKeys ? 1 : kLanes, a.items + s, m, buf, buf + kUpdBatch, ctr, red, a.ctl, threadIdx.x);
+    __syncthreads();
   }
 }
 

@@ -75,7 +75,7 @@ int64_t ks_update_end(ks_handle* h) {
   if (!h) return -KS_ERR_ARG;
   cudaSetDevice(h->device);
   if (h->stream) cudaStreamSynchronize(h->stream);
-  for (DevBuf* b : {&h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2}) {
+  for (DevBuf* b : {&h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->upd_big}) {
     if (b->p) cudaFree(b->p);
     b->p = nullptr;
     b->cap = 0;
@@ -168,8 +168,11 @@ int64_t ks_update(ks_handle* h, const void* records, uint64_t n, uint32_t flags,
     k_rows_count<<<grid, 256, 0, h->stream>>>(r);
     k_rows_scan<<<1, 1024, 0, h->stream>>>(r);
     k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
+    KS_ENSURE(h, h->upd_big, ((size_t)max_rows + 1) * 4);
+    KS_CUDA(h, cudaMemsetAsync(st.scalars + 6, 0, 4, h->stream));
     UpdArgs u{};
     u.st = st;
+    u.big_list = as<uint32_t>(h->upd_big);
     u.items = as<uint4>(h->samples[cur]);
     u.row_start = as<uint32_t>(h->row_start);
     u.row_key = as<uint32_t>(h->row_key);
@@ -177,7 +180,8 @@ int64_t ks_update(ks_handle* h, const void* records, uint64_t n, uint32_t flags,
     u.max_rows = max_rows;
     u.ctl = h->d_ctl;
     k_upd_rows<<<(int)std::min<uint64_t>((n_samples + kUpdWarps - 1) / kUpdWarps, (uint64_t)h->sm_count * 16), kUpdWarps * 32, 0, h->stream>>>(u);
-    h->launches += 4;
+    k_upd_big_rows<<<h->sm_count * 4, kUpdBigThreads, 0, h->stream>>>(u);
+    h->launches += 5;
     KS_CUDA(h, cudaGetLastError());
   }
   cudaEventRecord(ev[1], h->stream);
