@@ -435,7 +435,6 @@ __global__ void __launch_bounds__(256) k_upd_keys_by_id(const unsigned long long
 __global__ void __launch_bounds__(256) k_upd_collect(const UpdRow* __restrict__ rows, const uint32_t* __restrict__ rank_of_id, uint32_t n_ids, uint32_t* __restrict__ sort_key,
                                                      uint32_t* __restrict__ pair_id, uint32_t* counter, uint32_t capacity) {
   const uint64_t total = (uint64_t)n_ids * n_ids;
-  const uint64_t t0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (uint64_t base = (uint64_t)blockIdx.x * blockDim.x; base < total; base += (uint64_t)gridDim.x * blockDim.x) {
     const uint64_t t = base + threadIdx.x;
     bool mine = false;
@@ -456,7 +455,6 @@ __global__ void __launch_bounds__(256) k_upd_collect(const UpdRow* __restrict__ 
       pair_id[at] = ia * kUpdMaxKeys + ib;
     }
   }
-  (void)t0;
 }
 
 struct UpdEmitArgs {
