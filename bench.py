@@ -8,6 +8,9 @@ tables) over one seeded synthetic trace.  ``value`` is records/s with the trace 
 same metric through the public API with HOST buffers (pinned), host<->device copies inside the timed region.
 At N > 1 (torchrun, one rank per GPU) every rank takes one time window of the trace; see DESIGN.md.
 
+``--workload c5`` measures the resident table instead (online incremental mode): a step is one window of 65,536 launches
+merged into the table, the metric its latency (lower is better); one GPU.
+
 ``--impl reference`` times the CPU restatement of the reference's post-processing (oracle/) on the box's host
 cores on a bounded sample of the same workload.
 """
@@ -145,6 +148,69 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_online(args, rank):
+    """--workload c5: the resident table.  A step is one window of 65,536 launches merged into the table; ``value`` is the
+    median latency of an update with the window already in device memory, ``e2e`` the same with the window in pinned host
+    memory (its copy to the device inside the call).  One GPU: the path does not shard (a table is one sequence of windows)."""
+    if rank != 0:
+        return
+    import torch
+
+    from kernel_scheduling_b200 import trace
+    from kernel_scheduling_b200.pair_table import PairTableBuilder
+    from kernel_scheduling_b200.records import RECORD_DTYPE
+    from oracle import pair_table_oracle as oracle
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the GPU arm")
+    per = 65536
+    warm, steps = max(args.warmup, 3), max(args.steps, 1)
+    windows = warm + steps
+    rec = trace.generate(trace.config("c5", 2 * windows * per), interleave_solo=True)
+    dev = torch.from_numpy(rec.view(np.uint8).reshape(-1)).cuda()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.wait_first(5.0)
+    lat = {"device": [], "host": []}
+    launches = 0
+    with PairTableBuilder(device=0) as b:
+        b.update_begin()
+        l0 = b.launch_count
+        for w in range(windows):  # windows already in device memory
+            t0 = time.perf_counter()
+            b.update(dev.data_ptr() + w * per * 48, per)
+            lat["device"].append(1e3 * (time.perf_counter() - t0))
+        launches = (b.launch_count - l0) // windows
+        pinned = b.pinned_records(per)
+        for w in range(windows, 2 * windows):  # windows in pinned host memory
+            pinned[:] = rec[w * per: (w + 1) * per]
+            t0 = time.perf_counter()
+            b.update(pinned)
+            lat["host"].append(1e3 * (time.perf_counter() - t0))
+        keys, pairs = b.update_table()
+        b.update_end()
+    clocks = sampler.stop()
+    t0 = time.perf_counter()
+    oracle.build_pair_table(rec[: windows * per], check_bijection=False)
+    cpu_ms = 1e3 * (time.perf_counter() - t0)
+    dev_ms, host_ms = lat["device"][warm:], lat["host"][warm:]
+    line = {
+        "metric": "per-window update latency (p50)", "value": float(np.percentile(dev_ms, 50)), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": float(np.mean(dev_ms)), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "u32/u64 integer, f64 tables",
+        "data": "synthetic",
+        "config": {"workload": f"c5: resident table, windows of {per} launches, {len(keys)} keys, {len(pairs)} table rows after {2 * windows} windows",
+                   "l2": "a window is 3 MB: the latency of a short chain of launches, not a bandwidth figure"},
+        "p99": float(np.percentile(dev_ms, 99)), "clocks": clocks, "gpu_launches": int(launches * steps),
+        "e2e": {"value": float(np.percentile(host_ms, 50)), "unit": "ms", "h2d_bytes_per_step": per * RECORD_DTYPE.itemsize, "d2h_bytes_per_step": 128,
+                "p99": float(np.percentile(host_ms, 99))},
+        "roofline": None,
+        "cpu_baseline": {"value": cpu_ms, "unit": "ms", "cores": 1, "kind": "port",
+                         "sample": f"the reference has no incremental mode: one rebuild of the table over the first {windows * per} launches with the numpy oracle, 1 thread"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -152,6 +218,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload.lower() == "c5":
+        run_online(args, rank)
         return
 
     import torch
