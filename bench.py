@@ -6,7 +6,7 @@
 A step is one pass of the whole path (decode + hash, grouping sort, interval join, segmented statistics,
 tables) over one seeded synthetic trace.  ``value`` is records/s with the trace resident in HBM; ``e2e`` is the
 same metric through the public API with HOST buffers (pinned), host<->device copies inside the timed region.
-At N > 1 (torchrun, one rank per GPU) every rank takes one time window of the trace; see DESIGN.md.
+At N > 1 (torchrun, one rank per GPU) every rank takes one time window of the trace.
 
 ``--workload c5`` measures the resident table instead (online incremental mode): a step is one window of 65,536 launches
 merged into the table, the metric its latency (lower is better); one GPU.

@@ -47,7 +47,7 @@ def postprocess_cases():
     cases = []
     base = 1_000_000_000_000
     inputs = [
-        ("survey_example", np.arange(1000, 5001, 1000), np.array([2000, 4000, 6000])),
+        ("small_example", np.arange(1000, 5001, 1000), np.array([2000, 4000, 6000])),
         ("disjoint", base + np.arange(0, 50) * 7919, base + np.arange(0, 40) * 7919 + 3),
         ("empty_second", base + np.arange(0, 10) * 100, np.array([], dtype=np.int64)),
     ]
