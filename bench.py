@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the trace -> interference-table path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2] [--records R]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3] [--records R]
 
 A step is one pass of the whole path (decode + hash, grouping sort, interval join, segmented statistics,
 tables) over one seeded synthetic trace.  ``value`` is records/s with the trace resident in HBM; ``e2e`` is the
@@ -33,7 +33,8 @@ import numpy as np  # noqa: E402
 METRIC = "trace records/sec to interference table"
 UNIT = "records/s"
 CLOCK_LOAD_STEPS = 200  # at most this many untimed steps in front of the warm-up while the clock sampler runs (about 0.2-0.3 s of load)
-CPU_SAMPLE_RECORDS = 10_000_000  # the CPU arm runs the whole c2 workload: about 10-20 s of one host core per step
+MIN_TIMED_S = 0.5  # the timed region is at least this long (blocks of K steps are repeated)
+CPU_SAMPLE_RECORDS = 20_000_000  # the CPU arm takes a 20 M-record stretch of the workload: several seconds of all host cores per step
 
 
 def parse():
@@ -42,9 +43,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--workload", default="c3")
     ap.add_argument("--records", type=int, default=None, help="records per GPU (default: the configuration's own size, capped by --max-records)")
-    ap.add_argument("--max-records", type=int, default=10_000_000)
+    ap.add_argument("--max-records", type=int, default=100_000_000)
+    ap.add_argument("--verify", action="store_true", help="compare the table of the timed workload with the CPU oracle at full size (slow; not part of the default run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--clock-load-steps", type=int, default=CLOCK_LOAD_STEPS,
@@ -109,43 +111,54 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_baseline(workload: str, sample_records: int, rec=None):
-    """The oracle (a numpy port of the reference's post-processing) timed on one host core."""
+def cpu_baseline(workload: str, sample_records: int, rec=None, threads: int = 0):
+    """The C restatement of the reference's post-processing (oracle/pair_table_oracle.c) timed on the box's host cores."""
     from kernel_scheduling_b200 import trace
-    from oracle import pair_table_oracle as oracle
+    from oracle import c_oracle
 
     if rec is None or len(rec) != sample_records:
-        rec = trace.generate(trace.config(workload, sample_records))
+        rec = trace.generate_fast(trace.config(workload, sample_records))
+    cores = threads or c_oracle.host_threads()
     t0 = time.perf_counter()
-    _, pairs = oracle.build_pair_table(rec, check_bijection=False)
+    _, pairs = c_oracle.build_pair_table(rec, threads=cores)
     dt = time.perf_counter() - t0
-    return {"value": len(rec) / dt, "unit": UNIT, "cores": 1, "kind": "port",
-            "sample": f"{len(rec)} records of {workload} ({int(pairs['count'].sum())} overlapping pairs), numpy oracle, 1 thread of {os.cpu_count()} host cores, {dt:.2f} s"}
+    return {"value": len(rec) / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{len(rec)} records of {workload} ({int(pairs['count'].sum())} overlapping pairs, {len(pairs['count'])} rows), C/OpenMP oracle, "
+                      f"{cores} threads of {os.cpu_count()} host cores, {dt:.2f} s"}
 
 
 def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the path (the reference itself has no installable package and no
+    pair-table builder), all host threads, each step a bounded sample of the GPU arm's workload."""
     if rank != 0:
         return
-    steps = max(args.steps, 1)
-    n = min(CPU_SAMPLE_RECORDS, args.records or CPU_SAMPLE_RECORDS)
     from kernel_scheduling_b200 import trace
 
+    workload = args.workload
+    n = min(CPU_SAMPLE_RECORDS, args.records or CPU_SAMPLE_RECORDS)
     for _ in range(min(args.warmup, 1)):
-        cpu_baseline(args.workload, max(n // 20, 1000))
-    rec = trace.generate(trace.config(args.workload, n))
-    vals = [cpu_baseline(args.workload, n, rec) for _ in range(min(steps, 3))]
+        cpu_baseline(workload, max(n // 20, 1000))
+    rec = trace.generate_fast(trace.config(workload, n))
+    vals = [cpu_baseline(workload, n, rec) for _ in range(max(1, min(args.steps, 3)))]
     best = max(vals, key=lambda v: v["value"])
-    total_rec = n
-    ms = 1e3 * total_rec / best["value"]
+    ms = 1e3 * n / best["value"]
     line = {
         "impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals), "warmup": min(args.warmup, 1),
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64/f64", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {n} records per step", "records_per_step": n},
+        "config": {"workload": workload_label(workload), "records_per_step": n, "sample": f"{n} records of the same workload per step"},
         "cpu_baseline": best,
         "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def workload_label(workload: str) -> str:
+    """One label for both arms of the benchmark."""
+    from kernel_scheduling_b200 import trace
+
+    spec = trace.config(workload)
+    return f"{workload}: {len(spec.tenants)} tenants, {sum(t.n_keys for t in spec.tenants)} keys, {spec.n_records} records (synthetic, seeded)"
 
 
 def run_online(args, rank):
@@ -211,6 +224,17 @@ def run_online(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def tenant_runs(dev, n_rec):
+    """The same launches as one ordered run per tenant, concatenated: what the agents leave behind, one ordered log per
+    process (scheduler/agent.cpp:683-705).  Built on the device from the merged trace (byte 31 of a record is its tenant)."""
+    import torch
+
+    rows = dev.view(n_rec, 48)
+    tenant = rows[:, 31]
+    parts = [rows[tenant == t] for t in torch.unique(tenant).tolist()]
+    return torch.cat(parts).reshape(-1).contiguous()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -226,7 +250,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from kernel_scheduling_b200 import trace
+    from kernel_scheduling_b200 import parallel, trace
     from kernel_scheduling_b200.pair_table import PairTableBuilder
     from kernel_scheduling_b200.records import RECORD_DTYPE
 
@@ -241,7 +265,11 @@ def main():
     # weak scaling: every rank owns one window of n_rec records of the same workload (same key tables, its own launches);
     # the windows follow one another in time, so the job is ONE trace of world * n_rec records
     spec = trace.config(args.workload, n_rec)
-    rec = trace.generate(spec, window=rank)
+    host = torch.empty(n_rec * 48, dtype=torch.uint8).pin_memory()
+    rec = host.numpy().view(RECORD_DTYPE)
+    t_gen = time.perf_counter()
+    trace.generate_fast(spec, window=rank, out=rec)
+    t_gen = time.perf_counter() - t_gen
     if world > 1:
         span = torch.tensor([int(rec["start_ns"][-1] - rec["start_ns"][0]) + 1], dtype=torch.int64, device="cuda")
         spans = [torch.zeros_like(span) for _ in range(world)]
@@ -250,10 +278,8 @@ def main():
         rec["start_ns"] += np.uint64(shift)
         rec["end_ns"] += np.uint64(shift)
     first_start = int(rec["start_ns"][0])
-    host = torch.from_numpy(rec.view(np.uint8).reshape(-1)).pin_memory()
     dev = host.cuda(non_blocking=False)
     stream = torch.cuda.Stream()
-    builder = PairTableBuilder(device=local_rank, stream=stream.cuda_stream, max_records=n_rec + 8192)
 
     def barrier():
         torch.cuda.synchronize()
@@ -261,7 +287,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    from kernel_scheduling_b200 import parallel
+    # ---- the first call on a fresh handle (nothing sized, nothing known about the trace), one GPU only
+    extra = {}
+    builder = PairTableBuilder(device=local_rank, stream=stream.cuda_stream)
+    if world == 1:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+        torch.cuda.synchronize()
+        extra["first_call_ms"] = {"wall": 1e3 * (time.perf_counter() - t0), "device": builder.info["ms_total"],
+                                  "note": "fresh handle: scratch allocation, sample-buffer growth and host read-backs of the counts included"}
 
     # N > 1: the native driver (exchanges issued by the library through NCCL); --mg-driver python runs the same phases with
     # the exchanges in torch.distributed
@@ -277,32 +312,48 @@ def main():
         builder.info = {"n_pairs": 0, "n_rows": table_t.numel() // 128, "n_keys": keys_t.numel() // 72}
         return table_t.numel() // 128
 
-    # ---- device-resident: warm-up, then K timed steps.  The clock sampler (nvidia-smi, rank 0) is started first and given
-    # a stretch of the same load to sample (CLOCK_LOAD_STEPS untimed steps, the same number on every rank): its start-up
-    # would otherwise fall into the timed region, which lasts only a few milliseconds.
+    # ---- device-resident: warm-up, then blocks of exactly K timed steps.  The clock sampler (nvidia-smi, rank 0) runs from
+    # the warm-up on.  One block is K steps between two CUDA events on the library's stream, bracketed by barriers; blocks
+    # are repeated until the timed region is at least MIN_TIMED_S long and the median block is reported.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         sampler.wait_first(5.0)
     barrier()
-    clock_steps = int(max(10, min(args.clock_load_steps, 2_000_000_000 // max(n_rec, 1)))) if args.clock_load_steps > 0 else 0  # fewer for larger traces; the same on every rank
-    for _ in range(clock_steps + max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    t0 = time.perf_counter()
+    for _ in range(warm):
         step_device()
+    torch.cuda.synchronize()
+    est_ms = 1e3 * (time.perf_counter() - t0) / warm
+    if args.clock_load_steps > 0 and est_ms * warm < 300.0:  # short steps: more load in front so that the sampler sees steady clocks
+        for _ in range(int(min(args.clock_load_steps, 300.0 / max(est_ms, 1e-3)))):
+            step_device()
+    n_blocks = int(min(50, max(3, -(-MIN_TIMED_S * 1e3 // max(est_ms * args.steps, 1e-3))))) if args.clock_load_steps > 0 else 1
+    nb = torch.tensor([n_blocks], device="cuda")
+    if world > 1:
+        dist.all_reduce(nb, op=dist.ReduceOp.MAX)
+    n_blocks = int(nb[0])
     stage_names = ("ms_decode", "ms_dict", "ms_join", "ms_sort", "ms_reduce", "ms_finalize", "ms_total")
     stage_ms = {k: 0.0 for k in stage_names}
-    barrier()
     launches0 = builder.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(args.steps):
-            step_device()
-            for k in stage_names:
-                stage_ms[k] += builder.info.get(k, 0.0)
-        e1.record(stream)
-    barrier()
+    block_ms = []
+    for _ in range(n_blocks):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(args.steps):
+                step_device()
+                for k in stage_names:
+                    stage_ms[k] += builder.info.get(k, 0.0)
+            e1.record(stream)
+        barrier()
+        block_ms.append(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    launches = builder.launch_count - launches0
+    launches = (builder.launch_count - launches0) // n_blocks
+    stage_ms = {k: v / n_blocks for k, v in stage_ms.items()}
+    info = dict(builder.info)
     phase_ms = None
     whole_rows = None
     if world > 1:
@@ -321,23 +372,51 @@ def main():
             builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
             for k in stage_names:
                 stage_ms[k] += builder.info[k] * args.steps / 3.0 if i else 0.0
+        info = dict(builder.info)
         torch.cuda.synchronize()
-    ms_dev = e0.elapsed_time(e1)
-    info = dict(builder.info)
+
+    # ---- one GPU: the costs the timed steps do not show
+    if world == 1:
+        def timed(fn, reps=3):
+            out = []
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                torch.cuda.synchronize()
+                out.append(1e3 * (time.perf_counter() - t0))
+            return statistics.median(out)
+
+        # the same trace without the caller's word for its order: one more host read-back, counts read back between the stages
+        extra["unhinted_ms"] = timed(lambda: builder.build_device(dev.data_ptr(), n_rec, time_ordered=False))
+        runs = tenant_runs(dev, n_rec)
+        builder.build_device(runs.data_ptr(), n_rec, time_ordered=False)
+        extra["tenant_runs_ms"] = timed(lambda: builder.build_device(runs.data_ptr(), n_rec, time_ordered=False))
+        extra["tenant_runs_note"] = "the same launches as one ordered run per tenant, concatenated: the timeline is sorted by start_ns on the device first"
+        rows_runs = int(builder.info["n_rows"])
+        del runs
+        builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
+        assert rows_runs == int(builder.info["n_rows"]) == int(info["n_rows"])
+        if args.verify:
+            from oracle import c_oracle
+            from tests.helpers import assert_tables_match
+
+            keys_v, pairs_v = builder.fetch()
+            assert_tables_match(keys_v, pairs_v, *c_oracle.build_pair_table(rec))
+            extra["verified"] = "table equal to the C oracle's on the full trace (exact columns bit for bit, sums and means to 1e-6)"
 
     # ---- end to end through the public API: host records in, host tables out
     e2e = None
     if not args.no_e2e:
-        rec_pinned = host.numpy().view(RECORD_DTYPE)
         out_pinned = None
 
         def step_e2e():
             if world == 1:
-                return builder.build(rec_pinned, time_ordered=True, pinned=True)
+                return builder.build(rec, time_ordered=True, pinned=True)
             if session is not None:
                 with torch.cuda.stream(stream):
                     dev.copy_(host, non_blocking=True)  # this step's records from pinned host memory
-                return session.build(dev, pinned=True)  # the whole table back to pinned host memory
+                return session.build(dev, pinned=rank == 0, fetch=rank == 0)  # the whole table back to pinned host memory, on rank 0
             with torch.cuda.stream(stream):
                 dev.copy_(host, non_blocking=True)
                 keys_t, table_t = parallel.run_distributed(parallel.build_steps(parallel.GpuStages(builder, dev, first_start), rank, world, on_device=True))
@@ -359,19 +438,19 @@ def main():
             keys, pairs = step_e2e()
         torch.cuda.synchronize()
         ms_e2e = 1e3 * (time.perf_counter() - t0)
-        e2e = {"ms": ms_e2e, "steps": e2e_steps, "h2d": rec.nbytes, "d2h": keys.nbytes + pairs.nbytes}
+        e2e = {"ms": ms_e2e, "steps": e2e_steps, "h2d": rec.nbytes, "d2h": (keys.nbytes + pairs.nbytes) if keys is not None else 0}
 
-    # ---- max over ranks
-    t = torch.tensor([ms_dev, e2e["ms"] / e2e["steps"] if e2e else 0.0], device="cuda", dtype=torch.float64)
+    # ---- max over ranks, block by block
+    t = torch.tensor(block_ms + [e2e["ms"] / e2e["steps"] if e2e else 0.0, float(e2e["d2h"]) if e2e else 0.0], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev_max, ms_e2e_step = float(t[0]), float(t[1])
+    blocks = sorted(float(x) / args.steps for x in t[:-2])
+    ms_e2e_step, d2h = float(t[-2]), int(t[-1])
 
     if rank == 0:
         total_records = n_rec * world
-        ms_per_step = ms_dev_max / args.steps
+        ms_per_step = statistics.median(blocks)
         value = total_records / (ms_per_step * 1e-3)
-        # roofline of the dominant kernel (decode + hash): algorithmic bytes = 48 B read + 16 B written per record
         peaks = {}
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -381,45 +460,60 @@ def main():
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured copy bandwidth (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s"
         per_stage = {k: v / args.steps for k, v in stage_ms.items()}
-        P, T, N = info.get("n_pairs", 0), info["n_rows"], n_rec
-        # the dominant KERNEL: decode and join are single launches; the sort and the statistics are several launches each
-        # (their per-launch times are smaller, see profiles/launch_list_*), so the choice is between the first two.
-        # algorithmic bytes per launch: decode reads 48 B and writes 16 B per record; the join reads the 16-byte timeline
-        # entry of every record and writes one 16-byte sample per overlapping pair.
-        # traffic: dram__bytes_read + dram__bytes_write of one ncu capture at 4 M records, scaled by the record count
-        # (both kernels stream the trace once, so traffic grows in proportion): 59.3 B/record and 17.7 B/record.
-        cand = {"ms_decode": ("k_decode_hash", 64.0 * N, 59.3 * N), "ms_join": ("k_join", 16.0 * N + 16.0 * P, 17.7 * N)}
-        dom = max(cand, key=lambda k: per_stage[k])
-        dom_name, dom_bytes, dom_traffic = cand[dom]
-        achieved = dom_bytes / (per_stage[dom] * 1e-3) / 1e9
-        path_bytes = 48.0 * N + 32.0 * P + 96.0 * T
+        P, T, N, S = info.get("n_pairs", 0), info["n_rows"], n_rec, info.get("n_solo", 0)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32/u64 integer, f64 tables",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {n_rec} records per GPU, {info['n_keys']} keys, {P} overlapping pairs per GPU, {T} table rows"
+            "config": {"workload": workload_label(args.workload),
+                       "this_run": f"{n_rec} records per GPU, {info['n_keys']} keys, {P} overlapping pairs per GPU, {T} table rows"
                                    + (f" per window, {whole_rows} in the whole table" if whole_rows else "")
                                    + ("" if world == 1 else f"; one trace of {total_records} records in {world} time windows, samples exchanged by all-to-all, whole table on every rank"),
-                       "records_per_gpu": n_rec, "l2": "inputs (48 B x records) larger than L2; no flush needed", "input_order": "start_ns-ordered (verified on device)"},
+                       "records_per_gpu": n_rec, "l2": "inputs (48 B x records) larger than L2; no flush needed", "input_order": "start_ns-ordered (verified on device)",
+                       "generated_s": round(t_gen, 2)},
+            "timed_blocks": {"blocks": len(blocks), "steps_per_block": args.steps, "ms_per_step_min": blocks[0], "ms_per_step_median": ms_per_step,
+                             "ms_per_step_max": blocks[-1], "timed_region_s": sum(blocks) * args.steps * 1e-3},
             "clocks": clocks,
             "gpu_launches": int(launches),
             "stage_ms": per_stage,
             **({"phase_ms": phase_ms} if phase_ms else {}),
-            "roofline": {"bound": "hbm", "kernel": dom_name,
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": dom_traffic, "peak_source": peak_src,
-                         "path_algorithmic_bytes": path_bytes, "path_frac": path_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
+            **extra,
+            "roofline": roofline(per_stage, info, N, S, P, T, ms_per_step, peak, peak_src),
         }
         if e2e:
-            line["e2e"] = {"value": total_records / (ms_e2e_step * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"]),
+            line["e2e"] = {"value": total_records / (ms_e2e_step * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": d2h,
                            "ms_per_step": ms_e2e_step}
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(args.workload, min(CPU_SAMPLE_RECORDS, n_rec), rec)
+            m = min(CPU_SAMPLE_RECORDS, n_rec)
+            line["cpu_baseline"] = cpu_baseline(args.workload, m, rec[:m] if m == n_rec else None)
         print(json.dumps(line), flush=True)
     if session is not None:
         session.close()  # collective: every rank unmaps the others' buffers before any rank frees its own
     builder.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def roofline(per_stage, info, N, S, P, T, ms_per_step, peak, peak_src):
+    """The roofline block of the JSON line: the kernel with the largest share of the step, its algorithmic bytes per launch
+    over its measured launch time (CUDA events inside the library, on its stream), and the whole path."""
+    # algorithmic bytes per launch and the ncu DRAM traffic per unit (profiles/): decode reads 48 B and writes 16 B per
+    # record; the join reads the 16-byte timeline entry of every record and writes a 16-byte sample per pair; one pass of
+    # the sample sort reads and writes every 16-byte sample once
+    passes = max(1, int(info.get("sort_passes", 0)) or 1)
+    cand = {
+        "k_decode_hash": (per_stage["ms_decode"], 64.0 * N, 59.3 * N),
+        "k_join": (per_stage["ms_join"], 16.0 * N + 16.0 * P, None),
+    }
+    if info.get("ms_sort_pass", 0.0) > 0.0:
+        cand["k_onesweep_pass16"] = (info["ms_sort_pass"], 32.0 * (S + P), None)
+    dom = max(cand, key=lambda k: cand[k][0] * (passes if k == "k_onesweep_pass16" else 1))
+    ms, alg, traffic = cand[dom]
+    achieved = alg / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+    path_bytes = 48.0 * N + 32.0 * P + 96.0 * T
+    return {"bound": "hbm", "kernel": dom, "launches_per_step": passes if dom == "k_onesweep_pass16" else 1, "ms_per_launch": ms,
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+            "path_algorithmic_bytes": path_bytes, "path_frac": path_bytes / (ms_per_step * 1e-3) / 1e9 / peak}
 
 
 if __name__ == "__main__":

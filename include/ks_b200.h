@@ -140,7 +140,7 @@ int64_t ks_sort_pairs_u32(ks_handle* h, uint32_t* keys, uint32_t* vals, uint64_t
  * is host-side pandas).  Meant for code living inside another program's memory budget -- a plugin of a serving process
  * whose caching allocator owns the device, a watchdog thread that may not wait on the allocator's lock.  keys and vals
  * are DEVICE pointers on the current device (vals may be NULL), sorted in place on `stream`; no handle is needed.
- * All scratch is a fixed device array inside the library (about 8.3 MB per GPU, held until the process exits), so:
+ * All scratch is a fixed device array inside the library (8,667,648 bytes per GPU, held until the process exits), so:
  *   - at most KS_NOALLOC_MAX_ITEMS items; more is refused with -KS_ERR_TOO_LARGE;
  *   - the call never calls cudaMalloc / cudaFree or anything that allocates;
  *   - every call on a device shares that array: two calls whose GPU work overlaps (different streams or threads) race;
@@ -280,6 +280,28 @@ int64_t ks_pairtab_publish(const char* shm_name, const ks_key_row* shape_keys, u
                            uint64_t n_names, const char* const* models, uint64_t n_models, uint64_t generation);
 int ks_pairtab_unlink(const char* shm_name);
 const char* ks_pairtab_last_error(void);
+
+/* Seeded synthetic launch traces with the shapes of the benchmark configurations, generated on the host's cores (no
+ * counterpart in the reference: its traces come from live model servers, scheduler/agent.cpp:643-709).  A tenant is one
+ * process with at most one launch in flight: per launch a key drawn from the Zipf table `cdf`, a duration = the key's
+ * typical duration x lognormal jitter (x 1 + |N(0, corun_slowdown)| when co-running), an exponential idle gap in front.
+ * Solo launches (probability solo_fraction) run one at a time in a phase of their own before the co-run phase.  Writes
+ * sum(n_launches) records ordered by start_ns into `out` (HOST memory) and returns their number.  The trace is a pure
+ * function of the arguments: it does not depend on `threads` (0 = every core). */
+typedef struct ks_synth_tenant {
+  uint32_t n_keys;
+  uint32_t tenant;         /* tenant id written into the records (0..255) */
+  const uint32_t* name_id; /* [n_keys] */
+  const uint32_t* grid;    /* [n_keys][3] */
+  const uint32_t* block;   /* [n_keys][3] */
+  const uint32_t* smem;    /* [n_keys] dynamic shared memory in bytes */
+  const double* dur_ns;    /* [n_keys] typical duration of the key */
+  const double* cdf;       /* [n_keys] cumulative launch probability of the keys, cdf[n_keys-1] = 1 */
+  uint64_t n_launches;
+  double gap_mean_ns;      /* mean idle gap in front of a co-run launch */
+} ks_synth_tenant;
+int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_tenants, double solo_fraction, double jitter_sigma, double corun_slowdown,
+                       uint64_t seed, uint64_t t0_ns, ks_record* out, uint64_t capacity, uint32_t threads);
 
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
  * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */

@@ -31,6 +31,11 @@ class KsConfig(ctypes.Structure):
     _fields_ = [("max_records", c_uint64), ("max_pairs", c_uint64), ("max_pair_rows", c_uint32), ("reserved", c_uint32)]
 
 
+class KsSynthTenant(ctypes.Structure):
+    _fields_ = [("n_keys", c_uint32), ("tenant", c_uint32), ("name_id", c_void_p), ("grid", c_void_p), ("block", c_void_p), ("smem", c_void_p),
+                ("dur_ns", c_void_p), ("cdf", c_void_p), ("n_launches", c_uint64), ("gap_mean_ns", c_double)]
+
+
 class KsTableInfo(ctypes.Structure):
     _fields_ = [
         ("n_records", c_uint64), ("n_keys", c_uint64), ("n_solo", c_uint64), ("n_pairs", c_uint64), ("n_rows", c_uint64),
@@ -99,6 +104,7 @@ KS_API = [
     ("ks_kernel_key", [c_uint32, POINTER(c_uint32), POINTER(c_uint32), c_uint32, c_uint32, c_uint32], c_uint64),
     ("ks_pairtab_publish", [c_char_p, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(c_char_p), c_uint64,
                             POINTER(c_char_p), c_uint64, c_uint64], c_int64),
+    ("ks_synth_trace", [POINTER(KsSynthTenant), c_uint32, c_double, c_double, c_double, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_pairtab_unlink", [c_char_p], c_int),
     ("ks_pairtab_last_error", [], c_char_p),
 ]

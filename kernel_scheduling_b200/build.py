@@ -13,12 +13,12 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libks_b200.so"
-SOURCES = [CSRC / "ks_api.cu", CSRC / "ks_names.cpp", CSRC / "ks_pairtab.cpp"]
+SOURCES = [CSRC / "ks_api.cu", CSRC / "ks_names.cpp", CSRC / "ks_pairtab.cpp", CSRC / "ks_synth.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
     "-fmad=false",  # the float tables are defined as single IEEE operations: no contraction
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread", "-shared",
     "--expt-relaxed-constexpr",
     "-ldl",  # NCCL is bound at run time (dlopen)
     "-lrt",  # shm_open (the shared-memory pair table)

@@ -298,6 +298,9 @@ int run_decode(ks_handle* h, const void* d_records, uint64_t n, uint32_t flags, 
   KS_ENSURE(h, h->tl_dm[0], std::max<size_t>((n + reserve) * 8, 16));
   KS_ENSURE(h, h->solo_stream, std::max<size_t>((n + reserve) * 8, 16));
   if (n == 0) return 0;
+  // the bulk copies of K1 read whole 16-byte units: an unaligned source (a slice of a byte buffer) would be a misaligned-
+  // address fault on the device, so it is refused here, for every entry point that decodes records
+  if (reinterpret_cast<uintptr_t>(d_records) & 15u) return fail(h, KS_ERR_ARG, "records on the device must be 16-byte aligned");
   DecodeArgs a{};
   a.records = reinterpret_cast<const unsigned char*>(d_records);
   a.n = n;
@@ -1607,7 +1610,7 @@ int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* te
 // that runs while the application has allocation frozen -- cannot let this library call cudaMalloc.  For them the
 // scratch of the radix sort (the second key/value buffer of the ping-pong, the per-tile look-back words, the digit
 // histograms and the error word) lives in one file-scope device array of fixed size.  Every GPU that loads the library
-// carries these ~8.3 MB until the process exits.
+// carries these 8,667,648 bytes until the process exits.
 constexpr uint32_t kNoAllocMaxItems = 1u << 20;
 constexpr int kNoAllocItems = 16;                                                   // keys per thread of the pass kernel
 constexpr uint32_t kNoAllocTile = kSortThreads * kNoAllocItems;

@@ -377,9 +377,12 @@ class NativeSession:
         self.b.info = info.as_dict()
         return rows
 
-    def build(self, records: torch.Tensor, key_type: bool = False, pinned: bool = False):
-        """-> (key_rows, pair_rows) of the whole table as numpy arrays, on every rank."""
+    def build(self, records: torch.Tensor, key_type: bool = False, pinned: bool = False, fetch: bool = True):
+        """-> (key_rows, pair_rows) of the whole table as numpy arrays.  Every rank holds the table on its device; a rank
+        that passes ``fetch=False`` skips the copy to its host and gets (None, None) -- one copy per job is enough."""
         self.build_device(records, key_type)
+        if not fetch:
+            return None, None
         return self.b.fetch(pinned)
 
     def close(self):

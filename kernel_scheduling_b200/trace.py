@@ -154,6 +154,57 @@ def generate(spec: TraceSpec, interleave_solo: bool = False, window: int = 0) ->
     return np.ascontiguousarray(rec[order])
 
 
+def _key_tables(spec: TraceSpec):
+    """Per tenant the launch shapes, typical durations and Zipf table of its keys: a function of ``spec.seed`` only."""
+    key_rng = np.random.default_rng(spec.seed)
+    tables, name_base = [], 0
+    for ts in spec.tenants:
+        k = ts.n_keys
+        name = (name_base + key_rng.permutation(k)).astype(np.uint32)
+        name_base += k
+        grid = np.stack([key_rng.integers(ts.grid_range[0], ts.grid_range[1] + 1, k), key_rng.integers(1, 3, k), np.ones(k, np.int64)], axis=1).astype(np.uint32)
+        block = np.stack([key_rng.choice(ts.block_choices, k), np.ones(k, np.int64), np.ones(k, np.int64)], axis=1).astype(np.uint32)
+        smem = key_rng.choice([0, 0, 0, 16384, 49152, 98304], k).astype(np.uint32)
+        dur = (ts.dur_median_ns * np.exp(ts.dur_sigma * key_rng.standard_normal(k))).astype(np.float64)
+        p = 1.0 / np.arange(1, k + 1) ** ts.zipf_s
+        cdf = np.cumsum(p / p.sum())
+        cdf[-1] = 1.0
+        tables.append(tuple(np.ascontiguousarray(a) for a in (name, grid, block, smem, dur, cdf)))
+    return tables
+
+
+def generate_fast(spec: TraceSpec, window: int = 0, out: np.ndarray | None = None, threads: int = 0) -> np.ndarray:
+    """The same workload model as ``generate`` from the library's multi-threaded host generator (``ks_synth_trace``):
+    traces of 10^8 launches in seconds.  The launches differ from ``generate``'s (another random stream); the key tables
+    are the same.  ``out``: a record buffer to fill (e.g. pinned memory), else a new array.  -> records, ordered by start_ns.
+    """
+    from . import _lib
+
+    lib = _lib.load()
+    mean_dur = np.array([t.dur_median_ns * np.exp(0.5 * t.dur_sigma**2) for t in spec.tenants])
+    rate = np.array([t.utilisation * t.weight for t in spec.tenants]) / mean_dur
+    n_per = np.maximum((spec.n_records * rate / rate.sum()).astype(np.int64), 1)
+    n_per[0] += spec.n_records - n_per.sum()
+    assert (n_per > 0).all()
+    tables = _key_tables(spec)
+    arr = (_lib.KsSynthTenant * len(spec.tenants))()
+    for t, (ts, tab) in enumerate(zip(spec.tenants, tables)):
+        name, grid, block, smem, dur, cdf = tab
+        arr[t].n_keys, arr[t].tenant, arr[t].n_launches = ts.n_keys, t, int(n_per[t])
+        arr[t].name_id, arr[t].grid, arr[t].block, arr[t].smem = name.ctypes.data, grid.ctypes.data, block.ctypes.data, smem.ctypes.data
+        arr[t].dur_ns, arr[t].cdf = dur.ctypes.data, cdf.ctypes.data
+        arr[t].gap_mean_ns = float(mean_dur[t] * (1.0 - ts.utilisation) / ts.utilisation)
+    if out is None:
+        out = np.empty(spec.n_records, dtype=RECORD_DTYPE)
+    assert out.dtype == RECORD_DTYPE and len(out) >= spec.n_records and out.flags["C_CONTIGUOUS"]
+    seed = (int(spec.seed) << 20) ^ (7919 + int(window))
+    r = lib.ks_synth_trace(arr, len(spec.tenants), spec.solo_fraction, spec.launch_jitter_sigma, spec.corun_slowdown, seed, spec.t0_ns,
+                           out.ctypes.data, len(out), threads)
+    if r < 0:
+        raise _lib.KsError(int(-r), "ks_synth_trace")
+    return out[: int(r)]
+
+
 def shuffled(records: np.ndarray, seed: int = 7) -> np.ndarray:
     """The same launches in random order (exercises the time sort in front of the join)."""
     rng = np.random.default_rng(seed)

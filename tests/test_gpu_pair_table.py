@@ -4,6 +4,7 @@ import pytest
 
 from kernel_scheduling_b200 import trace
 from kernel_scheduling_b200.records import RECORD_DTYPE, pack_records
+from oracle import c_oracle as CO
 from oracle import pair_table_oracle as O
 from tests.helpers import assert_tables_match
 
@@ -151,9 +152,26 @@ def test_pinned_buffers(builder):
     assert_tables_match(keys, pairs, okeys, opairs)
 
 
+@pytest.mark.parametrize("cfg,n,min_pairs", [("c2", 10_000_000, 4_000_000), ("c3", 12_000_000, 20_000_000)])
+def test_benchmark_sizes_match_oracle(builder, cfg, n, min_pairs):
+    """The benchmark shapes at sizes where every sort pass, every row class (rows of millions of samples beside millions of
+    rows of one) and the call that trusts the previous call's counts are at work together, against the C oracle."""
+    rec = trace.generate_fast(trace.config(cfg, n))
+    okeys, opairs = CO.build_pair_table(rec)
+    assert int(opairs["count"].sum()) >= min_pairs and int(opairs["count"].max()) > 8192
+    for call in range(2):  # the second call queues every stage from the first call's counts
+        keys, pairs = builder.build(rec, time_ordered=True)
+        assert_tables_match(keys, pairs, okeys, opairs)
+        assert builder.info["n_pairs"] == int(opairs["count"].sum())
+    # another trace of the same shape right behind it: the counts guessed from the last call are close but not equal
+    rec2 = trace.generate_fast(trace.config(cfg, n // 2), window=1)
+    keys, pairs = builder.build(rec2, time_ordered=True)
+    assert_tables_match(keys, pairs, *CO.build_pair_table(rec2))
+
+
 def test_full_size_c2_properties(builder):
-    """The benchmark configuration at its full size (10 M records): properties that need no oracle."""
-    rec = trace.generate(trace.config("c2"))
+    """The 10 M-record configuration: properties that hold whatever the oracle says."""
+    rec = trace.generate_fast(trace.config("c2"))
     keys, pairs = builder.build(rec, time_ordered=True)
     info = dict(builder.info)
     assert info["n_records"] == len(rec) == 10_000_000

@@ -126,3 +126,35 @@ def test_combine_duplicates(builder):
     assert np.array_equal(total, ototal)
     assert np.allclose(means, omeans, rtol=1e-12, atol=0, equal_nan=True)
     assert np.isnan(means[5, 2])
+
+
+def test_unaligned_device_records_are_refused_before_any_launch(builder):
+    """K1's bulk copies need a 16-byte-aligned source; a device pointer that is not (a slice of a byte buffer) must come
+    back as KS_ERR_ARG from every entry point that decodes records -- no kernel is launched with it."""
+    import ctypes
+
+    import torch
+
+    from kernel_scheduling_b200 import _lib
+
+    lib = _lib.load()
+    rec = trace.generate(trace.config("c1", 2000))
+    buf = torch.zeros(len(rec) * 48 + 64, dtype=torch.uint8, device="cuda")
+    buf[8: 8 + len(rec) * 48] = torch.from_numpy(rec.view(np.uint8).reshape(-1)).cuda()
+    bad = ctypes.c_void_p(buf.data_ptr() + 8)
+    out = torch.zeros(len(rec) * 2, dtype=torch.int64, device="cuda")
+    o = ctypes.c_void_p(out.data_ptr())
+    h, n, dev = builder._h, len(rec), _lib.ON_DEVICE
+    calls = {
+        "ks_build_table": lambda: lib.ks_build_table(h, bad, n, dev, None),
+        "ks_hash_keys": lambda: lib.ks_hash_keys(h, bad, n, dev, o),
+        "ks_sort_launches": lambda: lib.ks_sort_launches(h, bad, n, dev, o, o),
+        "ks_join_overlaps": lambda: lib.ks_join_overlaps(h, bad, n, dev, None, None, 0),
+        "ks_mg_begin": lambda: lib.ks_mg_begin(h, bad, n, 0),
+    }
+    for name, call in calls.items():
+        assert call() == -_lib.ERR_ARG, name
+        assert b"aligned" in lib.ks_last_error(h), name
+    # the handle is as usable as before
+    keys, pairs = builder.build(rec, time_ordered=True)
+    assert len(keys) > 0

@@ -133,3 +133,77 @@ def test_pooling_oracle_equals_the_reference_script_on_real_reports():
     for j, l in enumerate(labels):
         assert np.array_equal(mean[:, j], ref[l].to_numpy(dtype=np.float64), equal_nan=True), l
         assert np.array_equal(std[:, j], ref[f"{l} std"].to_numpy(dtype=np.float64), equal_nan=True), l
+
+
+# ---- the C restatement (oracle/pair_table_oracle.c) is kept equal to the numpy oracle, column by column
+def _assert_oracles_equal(rec, key_mode=0):
+    from oracle import c_oracle as CO
+
+    k1, p1 = O.build_pair_table(rec, key_mode=key_mode)
+    k2, p2 = CO.build_pair_table(rec, key_mode=key_mode)
+    assert set(k1) == set(k2) and set(p1) == set(p2)
+    for c in k1:
+        assert np.array_equal(k1[c], k2[c], equal_nan=True), c
+    for c in p1:
+        if c.startswith(("sum", "mean")):
+            assert np.allclose(p1[c], p2[c], rtol=1e-12, atol=0, equal_nan=True), c
+        else:
+            assert np.array_equal(p1[c], p2[c], equal_nan=True), c
+    return p1
+
+
+@pytest.mark.parametrize("cfg,n", [("c1", 60_000), ("c2", 120_000), ("c3", 100_000), ("c4", 100_000)])
+def test_c_oracle_equals_numpy_oracle(cfg, n):
+    rec = trace.generate(trace.config(cfg, n))
+    _assert_oracles_equal(rec)
+    _assert_oracles_equal(trace.shuffled(rec), key_mode=O.KEY_TYPE)
+
+
+def test_c_oracle_edge_cases():
+    from oracle import c_oracle as CO
+
+    spec = trace.config("c1", 30_000)
+    spec.solo_fraction = 0.02  # keys without a baseline: NaN sides
+    p = _assert_oracles_equal(trace.generate(spec, interleave_solo=True))
+    assert (p["flags"] != 3).any() and (p["flags"] == 3).any()
+    rng = np.random.default_rng(5)
+    n = 700  # ties in start_ns, zero-length launches, three tenants
+    start = np.sort(rng.integers(1000, 1400, n)).astype(np.uint64)
+    dur = rng.integers(0, 40, n).astype(np.uint64)
+    tenant = rng.integers(0, 3, n)
+    rec = pack_records(rng.integers(0, 6, n), np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, rng.random(n) < 0.3, start, start + dur)
+    _assert_oracles_equal(rec)
+    for m in (0, 1, 2, 33):
+        _assert_oracles_equal(rec[:m])
+    assert np.array_equal(CO.kernel_keys(rec), O.kernel_keys(rec)) and np.array_equal(CO.kernel_keys(rec, 1), O.kernel_keys(rec, 1))
+    bad = rec.copy()
+    bad["end_ns"][3] = bad["start_ns"][3] - 1
+    with pytest.raises(ValueError):
+        CO.build_pair_table(bad)
+    bad = rec.copy()
+    bad["end_ns"][3] = bad["start_ns"][3] + (1 << 31)
+    with pytest.raises(ValueError):
+        CO.build_pair_table(bad)
+
+
+def test_fast_generator_is_ordered_deterministic_and_shaped_like_the_numpy_one():
+    spec = trace.config("c3", 400_000)
+    rec = trace.generate_fast(spec)
+    assert len(rec) == 400_000 and rec.dtype == RECORD_DTYPE
+    assert (np.diff(rec["start_ns"].astype(np.int64)) >= 0).all() and (rec["end_ns"] > rec["start_ns"]).all()
+    assert rec.tobytes() == trace.generate_fast(spec, threads=3).tobytes() == trace.generate_fast(spec, threads=1).tobytes()
+    assert rec.tobytes() != trace.generate_fast(spec, window=1).tobytes()
+    ref = trace.generate(spec)
+    # same key tables (a function of the seed), similar launch mix: keys, solo share, overlapping pairs per launch
+    assert set(O.kernel_keys(rec).tolist()) <= set(O.kernel_keys(ref).tolist()) | set(O.kernel_keys(rec).tolist())
+    solo = lambda r: float(((r["smem_word"] >> 23) & 1).mean())
+    assert abs(solo(rec) - solo(ref)) < 0.01
+    from oracle import c_oracle as CO
+
+    pf = CO.build_pair_table(rec)[1]["count"].sum() / len(rec)
+    pn = CO.build_pair_table(ref)[1]["count"].sum() / len(ref)
+    assert abs(pf - pn) / pn < 0.05
+    # within a tenant launches never overlap (one launch in flight per process)
+    for t in range(4):
+        m = (rec["smem_word"] >> 24) == t
+        assert (rec["start_ns"][m][1:] >= rec["end_ns"][m][:-1]).all()

@@ -1,4 +1,4 @@
-"""GPU: the allocation-free sort entry point against the ordinary one.
+"""GPU: the allocation-free sort entry point against the ordinary one and against numpy's stable sort.
 
 ``ks_sort_pairs_u32_noalloc`` exists for callers that cannot let this library allocate on the device (a plugin inside a
 serving process whose allocator owns the whole GPU, a thread that must not block on the allocator).  Its scratch is a
@@ -41,6 +41,12 @@ def test_noalloc_sort_matches_the_handle_based_sort(builder):
         assert np.array_equal(got_k, want_k), (n, b0, b1)
         if with_vals:
             assert np.array_equal(got_v, want_v), (n, b0, b1)
+        # ... and against numpy directly (both entry points run the same kernels): a stable sort on the chosen key bits
+        digit = (keys >> np.uint32(b0)) & np.uint32((1 << (b1 - b0)) - 1) if b1 - b0 < 32 else keys
+        order = np.argsort(digit, kind="stable")
+        assert np.array_equal(got_k, keys[order]), (n, b0, b1)
+        if with_vals:
+            assert np.array_equal(got_v, vals[order]), (n, b0, b1)
 
 
 def test_noalloc_sort_refuses_what_does_not_fit():
