@@ -49,6 +49,7 @@ def parse():
     ap.add_argument("--verify", action="store_true", help="compare the table of the timed workload with the CPU oracle at full size (slow; not part of the default run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the first-call, unhinted and per-tenant-runs figures (profiler runs)")
     ap.add_argument("--clock-load-steps", type=int, default=CLOCK_LOAD_STEPS,
                     help="untimed steps in front of the warm-up while the clock sampler starts (0 for profiler runs)")
     ap.add_argument("--mg-driver", default="native", choices=["native", "python"], help="N > 1: who issues the exchanges (the library through NCCL, or torch.distributed)")
@@ -290,7 +291,7 @@ def main():
     # ---- the first call on a fresh handle (nothing sized, nothing known about the trace), one GPU only
     extra = {}
     builder = PairTableBuilder(device=local_rank, stream=stream.cuda_stream)
-    if world == 1:
+    if world == 1 and not args.no_extras:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
@@ -376,7 +377,7 @@ def main():
         torch.cuda.synchronize()
 
     # ---- one GPU: the costs the timed steps do not show
-    if world == 1:
+    if world == 1 and not args.no_extras:
         def timed(fn, reps=3):
             out = []
             for _ in range(reps):

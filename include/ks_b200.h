@@ -95,10 +95,10 @@ typedef struct ks_table_info {
   uint64_t max_duration_ns;
   uint64_t min_start_ns, max_start_ns;
   uint32_t was_time_ordered; /* 1 if the input needed no sort */
-  uint32_t reserved;
+  uint32_t sort_passes;      /* passes of the sample sort (one launch of the pass kernel each) */
   /* device time of the stages of the last call, CUDA events on the handle's stream */
   float ms_stage_in, ms_decode, ms_order, ms_dict, ms_join, ms_sort, ms_reduce, ms_finalize, ms_total;
-  float reserved_f;
+  float ms_sort_pass;        /* device time of the first pass of the sample sort alone */
 } ks_table_info;
 
 typedef struct ks_handle ks_handle;

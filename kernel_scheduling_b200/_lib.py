@@ -40,10 +40,10 @@ class KsTableInfo(ctypes.Structure):
     _fields_ = [
         ("n_records", c_uint64), ("n_keys", c_uint64), ("n_solo", c_uint64), ("n_pairs", c_uint64), ("n_rows", c_uint64),
         ("max_duration_ns", c_uint64), ("min_start_ns", c_uint64), ("max_start_ns", c_uint64),
-        ("was_time_ordered", c_uint32), ("reserved", c_uint32),
+        ("was_time_ordered", c_uint32), ("sort_passes", c_uint32),
         ("ms_stage_in", ctypes.c_float), ("ms_decode", ctypes.c_float), ("ms_order", ctypes.c_float), ("ms_dict", ctypes.c_float),
         ("ms_join", ctypes.c_float), ("ms_sort", ctypes.c_float), ("ms_reduce", ctypes.c_float), ("ms_finalize", ctypes.c_float),
-        ("ms_total", ctypes.c_float), ("reserved_f", ctypes.c_float),
+        ("ms_total", ctypes.c_float), ("ms_sort_pass", ctypes.c_float),
     ]
 
     def as_dict(self):

@@ -13,6 +13,7 @@
 #include "ks_misc.cuh"
 #include "ks_reduce.cuh"
 #include "ks_sort.cuh"
+#include "ks_tilestats.cuh"
 #include "ks_tsv.cuh"
 #include "ks_update.cuh"
 
@@ -96,10 +97,12 @@ struct ks_handle {
   size_t mg_host_cap = 0;
 
   // what the last ks_build_table saw: lets the next call queue every stage without reading counts back in between
-  bool attr_sort16 = false, attr_decode = false, attr_seg = false;  // kernel attributes set on this handle's device
+  bool attr_sort16 = false, attr_decode = false, attr_seg = false, attr_tile = false;  // kernel attributes set on this handle's device
   bool hint_valid = false;
   uint64_t hint_samples = 0, hint_nk = 0, hint_rows = 0;
   cudaEvent_t ev[12]{};
+  cudaEvent_t ev_sort[2]{};  // around the first pass of the last sample sort
+  int sort_passes = 0;
   // the three size classes of K4 are independent of one another: they run side by side on two helper streams
   cudaStream_t aux[2]{};
   cudaEvent_t fork_ev{}, classify_ev{}, join_ev[2]{};
@@ -143,7 +146,7 @@ int ensure(ks_handle* h, DevBuf& b, size_t bytes) {
 template <typename T>
 T* as(const DevBuf& b) { return reinterpret_cast<T*>(b.p); }
 
-constexpr int kSort16Threads = 512;  // threads per CTA of the sample sort: tiles of 4096 items, runs of 16 items per digit
+constexpr int kSort16Threads = 512;  // threads per CTA of the sample sort: tiles of 4096 items, runs of 8 items per digit
 
 int bit_length(uint64_t v) {
   int b = 0;
@@ -214,26 +217,28 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 }
 
 // K2 driver for the 16-byte sample stream: sorts set 0/1 of h->samples on key bits [0, end_bit); returns the set that
-// holds the result.
-int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr) {
+// holds the result.  nk_dev: the key count in device memory -- the passes then split the bits of ITS largest sort key
+// among them (end_bit only fixes the number of passes; kernels read the count when they run).
+int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr, const uint32_t* nk_dev = nullptr) {
   constexpr int ITEMS = 8;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
-  const int passes = (end_bit + 7) / 8;
+  const int passes = (end_bit + kSort16MaxBits - 1) / kSort16MaxBits;
+  h->sort_passes = passes;
   if (passes <= 0 || n == 0) return 0;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
-  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  const size_t lb_bytes = ((size_t)ntiles * kSort16Bins + 64) * sizeof(uint32_t);
   KS_ENSURE(h, h->lookback, lb_bytes);
-  KS_ENSURE(h, h->hist, 2 * 8 * 256 * sizeof(uint32_t));
+  KS_ENSURE(h, h->hist, 2 * 4 * kSort16Bins * sizeof(uint32_t));
   uint32_t* hist = as<uint32_t>(h->hist);
-  uint32_t* gbase = hist + 8 * 256;
-  KS_CUDA(h, cudaMemsetAsync(hist, 0, 8 * 256 * sizeof(uint32_t), h->stream));
+  uint32_t* gbase = hist + 4 * kSort16Bins;
+  KS_CUDA(h, cudaMemsetAsync(hist, 0, 4 * kSort16Bins * sizeof(uint32_t), h->stream));
   const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
   // first_in: the unsorted items live outside the two sets (a receive buffer); the first pass reads them from there
   const uint4* src0 = first_in ? first_in : as<uint4>(h->samples[0]);
-  k_radix_hist<uint32_t><<<hist_grid, 256, 0, h->stream>>>(reinterpret_cast<const uint32_t*>(src0), 4u, n_dev, (uint32_t)n, 0, end_bit, hist);
-  k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, passes);
+  k_radix_hist16<<<hist_grid, 256, 0, h->stream>>>(src0, n_dev, (uint32_t)n, end_bit, passes, nk_dev, hist);
+  k_radix_scan_hist16<<<1, kSort16Bins, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
   constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
   if (!h->attr_sort16) {  // the attribute is per device, so it is remembered per handle
@@ -244,18 +249,23 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
   const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * (1024 / THREADS));
   for (int p = 0; p < passes; ++p) {
     KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+    if (p == 0 && h->ev_sort[0]) cudaEventRecord(h->ev_sort[0], h->stream);
     SortPass16Args a{};
     a.in = p == 0 ? src0 : as<uint4>(h->samples[cur]);
     a.out = as<uint4>(h->samples[cur ^ 1]);
     a.n_dev = n_dev;
     a.n = (uint32_t)n;
-    a.shift = 8 * p;
-    a.bits = std::min(8, end_bit - a.shift);
-    a.gbase = gbase + p * 256;
+    digit_layout(end_bit, passes, p, &a.shift, &a.bits);
+    a.nk_dev = nk_dev;
+    a.pass = p;
+    a.passes = passes;
+    a.unstable = p == 0;
+    a.gbase = gbase + p * kSort16Bins;
     a.lookback = as<uint32_t>(h->lookback);
-    a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+    a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * kSort16Bins;
     a.err = &h->d_ctl->err;
     k_onesweep_pass16<ITEMS, THREADS><<<grid, THREADS, smem, h->stream>>>(a);
+    if (p == 0 && h->ev_sort[1]) cudaEventRecord(h->ev_sort[1], h->stream);
     cur ^= 1;
   }
   KS_CUDA(h, cudaGetLastError());
@@ -470,31 +480,86 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   return 0;
 }
 
-// rows + segment statistics over sorted samples (set `s`), n samples
+// rows + segment statistics over sorted samples, n samples (or the count in device memory, bounded by n): one fused pass
+// (ks_tilestats.cuh) finishes every row that fits a tile's window; the rows that do not are handed to the CTA-per-row kernel
+// (up to kBigMax samples, on a helper stream) and to the chunked chain of the largest rows
 int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t max_rows, const uint32_t* n_dev = nullptr) {
-  const uint32_t max_tiles = (uint32_t)((n + kRowsTile - 1) / kRowsTile);
-  KS_ENSURE(h, h->tile_cnt, ((size_t)max_tiles + 1) * 4);
+  const uint32_t max_tiles = (uint32_t)((n + kTsTile - 1) / kTsTile);
+  const uint32_t max_large = (uint32_t)(n / kBigMax) + 1;
+  const uint32_t max_chunks = (uint32_t)(n / kLargeChunk) + max_large + 1;
+  const size_t state_bytes = ((size_t)max_tiles + 64) * 4;  // look-back words + ticket
+  KS_ENSURE(h, h->tile_cnt, state_bytes);
   KS_ENSURE(h, h->row_start, ((size_t)max_rows + 2) * 4);
   KS_ENSURE(h, h->row_key, ((size_t)max_rows + 2) * 4);
-  RowsArgs r{};
-  r.skey = reinterpret_cast<const uint32_t*>(items);
-  r.key_stride = 4;
-  r.n_dev = n_dev;
-  r.n = (uint32_t)n;
-  r.tile_cnt = as<uint32_t>(h->tile_cnt);
-  r.row_start = as<uint32_t>(h->row_start);
-  r.row_key = as<uint32_t>(h->row_key);
-  r.row_of_kid = h->row_of_kid;
-  r.max_tiles = max_tiles;
-  r.max_rows = max_rows;
-  r.ctl = h->d_ctl;
-  const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_tiles, (uint32_t)h->sm_count * 8));
-  k_rows_count<<<grid, 256, 0, h->stream>>>(r);
-  k_rows_scan<<<1, 1024, 0, h->stream>>>(r);
-  k_rows_fill<<<grid, 256, 0, h->stream>>>(r);
-  h->launches += 3;
+  KS_ENSURE(h, h->stats, ((size_t)max_rows + 257) * sizeof(RowStats));
+  const uint32_t max_deferred = (uint32_t)(n / kTsRowMax) + max_tiles + 2;  // rows above kTsRowMax, and one row per tile that may leave its window
+  KS_ENSURE(h, h->small_rows, (size_t)max_deferred * 4);
+  KS_ENSURE(h, h->cta_rows, (size_t)max_deferred * 4);
+  KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
+  KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
+  KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
+  KS_ENSURE(h, h->large_hist, (size_t)max_large * 2 * kLanes * 256 * 4);
+  if (!h->attr_tile) {  // per device, so remembered per handle
+    KS_CUDA(h, cudaFuncSetAttribute(k_tile_stats, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_stats_smem_bytes()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes()));
+    h->attr_tile = true;
+  }
+  KS_CUDA(h, cudaMemsetAsync(h->tile_cnt.p, 0, state_bytes, h->stream));
+  TileStatsArgs t{};
+  t.items = items;
+  t.n_dev = n_dev;
+  t.n = (uint32_t)n;
+  t.tile_state = as<uint32_t>(h->tile_cnt);
+  t.ticket = as<uint32_t>(h->tile_cnt) + max_tiles + 32;
+  t.row_start = as<uint32_t>(h->row_start);
+  t.row_key = as<uint32_t>(h->row_key);
+  t.row_of_kid = h->row_of_kid;
+  t.stats = as<RowStats>(h->stats);
+  t.deferred = as<uint32_t>(h->small_rows);
+  t.max_deferred = max_deferred;
+  t.max_rows = max_rows;
+  t.ctl = h->d_ctl;
+  const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_tiles, (uint32_t)h->sm_count * 4));
+  k_tile_stats<<<grid, kTsThreads, tile_stats_smem_bytes(), h->stream>>>(t);
+  DeferredArgs d{};
+  SegArgs& s = d.seg;
+  s.items = items;
+  s.plain = nullptr;
+  s.n_lanes = kLanes;
+  s.row_start = as<uint32_t>(h->row_start);
+  s.n_rows_dev = &h->d_ctl->n_rows;
+  s.max_rows = max_rows;
+  s.stats = as<RowStats>(h->stats);
+  s.big_rows = as<uint32_t>(h->cta_rows);
+  s.large = as<LargeRow>(h->large_rows);
+  s.chunk_row = as<uint32_t>(h->chunk_row);
+  s.chunk_idx = as<uint32_t>(h->chunk_idx);
+  s.large_hist = as<uint32_t>(h->large_hist);
+  s.max_large = max_large;
+  s.max_chunks = max_chunks;
+  s.ctl = h->d_ctl;
+  d.deferred = as<uint32_t>(h->small_rows);
+  d.row_start = as<uint32_t>(h->row_start);
+  d.max_deferred = max_deferred;
+  k_seg_deferred<<<(int)std::max<uint32_t>(1, std::min<uint32_t>((max_deferred + 255) / 256, (uint32_t)h->sm_count * 4)), 256, 0, h->stream>>>(d);
+  // the CTA-per-row kernel beside the chain of the largest rows
+  KS_CUDA(h, cudaEventRecord(h->fork_ev, h->stream));
+  KS_CUDA(h, cudaStreamWaitEvent(h->aux[0], h->fork_ev, 0));
+  k_seg_big<<<h->sm_count * 2, 256, seg_big_smem_bytes(), h->aux[0]>>>(s);
+  KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
+  const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 4));
+  k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
+  k_segL_init<<<(max_large * 2 * kLanes + 255) / 256, 256, 0, h->stream>>>(s);
+  for (int r = 0; r < kLargeRounds; ++r) {
+    s.round = r;
+    k_segL_hist<<<lgrid, 256, 0, h->stream>>>(s);
+    k_segL_resolve<<<(int)std::min<uint32_t>(max_large, (uint32_t)h->sm_count * 8), 2 * kLanes * 32, 0, h->stream>>>(s);
+  }
+  k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
+  KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
+  h->launches += 6 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
-  return run_segment_stats(h, items, nullptr, n, max_rows);
+  return 0;
 }
 
 __global__ void k_stats_to_u64(const RowStats* stats, const uint32_t* row_start, uint32_t n_rows, unsigned long long* out) {
@@ -580,6 +645,7 @@ ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
   alloc(&h->solo_ns, (size_t)(kMaxKeys + 1) * 8);
   alloc(&h->key_rows, (size_t)(kMaxKeys + 1) * sizeof(ks_key_row));
   for (auto& e : h->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+  for (auto& e : h->ev_sort) ok = ok && cudaEventCreate(&e) == cudaSuccess;
   for (auto& st : h->aux) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&h->fork_ev, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&h->classify_ev, cudaEventDisableTiming) == cudaSuccess;
@@ -611,6 +677,7 @@ void ks_destroy(ks_handle* h) {
                     &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->upd_big, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
+  for (auto& e : h->ev_sort) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
   if (h->fork_ev) cudaEventDestroy(h->fork_ev);
   if (h->classify_ev) cudaEventDestroy(h->classify_ev);
@@ -710,9 +777,11 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   const uint64_t nk = hinted ? h->hint_nk : h->h_ctl->n_keys;
   const uint32_t* n_dev = hinted ? reinterpret_cast<const uint32_t*>(&h->d_ctl->n_pairs) : nullptr;
 
-  // K2: group the samples by sort key (whole bytes of the key when the key count is only a guess)
-  const int end_bit = hinted ? 8 * ((bit_length(nk + nk * nk) + 7) / 8) : bit_length(nk + nk * nk);
-  const int cur = radix_sort16(h, n_samples, end_bit, n_dev);
+  // K2: group the samples by sort key.  When the key count is only the previous call's, it fixes the number of passes and
+  // the kernels split the bits of the actual largest sort key among them.
+  const int end_bit = bit_length(nk + nk * nk);
+  const int sort_capacity_bits = ((end_bit + kSort16MaxBits - 1) / kSort16MaxBits) * kSort16MaxBits;
+  const int cur = radix_sort16(h, n_samples, end_bit, n_dev, nullptr, hinted ? &h->d_ctl->n_keys : nullptr);
   if (cur < 0) return cur;
   cudaEventRecord(ev[7], h->stream);
 
@@ -746,7 +815,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   { int r = read_ctl(h); if (r) return r; }
   if (hinted) {
     const Control& g = *h->h_ctl;
-    const bool guess_held = g.n_pairs <= n_samples && bit_length((uint64_t)g.n_keys + (uint64_t)g.n_keys * g.n_keys) <= end_bit && g.n_rows <= max_rows &&
+    const bool guess_held = g.n_pairs <= n_samples && bit_length((uint64_t)g.n_keys + (uint64_t)g.n_keys * g.n_keys) <= sort_capacity_bits && g.n_rows <= max_rows &&
                             !(g.err & (kErrTooLarge | kErrPairTableFull));
     if (!guess_held) {  // the trace changed shape: do it again, reading the counts back between the stages
       h->hint_valid = false;
@@ -792,6 +861,8 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     info->ms_reduce = ev_ms(ev[7], ev[8]);
     info->ms_finalize = ev_ms(ev[8], ev[9]);
     info->ms_total = ev_ms(ev[0], ev[9]);
+    info->sort_passes = (uint32_t)h->sort_passes;
+    info->ms_sort_pass = h->sort_passes > 0 && n_samples ? ev_ms(h->ev_sort[0], h->ev_sort[1]) : 0.f;
   }
   return (int64_t)h->n_pair_rows;
 }
@@ -1336,7 +1407,7 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
-  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  const size_t lb_bytes = ((size_t)ntiles * kSort16Bins + 64) * sizeof(uint32_t);
   KS_ENSURE(h, h->lookback, lb_bytes);
   KS_ENSURE(h, h->hist, 2 * 8 * 256 * sizeof(uint32_t));
   uint32_t* hist = as<uint32_t>(h->hist);
@@ -1355,7 +1426,7 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   a.bits = 8;
   a.gbase = gbase;
   a.lookback = as<uint32_t>(h->lookback);
-  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * kSort16Bins;
   a.err = &h->d_ctl->err;
   if (counts) for (uint32_t r = 0; r < n_ranks; ++r) counts[r] = 0;
   if (n) {

@@ -24,6 +24,7 @@ constexpr int kDecodeTile = kDecodeThreads * kDecodePerThread;
 constexpr int kDecodeTileBytes = kDecodeTile * 48;
 constexpr int kCtaCountBits = 10;
 constexpr int kDecodeCtasPerSm = 3;  // 61 KB of shared memory per CTA; four CTAs with a 512-slot count cache measured the same
+constexpr uint32_t kCountFlushTiles = 32;       // the count cache is flushed and emptied every so many tiles of a CTA
 constexpr uint32_t kCtaCountSlots = 1u << kCtaCountBits;  // per-CTA launch-count cache (open addressing on the dictionary slot)
 
 struct DecodeArgs {
@@ -228,6 +229,21 @@ __global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm) k_decode_has
     if (tid == 0) {
       const uint64_t next = tile + (uint64_t)kDecodeStages * gridDim.x;
       if (next < ntiles) issue(next, stage);
+    }
+    // The count cache takes keys first come, first served.  A trace whose key mix changes (one tenant's solo run, then
+    // another's, then all of them together) would leave it full of keys that no longer occur, and the hottest keys of the
+    // later mix would all go to the same few global counters.  So it is emptied every kCountFlushTiles tiles and refills
+    // with the keys of the stretch at hand, the frequent ones first.
+    if ((it + 1) % kCountFlushTiles == 0) {
+      for (uint32_t i = tid; i < kCtaCountSlots; i += kDecodeThreads) {
+        const uint32_t s = cc_slot[i];
+        if (s) {
+          atomicAdd(&a.dict_launches[s - 1], cc_cnt[i]);
+          if (cc_solo[i]) atomicAdd(&a.dict_solo[s - 1], cc_solo[i]);
+          cc_slot[i] = 0; cc_cnt[i] = 0; cc_solo[i] = 0;
+        }
+      }
+      __syncthreads();
     }
   }
 

@@ -249,7 +249,7 @@ int mg_partition_to_peers(ks_handle* h, const uint32_t* splitters, uint32_t shif
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
-  const size_t lb_bytes = ((size_t)ntiles * 256 + 64) * sizeof(uint32_t);
+  const size_t lb_bytes = ((size_t)ntiles * kSort16Bins + 64) * sizeof(uint32_t);
   KS_ENSURE(h, h->lookback, lb_bytes);
   KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
   SortPass16Args a{};
@@ -265,7 +265,7 @@ int mg_partition_to_peers(ks_handle* h, const uint32_t* splitters, uint32_t shif
   a.bits = 8;
   a.gbase = nullptr;
   a.lookback = as<uint32_t>(h->lookback);
-  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * 256;
+  a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * kSort16Bins;
   a.err = &h->d_ctl->err;
   constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
   KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -494,6 +494,7 @@ __global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
           if (v > lo[l]) next[l] = min(next[l], v);
         }
       }
+      __syncthreads();  // every thread has read sh_a / sh_b of the first pass (the select loop may not have run)
 #pragma unroll
       for (int l = 0; l < kLanes; ++l) {
         const uint32_t le_w = warp_sum(le[l]), nx_w = warp_min(next[l]);
