@@ -49,6 +49,10 @@ def parse():
     ap.add_argument("--verify", action="store_true", help="compare the table of the timed workload with the CPU oracle at full size (slow; not part of the default run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--streamed", action="store_true", help="one GPU: the window-by-window build (default for more than 160 M records)")
+    ap.add_argument("--window-records", type=int, default=0, help="streamed build: launches per join window (0 = the library's default, 2^26)")
+    ap.add_argument("--parts", type=int, default=0, help="streamed build: key ranges (0 = 16)")
+    ap.add_argument("--gen-window", type=int, default=125_000_000, help="streamed build: the trace is generated in windows of this many records")
     ap.add_argument("--no-extras", action="store_true", help="skip the first-call, unhinted and per-tenant-runs figures (profiler runs)")
     ap.add_argument("--clock-load-steps", type=int, default=CLOCK_LOAD_STEPS,
                     help="untimed steps in front of the warm-up while the clock sampler starts (0 for profiler runs)")
@@ -266,10 +270,28 @@ def main():
     # weak scaling: every rank owns one window of n_rec records of the same workload (same key tables, its own launches);
     # the windows follow one another in time, so the job is ONE trace of world * n_rec records
     spec = trace.config(args.workload, n_rec)
-    host = torch.empty(n_rec * 48, dtype=torch.uint8).pin_memory()
+    # one GPU and more records than one call of the ordinary build can take (2^30 overlapping pairs): the streamed build,
+    # and the trace is made window by window (the same windows an N-GPU job of this size gives its ranks)
+    streamed = world == 1 and (args.streamed or n_rec > 160_000_000)
+    gen_window = n_rec if not streamed else min(n_rec, args.gen_window)
+    host = torch.empty(gen_window * 48, dtype=torch.uint8).pin_memory()
     rec = host.numpy().view(RECORD_DTYPE)
     t_gen = time.perf_counter()
-    trace.generate_fast(spec, window=rank, out=rec)
+    if not streamed:
+        trace.generate_fast(spec, window=rank, out=rec)
+        dev = None
+    else:
+        dev = torch.empty(n_rec * 48, dtype=torch.uint8, device="cuda")
+        shift, done = 0, 0
+        while done < n_rec:
+            m = min(gen_window, n_rec - done)
+            part = trace.generate_fast(trace.config(args.workload, m), window=done // gen_window, out=rec[:m])
+            part["start_ns"] += np.uint64(shift)
+            part["end_ns"] += np.uint64(shift)
+            shift += int(part["start_ns"][-1] - part["start_ns"][0]) + 1
+            dev[done * 48: (done + m) * 48].copy_(host[: m * 48])
+            done += m
+        torch.cuda.synchronize()
     t_gen = time.perf_counter() - t_gen
     if world > 1:
         span = torch.tensor([int(rec["start_ns"][-1] - rec["start_ns"][0]) + 1], dtype=torch.int64, device="cuda")
@@ -279,7 +301,10 @@ def main():
         rec["start_ns"] += np.uint64(shift)
         rec["end_ns"] += np.uint64(shift)
     first_start = int(rec["start_ns"][0])
-    dev = host.cuda(non_blocking=False)
+    if dev is None:
+        dev = host.cuda(non_blocking=False)
+    if streamed:
+        args.no_e2e = args.no_extras = True  # both need the whole trace in one host buffer
     stream = torch.cuda.Stream()
 
     def barrier():
@@ -304,6 +329,8 @@ def main():
     session = parallel.NativeSession(builder, rank, world) if world > 1 and args.mg_driver == "native" else None
 
     def step_device():
+        if streamed:
+            return builder.build_streamed_device(dev.data_ptr(), n_rec, window_records=args.window_records, n_parts=args.parts)
         if world == 1:
             return builder.build_device(dev.data_ptr(), n_rec, time_ordered=True)
         if session is not None:
@@ -471,6 +498,7 @@ def main():
                                    + (f" per window, {whole_rows} in the whole table" if whole_rows else "")
                                    + ("" if world == 1 else f"; one trace of {total_records} records in {world} time windows, samples exchanged by all-to-all, whole table on every rank"),
                        "records_per_gpu": n_rec, "l2": "inputs (48 B x records) larger than L2; no flush needed", "input_order": "start_ns-ordered (verified on device)",
+                       **({"build": "streamed: joined window by window, samples kept in key ranges that are sorted and reduced one after the other"} if streamed else {}),
                        "generated_s": round(t_gen, 2)},
             "timed_blocks": {"blocks": len(blocks), "steps_per_block": args.steps, "ms_per_step_min": blocks[0], "ms_per_step_median": ms_per_step,
                              "ms_per_step_max": blocks[-1], "timed_region_s": sum(blocks) * args.steps * 1e-3},
@@ -486,7 +514,7 @@ def main():
                            "ms_per_step": ms_e2e_step}
         if world == 1 and not args.no_cpu_baseline:
             m = min(CPU_SAMPLE_RECORDS, n_rec)
-            line["cpu_baseline"] = cpu_baseline(args.workload, m, rec[:m] if m == n_rec else None)
+            line["cpu_baseline"] = cpu_baseline(args.workload, m, rec[:m] if m == n_rec and not streamed else None)
         print(json.dumps(line), flush=True)
     if session is not None:
         session.close()  # collective: every rank unmaps the others' buffers before any rank frees its own

@@ -122,6 +122,13 @@ void ks_pinned_free(void* p);
  * (scheduler/postprocess.py:8-41 and the absent make_pair_eff.py named at scheduler_daemon.cpp:5,193,848).
  * Returns the number of pair rows; the tables stay in the handle until the next call. info may be NULL. */
 int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t flags, ks_table_info* info);
+/* The same table for a trace whose overlapping pairs do not fit one call (2^30 samples, twice in memory): decoded once,
+ * joined in windows of window_records launches (0 = 2^26), the samples kept in n_parts key ranges (0 = 16, at most 16) that
+ * are sorted and reduced one after the other.  No counterpart in the reference, whose script gives up on long logs by cutting
+ * them to 200,000 rows (scheduler/postprocess.py:12).  records: fewer than 2^30, ordered by start_ns (KS_ERR_NOT_ORDERED
+ * otherwise); flags: KS_ON_DEVICE, KS_KEY_TYPE.  info: ms_join = the windows (join + partition), ms_reduce = the key ranges. */
+int64_t ks_build_table_streamed(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t window_records, uint32_t n_parts,
+                                ks_table_info* info);
 int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows, uint32_t flags);
 int64_t ks_copy_key_rows(ks_handle* h, ks_key_row* dst, uint64_t capacity_rows, uint32_t flags);
 

@@ -56,6 +56,7 @@ struct ks_handle {
   DevBuf lookback, hist, tile_cnt, row_start, row_key, stats, big_rows, pair_rows;
   DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows, cta_rows;
   DevBuf tmp[6];
+  DevBuf stream_store;  // ks_build_table_streamed: the samples of all windows, one region per key range
   DevBuf tsv_text, tsv_lines, tsv_parsed, tsv_valid, tsv_cnt, tsv_vcnt, tsv_dict, tsv_maps;
   DevBuf tsv_kid, tsv_rowsolo, tsv_label, tsv_logtext, tsv_loglines, tsv_logcnt;
   uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0, tsv_max_kid = 0;
@@ -388,7 +389,8 @@ uint64_t sample_capacity(ks_handle* h) {
   return std::min<uint64_t>(h->samples[0].cap, h->samples[1].cap) / 16;
 }
 
-int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b, uint64_t tl_offset = 0, uint64_t n_halo = 0) {
+int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_a, uint32_t* idx_b, uint64_t tl_offset = 0, uint64_t n_halo = 0,
+             uint64_t n_own = 0) {
   if (n == 0) return 0;
   JoinArgs j{};
   j.tl_start = as<unsigned long long>(h->tl_start[tl]) + tl_offset;
@@ -401,7 +403,8 @@ int run_join(ks_handle* h, int tl, uint64_t n, uint64_t capacity, uint32_t* idx_
   j.idx_b = idx_b;
   j.capacity = capacity;
   j.ctl = h->d_ctl;
-  const unsigned grid = (unsigned)((n + kJoinTile - 1) / kJoinTile);
+  j.n_own = n_own;
+  const unsigned grid = (unsigned)(((n_own ? std::min(n_own, n) : n) + kJoinTile - 1) / kJoinTile);
   if (idx_a) k_join<true><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
   else k_join<false><<<grid, kJoinThreads, join_smem_bytes(), h->stream>>>(j);
   ++h->launches;
@@ -578,7 +581,10 @@ void mg_native_release(ks_handle* h, bool orderly);  // ks_mg_native.cuh
 
 float ev_ms(cudaEvent_t a, cudaEvent_t b) {
   float ms = 0.f;
-  cudaEventElapsedTime(&ms, a, b);
+  if (cudaEventElapsedTime(&ms, a, b) != cudaSuccess) {  // an event of a stage that did not run in this call: no time, and no
+    cudaGetLastError();                                   // error left behind for the next call to trip over
+    ms = 0.f;
+  }
   return ms;
 }
 
@@ -674,7 +680,7 @@ void ks_destroy(ks_handle* h) {
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
   DevBuf* bufs[] = {&h->records, &h->tl_start[0], &h->tl_start[1], &h->tl_dm[0], &h->tl_dm[1], &h->solo_stream, &h->keys_tmp,
                     &h->samples[0], &h->samples[1], &h->lookback, &h->hist, &h->tile_cnt, &h->row_start, &h->row_key, &h->stats,
-                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->upd_big, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5]};
+                    &h->big_rows, &h->pair_rows, &h->large_rows, &h->chunk_row, &h->chunk_idx, &h->large_hist, &h->small_rows, &h->small8_rows, &h->cta_rows, &h->tsv_text, &h->tsv_lines, &h->tsv_parsed, &h->tsv_valid, &h->tsv_cnt, &h->tsv_vcnt, &h->tsv_dict, &h->tsv_maps, &h->tsv_kid, &h->tsv_rowsolo, &h->tsv_label, &h->tsv_logtext, &h->tsv_loglines, &h->tsv_logcnt, &h->upd_rows, &h->upd_carry, &h->upd_scalars, &h->upd_list[0], &h->upd_list[1], &h->upd_list[2], &h->upd_list[3], &h->upd_ranks, &h->upd_pool, &h->upd_pool2, &h->upd_big, &h->tmp[0], &h->tmp[1], &h->tmp[2], &h->tmp[3], &h->tmp[4], &h->tmp[5], &h->stream_store};
   for (DevBuf* b : bufs) fr(b->p);
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& e : h->ev_sort) if (e) cudaEventDestroy(e);
@@ -1492,6 +1498,7 @@ int64_t ks_mg_finalize(ks_handle* h) {
 
 #include "ks_mg_native.cuh"
 #include "ks_update_host.cuh"
+#include "ks_stream_host.cuh"
 
 // =========================================================================================================
 // Agent timing log (TSV text) -> launch records on the device.  Three calls: parse (text in, counts out), dictionaries

@@ -33,7 +33,9 @@ struct JoinArgs {
   const unsigned long long* tl_start;
   const unsigned long long* tl_dm;
   const uint32_t* kid_of_slot;
-  uint64_t n;
+  uint64_t n;       // timeline entries that may be read
+  uint64_t n_own;   // 0, or: only the first n_own entries look for partners (the others are only found); a slice of a longer
+                    // timeline is joined this way, window after window
   uint4* samples;   // {sort key, duration of a, duration of b, span}
   uint32_t* idx_a;  // stage API: positions instead of samples (may be null)
   uint32_t* idx_b;
@@ -231,8 +233,9 @@ __global__ void __launch_bounds__(kJoinThreads) k_join(const JoinArgs a) {
   __shared__ JoinShared sh;
   const uint32_t tid = threadIdx.x;
   const uint64_t t0 = (uint64_t)blockIdx.x * kJoinTile;
-  if (t0 >= a.n) return;
-  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, a.n - t0);    // launches of this tile
+  const uint64_t n_own = a.n_own ? min(a.n_own, a.n) : a.n;
+  if (t0 >= n_own) return;
+  const uint32_t tn = (uint32_t)min((uint64_t)kJoinTile, n_own - t0);  // launches of this tile
   const uint32_t wn = (uint32_t)min((uint64_t)kJoinWindow, a.n - t0);  // staged entries
   // the window is in start order: it fits 31 bits relative to its first entry iff its last entry does
   const unsigned long long base = a.tl_start[t0];

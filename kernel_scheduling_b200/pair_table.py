@@ -75,6 +75,18 @@ class PairTableBuilder:
         self.info = info.as_dict()
         return rows
 
+    def build_streamed_device(self, records, n=None, window_records: int = 0, n_parts: int = 0, key_type: bool = False) -> int:
+        """The same table for traces whose overlapping pairs do not fit one call: joined window after window, the samples
+        kept in ``n_parts`` key ranges that are sorted and reduced one after the other (``ks_build_table_streamed``).
+        Records in start order.  Returns the number of pair rows; ``fetch`` copies the tables out."""
+        arg = self._records_arg(records, n)
+        flags = arg[2] | (_lib.KEY_TYPE if key_type else 0)
+        info = _lib.KsTableInfo()
+        rows = self._check(self._lib.ks_build_table_streamed(self._h, arg[0], arg[1], flags, int(window_records), int(n_parts), ctypes.byref(info)),
+                           "ks_build_table_streamed")
+        self.info = info.as_dict()
+        return rows
+
     def _pinned(self, slot: str, n: int, dtype) -> np.ndarray:
         """A page-locked array owned by the builder (grown on demand, reused by later calls)."""
         need = max(n, 1) * dtype.itemsize

@@ -200,3 +200,50 @@ def test_full_size_c2_properties(builder):
             assert np.allclose(pairs2[c], pairs[c], rtol=1e-6, atol=0, equal_nan=True), c
         else:
             assert np.array_equal(pairs2[c], pairs[c], equal_nan=True), c
+
+
+def _streamed(builder, rec, **kw):
+    import torch
+
+    dev = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).cuda() if len(rec) else None
+    builder.build_streamed_device(dev.data_ptr() if len(rec) else 0, len(rec), **kw) if len(rec) else builder.build_streamed_device(rec, **kw)
+    return builder.fetch()
+
+
+@pytest.mark.parametrize("cfg,n,window,parts", [("c1", 60_000, 7_000, 3), ("c2", 400_000, 150_000, 16), ("c3", 300_000, 40_000, 5), ("c4", 2_000_000, 300_000, 7)])
+def test_streamed_build_equals_oracle(builder, cfg, n, window, parts):
+    """Windows much smaller than the trace, launches that overlap across window ends, key ranges reduced one by one."""
+    rec = trace.generate_fast(trace.config(cfg, n))
+    keys, pairs = _streamed(builder, rec, window_records=window, n_parts=parts)
+    okeys, opairs = CO.build_pair_table(rec)
+    assert_tables_match(keys, pairs, okeys, opairs)
+    assert builder.info["n_pairs"] == int(opairs["count"].sum()) and builder.info["n_rows"] == len(pairs)
+    # ... and the ordinary call on the same handle afterwards
+    keys1, pairs1 = builder.build(rec, time_ordered=True)
+    assert keys1.tobytes() == keys.tobytes()
+    assert_tables_match(keys1, pairs1, okeys, opairs)
+
+
+def test_streamed_build_edge_cases(builder):
+    from kernel_scheduling_b200 import _lib
+
+    rec = trace.generate(trace.config("c1", 5000), interleave_solo=True)
+    for m, window, parts in ((0, 100, 4), (1, 100, 4), (2, 1, 2), (777, 50, 16), (5000, 5000, 1), (5000, 100_000, 0)):
+        keys, pairs = _streamed(builder, rec[:m], window_records=window, n_parts=parts)
+        assert_tables_match(keys, pairs, *O.build_pair_table(rec[:m]))
+    keys, pairs = _streamed(builder, rec, window_records=600, n_parts=3, key_type=True)
+    assert_tables_match(keys, pairs, *O.build_pair_table(rec, key_mode=O.KEY_TYPE))
+    # a launch that spans every window
+    n = 4000
+    start = np.arange(n, dtype=np.uint64) * 100 + 1000
+    dur = np.full(n, 60, dtype=np.uint64)
+    tenant = 1 + (np.arange(n) % 2)
+    tenant[3], dur[3] = 0, 100 * n
+    long = pack_records(tenant, np.ones((n, 3)), np.ones((n, 3)) * 32, np.zeros(n), tenant, np.zeros(n, bool), start, start + dur)
+    keys, pairs = _streamed(builder, long, window_records=250, n_parts=4)
+    assert_tables_match(keys, pairs, *O.build_pair_table(long))
+    with pytest.raises(_lib.KsError) as e:
+        _streamed(builder, trace.shuffled(rec), window_records=1000, n_parts=2)
+    assert e.value.status == _lib.ERR_NOT_ORDERED
+    keys, pairs = builder.build(rec, time_ordered=True)  # the handle stays usable
+    assert_tables_match(keys, pairs, *O.build_pair_table(rec))
