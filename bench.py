@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--records", type=int, default=None, help="records per GPU (default: the configuration's own size, capped by --max-records)")
     ap.add_argument("--max-records", type=int, default=100_000_000)
     ap.add_argument("--verify", action="store_true", help="compare the table of the timed workload with the CPU oracle at full size (slow; not part of the default run)")
+    ap.add_argument("--windows", type=int, default=10_000, help="--workload c5: windows of 65,536 launches to merge")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--streamed", action="store_true", help="one GPU: the window-by-window build (default for more than 160 M records)")
@@ -168,63 +169,46 @@ def workload_label(workload: str) -> str:
 
 def run_online(args, rank):
     """--workload c5: the resident table.  A step is one window of 65,536 launches merged into the table; ``value`` is the
-    median latency of an update with the window already in device memory, ``e2e`` the same with the window in pinned host
-    memory (its copy to the device inside the call).  One GPU: the path does not shard (a table is one sequence of windows)."""
+    median latency of an update with the window already in device memory over ``--windows`` windows (10,000 as the
+    configuration states), ``e2e`` the same for the last 200 windows, which arrive in pinned host memory (their copy to the
+    device inside the call).  One GPU: the path does not shard (a table is one sequence of windows)."""
     if rank != 0:
         return
     import torch
 
-    from kernel_scheduling_b200 import trace
-    from kernel_scheduling_b200.pair_table import PairTableBuilder
+    from kernel_scheduling_b200 import online, trace
     from kernel_scheduling_b200.records import RECORD_DTYPE
-    from oracle import pair_table_oracle as oracle
+    from oracle import c_oracle
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the GPU arm")
     per = 65536
-    warm, steps = max(args.warmup, 3), max(args.steps, 1)
-    windows = warm + steps
-    rec = trace.generate(trace.config("c5", 2 * windows * per), interleave_solo=True)
-    dev = torch.from_numpy(rec.view(np.uint8).reshape(-1)).cuda()
-    torch.cuda.synchronize()
+    windows = max(args.windows, 300)
     sampler = ClockSampler(0)
     sampler.start()
     sampler.wait_first(5.0)
-    lat = {"device": [], "host": []}
-    launches = 0
-    with PairTableBuilder(device=0) as b:
-        b.update_begin()
-        l0 = b.launch_count
-        for w in range(windows):  # windows already in device memory
-            t0 = time.perf_counter()
-            b.update(dev.data_ptr() + w * per * 48, per)
-            lat["device"].append(1e3 * (time.perf_counter() - t0))
-        launches = (b.launch_count - l0) // windows
-        pinned = b.pinned_records(per)
-        for w in range(windows, 2 * windows):  # windows in pinned host memory
-            pinned[:] = rec[w * per: (w + 1) * per]
-            t0 = time.perf_counter()
-            b.update(pinned)
-            lat["host"].append(1e3 * (time.perf_counter() - t0))
-        keys, pairs = b.update_table()
-        b.update_end()
+    res = online.run(windows, per, verify=args.verify, host_windows=200)
     clocks = sampler.stop()
+    # what the reference's offline flow would have to do per refresh: rebuild the table over the launches so far
+    m = min(CPU_SAMPLE_RECORDS, windows * per)
+    rec = trace.generate_fast(trace.config("c5", m), interleave_solo=True)
     t0 = time.perf_counter()
-    oracle.build_pair_table(rec[: windows * per], check_bijection=False)
+    c_oracle.build_pair_table(rec)
     cpu_ms = 1e3 * (time.perf_counter() - t0)
-    dev_ms, host_ms = lat["device"][warm:], lat["host"][warm:]
     line = {
-        "metric": "per-window update latency (p50)", "value": float(np.percentile(dev_ms, 50)), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": warm,
-        "ms_per_step": float(np.mean(dev_ms)), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "u32/u64 integer, f64 tables",
+        "metric": "per-window update latency (p50)", "value": res["p50"], "unit": "ms", "n_gpus": 1, "steps": windows - 200, "warmup": 5,
+        "ms_per_step": res["mean"], "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "u32/u64 integer, f64 tables",
         "data": "synthetic",
-        "config": {"workload": f"c5: resident table, windows of {per} launches, {len(keys)} keys, {len(pairs)} table rows after {2 * windows} windows",
+        "config": {"workload": f"c5: resident table, {windows} windows of {per} launches, {res['keys']} keys, {res['pair_rows']} table rows, largest row {res['largest_row_samples']} samples",
                    "l2": "a window is 3 MB: the latency of a short chain of launches, not a bandwidth figure"},
-        "p99": float(np.percentile(dev_ms, 99)), "clocks": clocks, "gpu_launches": int(launches * steps),
-        "e2e": {"value": float(np.percentile(host_ms, 50)), "unit": "ms", "h2d_bytes_per_step": per * RECORD_DTYPE.itemsize, "d2h_bytes_per_step": 128,
-                "p99": float(np.percentile(host_ms, 99))},
+        "p99": res["p99"], "max": res["max"], "p50_by_quarter_of_the_run": res["p50_by_quarter"], "device_ms_p50": res["device_ms_p50"],
+        "readout_ms": res["readout_ms"], "verified_against_batch_build": res["verified_against_batch_build"],
+        "clocks": clocks, "gpu_launches": int(res["gpu_launches_per_window"] * (windows - 200)),
+        "e2e": {"value": res["host_windows"]["p50"], "unit": "ms", "h2d_bytes_per_step": per * RECORD_DTYPE.itemsize, "d2h_bytes_per_step": 128,
+                "p99": res["host_windows"]["p99"], "windows": res["host_windows"]["windows"]},
         "roofline": None,
-        "cpu_baseline": {"value": cpu_ms, "unit": "ms", "cores": 1, "kind": "port",
-                         "sample": f"the reference has no incremental mode: one rebuild of the table over the first {windows * per} launches with the numpy oracle, 1 thread"},
+        "cpu_baseline": {"value": cpu_ms, "unit": "ms", "cores": c_oracle.host_threads(), "kind": "port",
+                         "sample": f"the reference has no incremental mode: one rebuild of the table over {m} launches with the C/OpenMP oracle, all host threads"},
     }
     print(json.dumps(line), flush=True)
 

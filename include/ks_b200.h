@@ -255,6 +255,28 @@ int64_t ks_tsv_dictionary(ks_handle* h, int which, uint64_t* hashes, uint64_t* w
 int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags);
 int64_t ks_tsv_finish(ks_handle* h, const uint32_t* name_ids, const uint32_t* tenants, uint32_t solo, ks_record* out, uint64_t capacity, uint32_t flags);
 
+/* Column extraction from any tab-separated log with a header line, on the device: the daemon's decision log
+ * (scheduler/scheduler_daemon.cpp:674-676, one row per finished kernel; fields :585-605) and the agent's timing log
+ * (scheduler/agent.cpp:692-705).  Per data line and requested column (at most 16) one 64-bit word, out[c * capacity + row]:
+ *   KS_COL_U64    decimal integer; blank or malformed = UINT64_MAX
+ *   KS_COL_MILLI  decimal with up to three fraction digits (printf "%.3f") -> value x 1000; blank = UINT64_MAX
+ *   KS_COL_DIMS   "(x, y, z)" or "x,y,z" -> x | y << 21 | z << 42 (each below 2^21); malformed = UINT64_MAX
+ *   KS_COL_HASH   64-bit FNV-1a of the field
+ *   KS_COL_SPAN   offset of the field in the text << 20 | its length
+ * Returns the number of data lines (only the first `capacity` are written).  KS_ON_DEVICE: text and out are device pointers. */
+#define KS_COL_U64 0u
+#define KS_COL_MILLI 1u
+#define KS_COL_DIMS 2u
+#define KS_COL_HASH 3u
+#define KS_COL_SPAN 4u
+int64_t ks_tsv_extract(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t n_cols, const uint32_t* cols, const uint32_t* kinds, uint64_t* out,
+                       uint64_t capacity, uint32_t flags);
+/* Per segment of `values` (segment s = [offsets[s], offsets[s+1])) a histogram of n_bins counters: bin = the value itself
+ * (log2_bins = 0) or its bit length, 0 for 0 (log2_bins = 1), clamped to the last bin.  out: n_segments x n_bins uint32.
+ * The queue-wait and batch-size histograms per kernel of the decision-log analytics. */
+int64_t ks_segment_hist(ks_handle* h, const uint32_t* values, const uint64_t* offsets, uint64_t n_segments, uint32_t n_bins, uint32_t log2_bins,
+                        uint32_t flags, uint32_t* out);
+
 /* ---- the resident table: windows of new launches merged into statistics that stay in HBM (BASELINE config 5: "online
  * incremental mode"; the reference has no such path, its tables are rebuilt offline).  At any time the table read out is
  * exactly the one ks_build_table gives for all launches so far: counts, sums, minima and maxima are accumulators, and
@@ -307,8 +329,9 @@ typedef struct ks_synth_tenant {
   uint64_t n_launches;
   double gap_mean_ns;      /* mean idle gap in front of a co-run launch */
 } ks_synth_tenant;
+#define KS_SYNTH_INTERLEAVE_SOLO 1u /* solo launches take their turn on their tenant's timeline instead of a phase of their own */
 int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_tenants, double solo_fraction, double jitter_sigma, double corun_slowdown,
-                       uint64_t seed, uint64_t t0_ns, ks_record* out, uint64_t capacity, uint32_t threads);
+                       uint64_t seed, uint64_t t0_ns, ks_record* out, uint64_t capacity, uint32_t threads, uint32_t flags);
 
 /* scheduler/kernel_key.hpp:13-55 ncu_function_base: symbol -> short kernel name.  Host-side (strings).
  * Writes a NUL-terminated string; returns its length, or -KS_ERR_CAPACITY. */

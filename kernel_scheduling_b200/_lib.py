@@ -25,6 +25,7 @@ TIMING = 8
 ERR_ARG, ERR_CUDA, ERR_RECORD, ERR_NOT_ORDERED, ERR_TOO_MANY_KEYS = 1, 2, 3, 4, 5
 ERR_TABLE_FULL, ERR_CAPACITY, ERR_WAIT, ERR_DUPLICATE, ERR_TOO_LARGE, ERR_COMM = 6, 7, 8, 9, 10, 11
 ERR_REBUILD = 12
+COL_U64, COL_MILLI, COL_DIMS, COL_HASH, COL_SPAN = 0, 1, 2, 3, 4
 
 
 class KsConfig(ctypes.Structure):
@@ -96,6 +97,8 @@ KS_API = [
     ("ks_tsv_parse", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_tsv_dictionary", [c_void_p, c_int, c_void_p, c_void_p], c_int64),
     ("ks_tsv_label", [c_void_p, c_void_p, c_uint64, c_uint64, c_uint32], c_int64),
+    ("ks_tsv_extract", [c_void_p, c_void_p, c_uint64, c_uint32, POINTER(c_uint32), POINTER(c_uint32), c_void_p, c_uint64, c_uint32], c_int64),
+    ("ks_segment_hist", [c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_uint32, c_void_p], c_int64),
     ("ks_tsv_finish", [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_function_base", [c_char_p, c_char_p, c_uint64], c_int64),
     ("ks_update_begin", [c_void_p, c_uint32], c_int64),
@@ -105,7 +108,7 @@ KS_API = [
     ("ks_kernel_key", [c_uint32, POINTER(c_uint32), POINTER(c_uint32), c_uint32, c_uint32, c_uint32], c_uint64),
     ("ks_pairtab_publish", [c_char_p, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(c_char_p), c_uint64,
                             POINTER(c_char_p), c_uint64, c_uint64], c_int64),
-    ("ks_synth_trace", [POINTER(KsSynthTenant), c_uint32, c_double, c_double, c_double, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32], c_int64),
+    ("ks_synth_trace", [POINTER(KsSynthTenant), c_uint32, c_double, c_double, c_double, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_uint32], c_int64),
     ("ks_pairtab_unlink", [c_char_p], c_int),
     ("ks_pairtab_last_error", [], c_char_p),
 ]

@@ -1578,6 +1578,87 @@ int64_t ks_tsv_parse(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t 
   return (int64_t)h->tsv_n_valid;
 }
 
+int64_t ks_tsv_extract(ks_handle* h, const char* text, uint64_t n_bytes, uint32_t n_cols, const uint32_t* cols, const uint32_t* kinds, uint64_t* out,
+                       uint64_t capacity, uint32_t flags) {
+  if (!h || (!text && n_bytes) || (flags & ~KS_ON_DEVICE) || !n_cols || n_cols > kTsvMaxCols || !cols || !kinds || (!out && capacity)) return -KS_ERR_ARG;
+  for (uint32_t c = 0; c < n_cols; ++c) if (kinds[c] > KS_COL_SPAN) return fail(h, KS_ERR_ARG, "ks_tsv_extract: unknown column kind");
+  if (n_bytes >= (1ull << 40)) return fail(h, KS_ERR_TOO_LARGE, "ks_tsv_extract: text of 2^40 bytes or more");
+  KS_CUDA(h, cudaSetDevice(h->device));
+  { int r = reset_run(h); if (r) return r; }
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  const unsigned char* d_text = nullptr;
+  { int r = stage_in<unsigned char>(h, h->tsv_text, reinterpret_cast<const unsigned char*>(text), n_bytes, dev, &d_text); if (r) return r; }
+  h->tsv_dev_text = d_text;
+  h->tsv_n_bytes = n_bytes;
+  h->tsv_n_lines = h->tsv_n_valid = 0;
+  if (n_bytes == 0) return 0;
+  const uint64_t ntiles = (n_bytes + kTsvTile - 1) / kTsvTile;
+  KS_ENSURE(h, h->tsv_cnt, (ntiles + 1) * 4);
+  TsvArgs a = tsv_args(h);
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * 8);
+  k_tsv_nl_count<<<grid, 256, 0, h->stream>>>(a);
+  k_tsv_scan<<<1, 1024, 0, h->stream>>>(a.tile_cnt, ntiles, &h->d_ctl->scratch0, d_text, n_bytes);
+  { int r = read_ctl(h); if (r) return r; }
+  const uint64_t n_lines = h->h_ctl->scratch0;
+  h->tsv_n_lines = n_lines;
+  KS_ENSURE(h, h->tsv_lines, (n_lines + 2) * 8);
+  a = tsv_args(h);
+  k_tsv_nl_fill<<<grid, 256, 0, h->stream>>>(a);
+  h->launches += 3;
+  const uint64_t rows = n_lines ? n_lines - 1 : 0, take = std::min(rows, capacity);
+  if (take) {
+    TsvExtractArgs x{};
+    x.text = d_text;
+    x.n_bytes = n_bytes;
+    x.line_start = as<unsigned long long>(h->tsv_lines);
+    x.n_lines = n_lines;
+    x.n_cols = n_cols;
+    for (uint32_t c = 0; c < n_cols; ++c) { x.col[c] = cols[c]; x.kind[c] = kinds[c]; }
+    x.capacity = capacity;
+    if (dev) {
+      x.out = reinterpret_cast<unsigned long long*>(out);
+    } else {
+      KS_ENSURE(h, h->tsv_parsed, (size_t)n_cols * capacity * 8);
+      x.out = as<unsigned long long>(h->tsv_parsed);
+    }
+    k_tsv_extract<<<(int)std::max<uint64_t>(1, std::min<uint64_t>((n_lines + 255) / 256, (uint64_t)h->sm_count * 16)), 256, 0, h->stream>>>(x);
+    ++h->launches;
+    KS_CUDA(h, cudaGetLastError());
+    if (!dev) {
+      for (uint32_t c = 0; c < n_cols; ++c) { int r = copy_out(h, out + (size_t)c * capacity, x.out + (size_t)c * capacity, take * 8, false); if (r) return r; }
+    }
+  }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)rows;
+}
+
+int64_t ks_segment_hist(ks_handle* h, const uint32_t* values, const uint64_t* offsets, uint64_t n_segments, uint32_t n_bins, uint32_t log2_bins, uint32_t flags,
+                        uint32_t* out) {
+  if (!h || !offsets || (n_segments && !out) || !n_bins || n_bins > 4096 || (flags & ~KS_ON_DEVICE)) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  if (n_segments == 0) return 0;
+  const bool dev = (flags & KS_ON_DEVICE) != 0;
+  uint64_t n_values;
+  const unsigned long long* d_off = nullptr;
+  { int r = stage_in<unsigned long long>(h, h->tmp[0], reinterpret_cast<const unsigned long long*>(offsets), n_segments + 1, dev, &d_off); if (r) return r; }
+  if (dev) { KS_CUDA(h, cudaMemcpyAsync(&n_values, offsets + n_segments, 8, cudaMemcpyDeviceToHost, h->stream)); KS_CUDA(h, cudaStreamSynchronize(h->stream)); }
+  else n_values = offsets[n_segments];
+  if (!values && n_values) return -KS_ERR_ARG;
+  const uint32_t* d_val = nullptr;
+  { int r = stage_in<uint32_t>(h, h->tmp[1], values, n_values, dev, &d_val); if (r) return r; }
+  const size_t bytes = (size_t)n_segments * n_bins * 4;
+  uint32_t* d_out = out;
+  if (!dev) { KS_ENSURE(h, h->tmp[2], bytes); d_out = as<uint32_t>(h->tmp[2]); }
+  KS_CUDA(h, cudaMemsetAsync(d_out, 0, bytes, h->stream));
+  k_segment_hist<<<(int)std::max<uint64_t>(1, std::min<uint64_t>((n_segments + 7) / 8, (uint64_t)h->sm_count * 8)), 256, 0, h->stream>>>(d_val, d_off, n_segments, n_bins,
+                                                                                                                                  log2_bins, d_out);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  if (!dev) { int r = copy_out(h, out, d_out, bytes, false); if (r) return r; }
+  KS_CUDA(h, cudaStreamSynchronize(h->stream));
+  return (int64_t)n_segments;
+}
+
 // The profiling daemon's log of the same run: which launches of process `pid` ran alone (solo samples) and which in a
 // gang.  Applies to the text parsed last; rows the log does not mention are dropped.  Returns the rows that remain.
 int64_t ks_tsv_label(ks_handle* h, const char* log_text, uint64_t n_bytes, uint64_t pid, uint32_t flags) {

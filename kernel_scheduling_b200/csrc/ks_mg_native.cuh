@@ -664,6 +664,19 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   }
   tr.mark("allgather4");
   { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 2
+  {
+    // A key range with more rows than the row arrays were sized for (and no limit asked for): every rank sees it in the
+    // gathered headers, sizes its arrays for the largest range and the whole build is made again, by all ranks alike.
+    uint64_t most_rows = 0;
+    for (int q = 0; q < world; ++q) {
+      const Control& c = mg_head(h, H, q).ctl;
+      if ((c.err & kErrTooLarge) && !(c.err & ~(kErrTooLarge | kErrUnordered))) most_rows = std::max<uint64_t>(most_rows, c.pad2[0]);
+    }
+    if (most_rows > h->cfg.max_pair_rows && most_rows < (1ull << 31) && h->rows_auto) {
+      h->cfg.max_pair_rows = (uint32_t)std::min<uint64_t>(most_rows + most_rows / 8, 0x7FFFFFFFull);
+      return ks_mg_build(h, records, n_owned, flags, info);
+    }
+  }
   { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
   std::vector<uint64_t> row_off(world + 1, 0);
   for (int q = 0; q < world; ++q) {

@@ -44,6 +44,7 @@ struct Launch {
 struct Model {
   double solo_fraction, jitter_sigma, corun_slowdown;
   uint64_t seed;
+  bool interleave;  // solo launches take their turn on their tenant's timeline instead of a phase of their own
 };
 
 inline Launch make_launch(const ks_synth_tenant& T, const Model& m, uint64_t i) {
@@ -79,7 +80,7 @@ void parallel_for(uint64_t n, unsigned threads, F&& fn) {
 
 struct CoLaunch {
   uint64_t start;
-  uint32_t key, dur;
+  uint32_t key, dur;  // bit 31 of key: a solo launch (interleaved traces only)
 };
 
 inline void write_record(ks_record* o, const ks_synth_tenant& T, uint32_t key, bool solo, uint64_t start, uint32_t dur) {
@@ -95,7 +96,7 @@ constexpr uint64_t kChunk = 1u << 18;
 }  // namespace
 
 extern "C" int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_tenants, double solo_fraction, double jitter_sigma, double corun_slowdown,
-                                  uint64_t seed, uint64_t t0_ns, ks_record* out, uint64_t capacity, uint32_t threads) {
+                                  uint64_t seed, uint64_t t0_ns, ks_record* out, uint64_t capacity, uint32_t threads, uint32_t flags) {
   if (!tenants || !n_tenants || n_tenants > 256 || (!out && capacity)) return -KS_ERR_ARG;
   uint64_t total = 0;
   for (uint32_t t = 0; t < n_tenants; ++t) {
@@ -105,7 +106,8 @@ extern "C" int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_ten
   }
   if (total > capacity) return -KS_ERR_CAPACITY;
   if (!threads) threads = std::max(1u, std::thread::hardware_concurrency());
-  const Model m{solo_fraction, jitter_sigma, corun_slowdown, seed};
+  if (flags & ~KS_SYNTH_INTERLEAVE_SOLO) return -KS_ERR_ARG;
+  const Model m{solo_fraction, jitter_sigma, corun_slowdown, seed, (flags & KS_SYNTH_INTERLEAVE_SOLO) != 0};
 
   // ---- pass A: per chunk of every tenant, the number of solo launches, their time, the co-run launches and their steps
   struct Chunk {
@@ -127,7 +129,7 @@ extern "C" int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_ten
     const ks_synth_tenant& T = tenants[c.tenant];
     for (uint64_t i = c.first; i < c.first + c.count; ++i) {
       const Launch L = make_launch(T, m, i);
-      if (L.solo) { ++c.n_solo; c.solo_time += (uint64_t)L.dur + 500; }
+      if (L.solo && !m.interleave) { ++c.n_solo; c.solo_time += (uint64_t)L.dur + 500; }
       else { ++c.n_co; c.co_step += L.gap + L.dur; }
     }
   });
@@ -155,13 +157,13 @@ extern "C" int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_ten
     uint64_t si = c.n_solo, st = c.solo_time, cj = c.n_co, ct = c.co_step;
     for (uint64_t i = c.first; i < c.first + c.count; ++i) {
       const Launch L = make_launch(T, m, i);
-      if (L.solo) {
+      if (L.solo && !m.interleave) {
         write_record(out + si, T, L.key, true, t0_ns + st, L.dur);
         ++si;
         st += (uint64_t)L.dur + 500;
       } else {
         ct += L.gap + L.dur;  // gap, launch, gap, launch ...
-        co[c.tenant][cj++] = CoLaunch{phase2 + ct - L.dur, L.key, L.dur};
+        co[c.tenant][cj++] = CoLaunch{phase2 + ct - L.dur, L.key | (L.solo ? 0x80000000u : 0u), L.dur};
       }
     }
   });
@@ -198,7 +200,7 @@ extern "C" int64_t ks_synth_trace(const ks_synth_tenant* tenants, uint32_t n_ten
           if (pos[t] < end[t] && (best < 0 || co[t][pos[t]].start < bs)) { best = (int)t; bs = co[t][pos[t]].start; }  // ties: lower tenant first
         if (best < 0) break;
         const CoLaunch& L = co[best][pos[best]++];
-        write_record(out + o++, tenants[best], L.key, false, L.start, L.dur);
+        write_record(out + o++, tenants[best], L.key & 0x7FFFFFFFu, (L.key >> 31) != 0, L.start, L.dur);
       }
     });
   }

@@ -198,8 +198,8 @@ __global__ void __launch_bounds__(256) k_tsv_parse(const TsvArgs a) {
     // field boundaries: walk the tabs
     uint64_t fs = b;
     int col = 0;
-    uint64_t name_off = 0;
-    uint32_t name_len = 0, model_slot = 0, kid = 0xFFFFFFFFu;
+    uint64_t name_off = 0, model_off = 0;
+    uint32_t name_len = 0, model_len = 0, kid = 0xFFFFFFFFu;
     bool have_name = false, have_model = false, have_start = false, have_end = false, have_block = false, have_grid = false;
     for (uint64_t i = b; ok && i <= e; ++i) {
       if (i == e || a.text[i] == '\t') {
@@ -210,21 +210,110 @@ __global__ void __launch_bounds__(256) k_tsv_parse(const TsvArgs a) {
         else if (col == 9) have_start = tsv_u64(f, fl, reinterpret_cast<unsigned long long*>(&r.start_ns));
         else if (col == 10) have_end = tsv_u64(f, fl, reinterpret_cast<unsigned long long*>(&r.end_ns));
         else if (col == 14) have_block = tsv_dims(f, fl, r.block);
-        else if (col == 15) { model_slot = tsv_dict_insert(a.model_hash, a.model_where, kTsvModelSlots, fnv1a(f, fl), fs, fl, a.ctl); have_model = true; }
+        else if (col == 15) { model_off = fs; model_len = fl; have_model = true; }
         else if (col == 16) have_grid = tsv_dims(f, fl, r.grid);
         fs = i + 1;
         ++col;
       }
     }
     ok = ok && have_name && have_start && have_end && have_block && have_grid && have_model && name_len < (1u << 20);
-    if (ok) {
+    if (ok) {  // only rows that are kept enter the dictionaries: models and names are numbered over the kept rows
       r.name_id = tsv_dict_insert(a.name_hash, a.name_where, kTsvNameSlots, fnv1a(a.text + name_off, name_len), name_off, name_len, a.ctl);
+      const uint32_t model_slot = tsv_dict_insert(a.model_hash, a.model_where, kTsvModelSlots, fnv1a(a.text + model_off, model_len), model_off, model_len, a.ctl);
       r.smem_word = model_slot << 24;  // replaced by the tenant id in k_tsv_finish
     }
     a.parsed[line] = r;
     a.valid[line] = ok ? 1 : 0;
     a.kernel_id[line] = kid;
     if (ok && kid != 0xFFFFFFFFu) atomicMax(&a.ctl->max_start, (unsigned long long)kid);
+  }
+}
+
+// ---- generic column extraction: any tab-separated log with a header line (the daemon's decision log,
+// scheduler_daemon.cpp:674-676; the agent's timing log).  One thread per data line walks the tabs once; every requested
+// column becomes one 64-bit word per line:
+//   KS_COL_U64    decimal integer ("123", also "123.0"); blank or malformed -> all ones
+//   KS_COL_MILLI  decimal with up to three fraction digits, as printf("%.3f") writes it -> the value x 1000; blank -> all ones
+//   KS_COL_DIMS   "(x, y, z)" or "x,y,z" -> x | y << 21 | z << 42 (each below 2^21); malformed -> all ones
+//   KS_COL_HASH   64-bit FNV-1a of the field's bytes (an empty field hashes like any other)
+//   KS_COL_SPAN   offset of the field in the text << 20 | its length (to read a string back on the host)
+constexpr uint32_t kTsvMaxCols = 16;
+struct TsvExtractArgs {
+  const unsigned char* text;
+  uint64_t n_bytes;
+  const unsigned long long* line_start;
+  uint64_t n_lines;  // including the header line
+  uint32_t n_cols;
+  uint32_t col[kTsvMaxCols], kind[kTsvMaxCols];
+  unsigned long long* out;  // [n_cols][capacity]
+  uint64_t capacity;
+};
+
+__device__ __forceinline__ unsigned long long tsv_field(const unsigned char* f, uint32_t fl, uint64_t off, uint32_t kind) {
+  const unsigned long long none = ~0ull;
+  if (kind == KS_COL_U64) {
+    unsigned long long v;
+    return tsv_u64(f, fl, &v) ? v : none;
+  }
+  if (kind == KS_COL_MILLI) {
+    if (fl == 0) return none;
+    unsigned long long v = 0;
+    uint32_t i = 0, frac = 0;
+    for (; i < fl && f[i] >= '0' && f[i] <= '9'; ++i) v = v * 10ull + (f[i] - '0');
+    if (i == 0) return none;
+    if (i < fl) {
+      if (f[i] != '.') return none;
+      for (++i; i < fl && frac < 3; ++i, ++frac) {
+        if (f[i] < '0' || f[i] > '9') return none;
+        v = v * 10ull + (f[i] - '0');
+      }
+      for (; i < fl; ++i) if (f[i] < '0' || f[i] > '9') return none;  // further digits are cut off
+    }
+    for (; frac < 3; ++frac) v *= 10ull;
+    return v;
+  }
+  if (kind == KS_COL_DIMS) {
+    uint32_t d[3];
+    if (!tsv_dims(f, fl, d) || d[0] >= (1u << 21) || d[1] >= (1u << 21) || d[2] >= (1u << 21)) return none;
+    return (unsigned long long)d[0] | ((unsigned long long)d[1] << 21) | ((unsigned long long)d[2] << 42);
+  }
+  if (kind == KS_COL_HASH) return fnv1a(f, fl);
+  return (off << 20) | (fl & 0xFFFFFu);  // KS_COL_SPAN
+}
+
+__global__ void __launch_bounds__(256) k_tsv_extract(const TsvExtractArgs a) {
+  for (uint64_t line = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x + 1; line < a.n_lines; line += (uint64_t)gridDim.x * blockDim.x) {  // line 0: header
+    const uint64_t row = line - 1;
+    if (row >= a.capacity) continue;
+    const uint64_t b = a.line_start[line];
+    uint64_t e = (line + 1 < a.n_lines || (a.n_bytes && a.text[a.n_bytes - 1] == '\n')) ? a.line_start[line + 1] - 1 : a.n_bytes;
+    if (e > b && a.text[e - 1] == '\r') --e;
+    for (uint32_t c = 0; c < a.n_cols; ++c) a.out[(size_t)c * a.capacity + row] = a.kind[c] == KS_COL_HASH ? fnv1a(a.text, 0) : ~0ull;  // a missing column
+    uint64_t fs = b;
+    uint32_t col = 0;
+    for (uint64_t i = b; i <= e; ++i) {
+      if (i == e || a.text[i] == '\t') {
+        for (uint32_t c = 0; c < a.n_cols; ++c)
+          if (a.col[c] == col) a.out[(size_t)c * a.capacity + row] = tsv_field(a.text + fs, (uint32_t)(i - fs), fs, a.kind[c]);
+        fs = i + 1;
+        ++col;
+      }
+    }
+  }
+}
+
+// histogram of the values of every segment: log2 bins (bin = bit length of the value, 0..32) or linear bins (value, clamped)
+__global__ void __launch_bounds__(256) k_segment_hist(const uint32_t* __restrict__ values, const unsigned long long* __restrict__ offsets, uint64_t n_segments,
+                                                      uint32_t n_bins, uint32_t log2_bins, uint32_t* __restrict__ out) {
+  const uint32_t lane = lane_id();
+  const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+  for (uint64_t s = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); s < n_segments; s += warps) {
+    const unsigned long long lo = offsets[s], hi = offsets[s + 1];
+    for (unsigned long long i = lo + lane; i < hi; i += 32) {
+      const uint32_t v = values[i];
+      const uint32_t bin = min(log2_bins ? (uint32_t)(32 - __clz(v)) : v, n_bins - 1);
+      atomicAdd(&out[s * n_bins + bin], 1u);
+    }
   }
 }
 

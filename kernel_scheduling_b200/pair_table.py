@@ -171,6 +171,27 @@ class PairTableBuilder:
         self._check(self._lib.ks_segment_stats(self._h, _lib.ptr(values), _lib.ptr(offsets), nseg, 0, _lib.ptr(out)), "ks_segment_stats")
         return out
 
+    def segment_hist(self, values: np.ndarray, offsets: np.ndarray, n_bins: int, log2_bins: bool = False) -> np.ndarray:
+        """-> (n_segments, n_bins) uint32: per segment a histogram of its values (bin = value, or its bit length; clamped)."""
+        values = np.ascontiguousarray(values, dtype=np.uint32)
+        offsets = np.ascontiguousarray(offsets, dtype=np.uint64)
+        nseg = len(offsets) - 1
+        out = np.zeros((max(nseg, 0), n_bins), dtype=np.uint32)
+        self._check(self._lib.ks_segment_hist(self._h, _lib.ptr(values), _lib.ptr(offsets), nseg, n_bins, int(log2_bins), 0, _lib.ptr(out)), "ks_segment_hist")
+        return out
+
+    def tsv_extract(self, text, columns) -> list:
+        """Columns of a tab-separated log with a header line, parsed on the device.  ``text``: bytes or a uint8 array;
+        ``columns``: [(column index, kind)] with kind one of ``_lib.COL_*``.  -> one uint64 array per requested column
+        (all ones where a field is blank or malformed)."""
+        text = np.frombuffer(text, dtype=np.uint8) if isinstance(text, (bytes, bytearray, memoryview)) else np.ascontiguousarray(text, dtype=np.uint8)
+        cols = (ctypes.c_uint32 * len(columns))(*[int(c) for c, _ in columns])
+        kinds = (ctypes.c_uint32 * len(columns))(*[int(k) for _, k in columns])
+        cap = max(int(np.count_nonzero(text == 10)) + 1, 1)  # at least as many as there are lines
+        out = np.zeros((len(columns), cap), dtype=np.uint64)
+        rows = self._check(self._lib.ks_tsv_extract(self._h, _lib.ptr(text), len(text), len(columns), cols, kinds, _lib.ptr(out), cap, 0), "ks_tsv_extract")
+        return [out[i, :rows].copy() for i in range(len(columns))]
+
     def count_batches(self, start1, start2):
         """[n_alone, n_pairs] of scheduler/postprocess.py:17-41 (the caller slices file 1 to its last 200,000 rows)."""
         s1 = np.ascontiguousarray(start1, dtype=np.uint64)

@@ -5,8 +5,8 @@
 The reference reads two agent timing logs (scheduler/postprocess.py:12-13; the first cut to its last 200,000
 rows), prints their lengths (:15), then for every distinct ``start_ns`` prints a running index (:20, :32) and
 counts whether one or two launches share that timestamp, and finally prints ``[n_alone, n_pairs]`` (:41).
-Here the two ``start_ns`` columns go to the GPU (``ks_count_batches``: two radix sorts and one intersection
-kernel); a duplicate timestamp inside a file raises AssertionError exactly where the reference's ``assert``
+Here the two files are parsed on the GPU (``ks_tsv_extract``: line splitting and the ``start_ns`` column) and the two
+columns stay there for the count (``ks_count_batches``: two radix sorts and one intersection kernel); a duplicate timestamp inside a file raises AssertionError exactly where the reference's ``assert``
 would (:24, :36).  ``--no-progress`` drops the index lines, which only exist to show the quadratic loop is alive.
 """
 from __future__ import annotations
@@ -14,7 +14,6 @@ from __future__ import annotations
 import sys
 
 import numpy as np
-import pandas as pd
 
 from . import _lib
 from .pair_table import PairTableBuilder
@@ -42,13 +41,20 @@ def main(argv=None) -> int:
     if len(files) != 2:
         print(__doc__, file=sys.stderr)
         return 2
-    df1 = pd.read_csv(files[0], sep="\t")[-200000:]
-    df2 = pd.read_csv(files[1], sep="\t")
-    print(len(df1), len(df2))
-    result = count_batches(df1["start_ns"].to_numpy(), df2["start_ns"].to_numpy())
+    with PairTableBuilder() as b:
+        # the start_ns column of both files (found by its name in the header line, as pandas does), parsed on the device
+        cols = []
+        for f in files:
+            text = np.fromfile(f, dtype=np.uint8)
+            header = bytes(text[: 4096]).split(b"\n", 1)[0].rstrip(b"\r").split(b"\t")
+            cols.append(b.tsv_extract(text, [(header.index(b"start_ns"), _lib.COL_U64)])[0])
+        s1, s2 = cols
+        s1 = s1[-200000:]
+        print(len(s1), len(s2))
+        result = count_batches(s1, s2, b)
     if progress:
         out = sys.stdout
-        for n in (df1["start_ns"].nunique(), df2["start_ns"].nunique()):
+        for n in (len(np.unique(s1)), len(np.unique(s2))):
             out.write("".join(f"{i}\n" for i in range(n)))
     print(result)
     return 0

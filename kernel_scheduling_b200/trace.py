@@ -173,10 +173,12 @@ def _key_tables(spec: TraceSpec):
     return tables
 
 
-def generate_fast(spec: TraceSpec, window: int = 0, out: np.ndarray | None = None, threads: int = 0) -> np.ndarray:
+def generate_fast(spec: TraceSpec, window: int = 0, out: np.ndarray | None = None, threads: int = 0, interleave_solo: bool = False) -> np.ndarray:
     """The same workload model as ``generate`` from the library's multi-threaded host generator (``ks_synth_trace``):
     traces of 10^8 launches in seconds.  The launches differ from ``generate``'s (another random stream); the key tables
-    are the same.  ``out``: a record buffer to fill (e.g. pinned memory), else a new array.  -> records, ordered by start_ns.
+    are the same.  ``out``: a record buffer to fill (e.g. pinned memory), else a new array.  ``interleave_solo``: the solo
+    launches take their turn on their tenant's timeline (the online configuration) instead of a phase of their own in front.
+    -> records, ordered by start_ns.
     """
     from . import _lib
 
@@ -199,7 +201,7 @@ def generate_fast(spec: TraceSpec, window: int = 0, out: np.ndarray | None = Non
     assert out.dtype == RECORD_DTYPE and len(out) >= spec.n_records and out.flags["C_CONTIGUOUS"]
     seed = (int(spec.seed) << 20) ^ (7919 + int(window))
     r = lib.ks_synth_trace(arr, len(spec.tenants), spec.solo_fraction, spec.launch_jitter_sigma, spec.corun_slowdown, seed, spec.t0_ns,
-                           out.ctypes.data, len(out), threads)
+                           out.ctypes.data, len(out), threads, 1 if interleave_solo else 0)
     if r < 0:
         raise _lib.KsError(int(-r), "ks_synth_trace")
     return out[: int(r)]

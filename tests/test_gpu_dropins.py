@@ -95,6 +95,23 @@ def test_device_tsv_parse_equals_pandas_ingest(builder, tmp_path):
     assert len(M.records_from_log(ing_b, builder, raw.split(b"\n")[0] + b"\n", False)) == 0
 
 
+def test_device_tsv_parse_numbers_models_over_the_kept_rows_only(builder, tmp_path):
+    """A file with two models whose second model first shows up on a row that is DROPPED (no end_ns): the tenants must be
+    numbered over the rows that are kept, as the pandas route numbers them -- which launch is side a depends on it."""
+    rec, frames = synthetic_timing_frames(3000)
+    a, b = frames[("qwen", False)].copy(), frames[("whisper", False)].copy()
+    both = pd.concat([b.iloc[:1], a, b.iloc[1:]]).reset_index(drop=True)  # row 0: the other model ...
+    both["end_ns"] = both["end_ns"].astype(float)
+    both.loc[0, "end_ns"] = np.nan                                        # ... on a row without a completion time
+    p = str(tmp_path / "two_models.tsv")
+    both.to_csv(p, sep="\t", index=False)
+    ing_a, ing_b = M.TraceIngest(), M.TraceIngest()
+    want = ing_a.records(pd.read_csv(p, sep="\t"), False)
+    got = M.records_from_log(ing_b, builder, p, False)
+    assert ing_a.models == ing_b.models and ing_a.models[0] == "qwen"
+    assert len(got) == len(want) == len(both) - 1 and got.tobytes() == want.tobytes()
+
+
 def _one_run_with_pairprof_log(n, tmp_path):
     """One profiling run as the reference leaves it on disk: an agent log per process holding ALL its launches (solo and
     gang, numbered by kernel_id) and the daemon's log that says which was which (pairprof_daemon.cpp:266, :317-318)."""
