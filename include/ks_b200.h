@@ -129,6 +129,10 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
  * otherwise); flags: KS_ON_DEVICE, KS_KEY_TYPE.  info: ms_join = the windows (join + partition), ms_reduce = the key ranges. */
 int64_t ks_build_table_streamed(ks_handle* h, const void* records, uint64_t n, uint32_t flags, uint64_t window_records, uint32_t n_parts,
                                 ks_table_info* info);
+/* Runs one sort pass in which a tile waits for a predecessor that was never started, with a wait limit of a few thousand
+ * polls: the wait must run out, the kernel must end and the call must return -KS_ERR_WAIT (0 would mean the bound is gone).
+ * The handle stays usable.  A check of the library's hang protection; no counterpart in the reference. */
+int64_t ks_selftest_bounded_wait(ks_handle* h);
 int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows, uint32_t flags);
 int64_t ks_copy_key_rows(ks_handle* h, ks_key_row* dst, uint64_t capacity_rows, uint32_t flags);
 

@@ -64,6 +64,7 @@ KS_API = [
     ("ks_pinned_free", [c_void_p], None),
     ("ks_build_table", [c_void_p, c_void_p, c_uint64, c_uint32, POINTER(KsTableInfo)], c_int64),
     ("ks_build_table_streamed", [c_void_p, c_void_p, c_uint64, c_uint32, c_uint64, c_uint32, POINTER(KsTableInfo)], c_int64),
+    ("ks_selftest_bounded_wait", [c_void_p], c_int64),
     ("ks_copy_pair_rows", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_copy_key_rows", [c_void_p, c_void_p, c_uint64, c_uint32], c_int64),
     ("ks_hash_keys", [c_void_p, c_void_p, c_uint64, c_uint32, c_void_p], c_int64),

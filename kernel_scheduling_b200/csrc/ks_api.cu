@@ -873,6 +873,48 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
   return (int64_t)h->n_pair_rows;
 }
 
+// A sort pass whose first tile is never started (the ticket counter begins at 1): the second tile's look-back finds no
+// word of tile 0, runs out of polls, sets the error bit and the kernel ends.  What the host then reports is returned.
+int64_t ks_selftest_bounded_wait(ks_handle* h) {
+  if (!h) return -KS_ERR_ARG;
+  KS_CUDA(h, cudaSetDevice(h->device));
+  constexpr int ITEMS = 8;
+  constexpr int THREADS = kSort16Threads;
+  const uint64_t n = 2 * (uint64_t)THREADS * ITEMS;
+  { int r = reset_run(h); if (r) return r; }
+  { int r = ensure_samples(h, std::max<uint64_t>(n, sample_capacity(h))); if (r) return r; }
+  const size_t lb_bytes = ((size_t)2 * kSort16Bins + 64) * sizeof(uint32_t);
+  KS_ENSURE(h, h->lookback, lb_bytes);
+  KS_ENSURE(h, h->hist, 2 * 4 * kSort16Bins * sizeof(uint32_t));
+  KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->hist.p, 0, 2 * 4 * kSort16Bins * sizeof(uint32_t), h->stream));
+  KS_CUDA(h, cudaMemsetAsync(h->samples[0].p, 0, n * 16, h->stream));
+  SortPass16Args a{};
+  a.in = as<uint4>(h->samples[0]);
+  a.out = as<uint4>(h->samples[1]);
+  a.n = (uint32_t)n;
+  a.bits = 8;
+  a.gbase = as<uint32_t>(h->hist);
+  a.lookback = as<uint32_t>(h->lookback);
+  a.ticket = as<uint32_t>(h->lookback) + (size_t)2 * kSort16Bins;
+  a.err = &h->d_ctl->err;
+  a.spin_limit = 1u << 12;
+  const uint32_t one = 1;
+  KS_CUDA(h, cudaMemcpyAsync(a.ticket, &one, 4, cudaMemcpyHostToDevice, h->stream));  // tile 0 is handed to nobody
+  constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
+  if (!h->attr_sort16) {
+    KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    h->attr_sort16 = true;
+  }
+  k_onesweep_pass16<ITEMS, THREADS><<<1, THREADS, smem, h->stream>>>(a);
+  ++h->launches;
+  KS_CUDA(h, cudaGetLastError());
+  { int r = read_ctl(h); if (r) return r; }
+  const int st = status_of_err(h->h_ctl->err, true);
+  if (st) return fail(h, st, std::string("ks_selftest_bounded_wait: ") + ks_status_string(st));
+  return 0;
+}
+
 int64_t ks_copy_pair_rows(ks_handle* h, ks_pair_row* dst, uint64_t capacity_rows, uint32_t flags) {
   if (!h || (!dst && h->n_pair_rows)) return -KS_ERR_ARG;
   if (capacity_rows < h->n_pair_rows) return fail(h, KS_ERR_CAPACITY, "ks_copy_pair_rows: buffer too small");

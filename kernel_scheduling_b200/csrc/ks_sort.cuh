@@ -292,6 +292,7 @@ struct SortPass16Args {
   const uint32_t* nk_dev;
   int pass, passes;
   int unstable;            // 1: equal digits may change their order inside a tile (the first pass of a sort)
+  uint32_t spin_limit;     // polls before a look-back gives up; 0 = kSpinLimit
   const uint32_t* gbase;   // [kSort16Bins]
   uint32_t* lookback;      // [tiles][kSort16Bins], zeroed before the pass
   uint32_t* ticket;
@@ -526,6 +527,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(con
       open = false;
 #endif
       uint32_t spins = 0;
+      const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
       while (open) {
         uint32_t v[SLOTS][4];
 #pragma unroll
@@ -555,7 +557,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(con
           open = open || left[q] != 0;
         }
         if (open && !progress) {
-          if (++spins > kSpinLimit) { atomicOr(a.err, kErrWait); break; }
+          if (++spins > spin_limit) { atomicOr(a.err, kErrWait); break; }
           __nanosleep(20);
         }
       }

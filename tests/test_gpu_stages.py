@@ -158,3 +158,17 @@ def test_unaligned_device_records_are_refused_before_any_launch(builder):
     # the handle is as usable as before
     keys, pairs = builder.build(rec, time_ordered=True)
     assert len(keys) > 0
+
+
+def test_a_wait_that_cannot_be_satisfied_runs_out_and_is_reported(builder):
+    """The sort's look-back waits for earlier tiles with a bounded number of polls.  A pass whose first tile is never
+    started must end by itself and come back as KS_ERR_WAIT; the handle works as before afterwards."""
+    from kernel_scheduling_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.ks_selftest_bounded_wait(builder._h) == -_lib.ERR_WAIT
+    assert b"wait" in lib.ks_last_error(builder._h)
+    rec = trace.generate(trace.config("c1", 3000))
+    keys, pairs = builder.build(rec, time_ordered=True)
+    okeys, opairs = O.build_pair_table(rec)
+    assert np.array_equal(keys["key"], okeys["key"]) and np.array_equal(pairs["count"], opairs["count"])
