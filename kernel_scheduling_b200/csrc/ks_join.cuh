@@ -74,35 +74,43 @@ __device__ __forceinline__ bool join_pair_ok(const JoinEntryT<TimeT>& ei, const 
   return !info_solo(ej.info) && ((ei.info ^ ej.info) >> 24) != 0 && ei.start < ej.start + ej.dur;
 }
 
-template <bool kIndexOutput, typename TimeT>
-__device__ __forceinline__ void join_emit(const JoinArgs& a, unsigned long long out, const JoinEntryT<TimeT>& ei, const JoinEntryT<TimeT>& ej, uint64_t gi,
-                                          uint64_t gj, uint32_t nk) {
-  if (out >= a.capacity) return;
-  const bool i_is_a = info_tenant(ei.info) < info_tenant(ej.info);
-  if constexpr (kIndexOutput) {
-    a.idx_a[out] = (uint32_t)(i_is_a ? gi : gj);
-    a.idx_b[out] = (uint32_t)(i_is_a ? gj : gi);
-  } else {
-    const uint32_t kid_i = __ldg(a.kid_of_slot + (ei.info & kMetaSlotMask)), kid_j = __ldg(a.kid_of_slot + (ej.info & kMetaSlotMask));
-    const uint32_t ka = i_is_a ? kid_i : kid_j, kb = i_is_a ? kid_j : kid_i;
-    a.samples[out] = make_uint4(nk + ka * nk + kb, i_is_a ? ei.dur : ej.dur, i_is_a ? ej.dur : ei.dur,
-                                (uint32_t)(max(ei.start + ei.dur, ej.start + ej.dur) - ei.start));
-  }
-}
+constexpr int kJoinChunk = kJoinThreads * 4;  // candidates examined per round: four consecutive ones per thread
 
 struct JoinShared {
   unsigned long long start_raw[kJoinWindow];  // TimeT view: the first sizeof(TimeT) * kJoinWindow bytes
   uint32_t dur[kJoinWindow];
   uint32_t info[kJoinWindow];
   __align__(16) uint32_t run_off[kJoinTile + 4];  // run lengths, then their exclusive scan
+  __align__(16) uint4 queue[kJoinChunk];          // the samples of one round, in the order they leave for global memory
   uint32_t warp_tot[kJoinThreads / 32];
-  uint32_t warp_tot2[kJoinThreads / 32];
   unsigned long long base_out;
   uint32_t spill;
   uint32_t wide;
 };
 
+// One sample (or one index pair, as a uint4 {a, b, 0, 0}) of the pair (i, j); gi / gj are the global positions.
+template <bool kIndexOutput, typename TimeT>
+__device__ __forceinline__ uint4 join_sample(const JoinArgs& a, const JoinEntryT<TimeT>& ei, const JoinEntryT<TimeT>& ej, uint64_t gi, uint64_t gj, uint32_t nk) {
+  const bool i_is_a = info_tenant(ei.info) < info_tenant(ej.info);
+  if constexpr (kIndexOutput) {
+    return make_uint4((uint32_t)(i_is_a ? gi : gj), (uint32_t)(i_is_a ? gj : gi), 0u, 0u);
+  } else {
+    const uint32_t kid_i = __ldg(a.kid_of_slot + (ei.info & kMetaSlotMask)), kid_j = __ldg(a.kid_of_slot + (ej.info & kMetaSlotMask));
+    const uint32_t ka = i_is_a ? kid_i : kid_j, kb = i_is_a ? kid_j : kid_i;
+    return make_uint4(nk + ka * nk + kb, i_is_a ? ei.dur : ej.dur, i_is_a ? ej.dur : ei.dur, (uint32_t)(max(ei.start + ei.dur, ej.start + ej.dur) - ei.start));
+  }
+}
+template <bool kIndexOutput>
+__device__ __forceinline__ void join_store(const JoinArgs& a, unsigned long long out, const uint4& v) {
+  if (out >= a.capacity) return;
+  if constexpr (kIndexOutput) { a.idx_a[out] = v.x; a.idx_b[out] = v.y; }
+  else a.samples[out] = v;
+}
+
 // The tile's work once the window is staged.  base = start_ns the TimeT values are relative to (0 for 64-bit).
+// Candidates are examined ONCE: in rounds of kJoinChunk consecutive candidates, four per thread, the pairs that pass go to
+// a shared-memory queue in candidate order (one block-wide scan of the threads' counts), and the queue leaves for global
+// memory as one contiguous, coalesced run behind a single update of the global sample counter.
 template <bool kIndexOutput, typename TimeT>
 __device__ __forceinline__ void join_tile(const JoinArgs& a, JoinShared& sh, uint64_t t0, uint32_t tn, uint32_t wn, unsigned long long base) {
   using Entry = JoinEntryT<TimeT>;
@@ -158,72 +166,76 @@ __device__ __forceinline__ void join_tile(const JoinArgs& a, JoinShared& sh, uin
   __syncthreads();
   const bool any_spill = sh.spill != 0;
 
-  // ---- this thread's share of the candidates: [c0, c1)
-  const uint32_t per = (total + kJoinThreads - 1) / kJoinThreads;
-  const uint32_t c0 = min(total, tid * per), c1 = min(total, c0 + per);
-  uint32_t owner0 = 0;
-  if (c0 < c1) {  // last launch whose run starts at or before candidate c0
-    uint32_t lo = 0, hi = kJoinTile;
-    while (lo + 1 < hi) {
-      const uint32_t mid = (lo + hi) >> 1;
-      if (sh.run_off[mid] <= c0) lo = mid; else hi = mid;
+  // ---- rounds over the candidates
+  for (uint32_t cb = 0; cb < total; cb += kJoinChunk) {
+    const uint32_t c0 = min(total, cb + tid * 4u), c1 = min(total, c0 + 4u);
+    uint32_t pair[4], n_valid = 0;  // li | lj << 16 of the candidates that pass
+    if (c0 < c1) {
+      uint32_t lo = 0, hi = kJoinTile;  // last launch whose run starts at or before candidate c0
+      while (lo + 1 < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (sh.run_off[mid] <= c0) lo = mid; else hi = mid;
+      }
+      uint32_t li = lo;
+      Entry ei = entry(li);
+      for (uint32_t q = c0; q < c1; ++q) {
+        while (sh.run_off[li + 1] <= q) { ++li; ei = entry(li); }
+        const uint32_t lj = li + 1 + (q - sh.run_off[li]);
+        const Entry ej = entry(lj);
+        if (join_pair_ok(ei, ej) && t0 + lj >= a.n_halo) pair[n_valid++] = li | (lj << 16);
+      }
     }
-    owner0 = lo;
+    const uint32_t vinc = warp_incl_scan(n_valid);
+    __syncthreads();  // the previous round's queue has left; warp_tot is free
+    if (lane == 31) sh.warp_tot[warp] = vinc;
+    __syncthreads();
+    uint32_t pos = vinc - n_valid, qn = 0;
+    for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
+      if (w < warp) pos += sh.warp_tot[w];
+      qn += sh.warp_tot[w];
+    }
+    if (qn == 0) continue;  // uniform
+    if (tid == 0) sh.base_out = atomicAdd(&a.ctl->n_pairs, (unsigned long long)qn);
+#pragma unroll
+    for (uint32_t v = 0; v < 4; ++v) {
+      if (v < n_valid) {
+        const uint32_t li = pair[v] & 0xFFFFu, lj = pair[v] >> 16;
+        sh.queue[pos + v] = join_sample<kIndexOutput>(a, entry(li), entry(lj), t0 + li, t0 + lj, nk);
+      }
+    }
+    __syncthreads();
+    const unsigned long long out0 = sh.base_out;
+    for (uint32_t i = tid; i < qn; i += kJoinThreads) join_store<kIndexOutput>(a, out0 + i, sh.queue[i]);
   }
 
-  uint32_t n_valid = 0, spill_before = 0;
-  unsigned long long out = 0;
-  for (int pass = 0; pass < 2; ++pass) {
-    uint32_t li = owner0;
-    Entry ei = entry(li);
-    for (uint32_t q = c0; q < c1; ++q) {
-      while (sh.run_off[li + 1] <= q) { ++li; ei = entry(li); }
-      const uint32_t lj = li + 1 + (q - sh.run_off[li]);
-      const Entry ej = entry(lj);
-      if (!join_pair_ok(ei, ej) || t0 + lj < a.n_halo) continue;
-      if (pass == 0) ++n_valid;
-      else { join_emit<kIndexOutput>(a, out, ei, ej, t0 + li, t0 + lj, nk); ++out; }
-    }
-    // runs that continue behind the window: their owner walks the rest from global memory (64-bit times)
-    uint32_t spill_cnt = 0;
-    if (any_spill) {
+  // ---- runs that continue behind the window (a launch longer than the look-ahead): their owner walks the rest from global
+  // memory (64-bit times), counts, reserves its own range of the sample stream and walks again to write
+  if (any_spill) {
 #pragma unroll 1
-      for (int k = 0; k < kJoinPerThread; ++k) {
-        const uint32_t sl = tid * kJoinPerThread + k;
-        if (!(sl < tn && sl + 1 + len4[k] == wn)) continue;  // only runs that reached the end of the window
-        JoinEntry es;
-        es.start = base + s_start[sl];
-        es.dur = sh.dur[sl];
-        es.info = sh.info[sl];
-        if (info_solo(es.info) || !es.dur) continue;
-        const unsigned long long end_s = es.start + es.dur;
+    for (int k = 0; k < kJoinPerThread; ++k) {
+      const uint32_t sl = tid * kJoinPerThread + k;
+      if (!(sl < tn && sl + 1 + len4[k] == wn)) continue;  // only runs that reached the end of the window
+      JoinEntry es;
+      es.start = base + s_start[sl];
+      es.dur = sh.dur[sl];
+      es.info = sh.info[sl];
+      if (info_solo(es.info) || !es.dur) continue;
+      const unsigned long long end_s = es.start + es.dur;
+      unsigned long long out = 0;
+      for (int pass = 0; pass < 2; ++pass) {
+        uint32_t cnt = 0;
         for (uint64_t j = t0 + wn; j < a.n; ++j) {
           const JoinEntry ej = join_entry(a, j);
           if (ej.start >= end_s) break;
           if (!join_pair_ok(es, ej) || j < a.n_halo) continue;
-          if (pass == 1) join_emit<kIndexOutput>(a, sh.base_out + spill_before + spill_cnt, es, ej, t0 + sl, j, nk);
-          ++spill_cnt;
+          if (pass == 1) join_store<kIndexOutput>(a, out + cnt, join_sample<kIndexOutput>(a, es, ej, t0 + sl, j, nk));
+          ++cnt;
+        }
+        if (pass == 0) {
+          if (!cnt) break;
+          out = atomicAdd(&a.ctl->n_pairs, (unsigned long long)cnt);
         }
       }
-    }
-    if (pass == 0) {
-      // one scan over (window pairs, spilled pairs) per thread; window pairs first, spilled pairs behind all of them
-      const uint32_t vinc = warp_incl_scan(n_valid), sinc = warp_incl_scan(spill_cnt);
-      __syncthreads();
-      if (lane == 31) { sh.warp_tot[warp] = vinc; sh.warp_tot2[warp] = sinc; }
-      __syncthreads();
-      uint32_t vbefore = vinc - n_valid, sbefore = sinc - spill_cnt, vtotal = 0, stotal = 0;
-      for (uint32_t w = 0; w < kJoinThreads / 32; ++w) {
-        if (w < warp) { vbefore += sh.warp_tot[w]; sbefore += sh.warp_tot2[w]; }
-        vtotal += sh.warp_tot[w];
-        stotal += sh.warp_tot2[w];
-      }
-      __syncthreads();
-      if (tid == 0) sh.base_out = (vtotal + stotal) ? atomicAdd(&a.ctl->n_pairs, (unsigned long long)(vtotal + stotal)) : 0ull;
-      __syncthreads();
-      if (vtotal + stotal == 0) return;
-      out = sh.base_out + vbefore;
-      spill_before = vtotal + sbefore;
     }
   }
 }
