@@ -447,7 +447,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   const int cgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>((max_rows + 255) / 256, (uint32_t)h->sm_count * 8));
   if (!h->attr_seg) {  // per device, so remembered per handle
     KS_CUDA(h, cudaFuncSetAttribute(k_seg_mid, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_mid_smem_bytes()));
-    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big<kBigMax>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes<kBigMax>()));
     h->attr_seg = true;
   }
   // Three streams.  The chain of launches of the large rows is the longest path, so it starts first and stays on the main
@@ -462,7 +462,7 @@ int run_segment_stats(ks_handle* h, const uint4* items, const uint32_t* plain, u
   k_seg_mid<<<h->sm_count * 3, kMidWarps * 32, seg_mid_smem_bytes(), h->aux[1]>>>(s);
   k_seg_small<8><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
   k_seg_small<32><<<h->sm_count * 4, 256, 0, h->aux[0]>>>(s);
-  k_seg_big<<<h->sm_count * 2, 256, seg_big_smem_bytes(), h->aux[0]>>>(s);
+  k_seg_big<kBigMax><<<h->sm_count * 2, 256, seg_big_smem_bytes<kBigMax>(), h->aux[0]>>>(s);
   KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
   KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
   const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 4));
@@ -498,13 +498,15 @@ int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t ma
   const uint32_t max_deferred = (uint32_t)(n / kTsRowMax) + max_tiles + 2;  // rows above kTsRowMax, and one row per tile that may leave its window
   KS_ENSURE(h, h->small_rows, (size_t)max_deferred * 4);
   KS_ENSURE(h, h->cta_rows, (size_t)max_deferred * 4);
+  KS_ENSURE(h, h->big_rows, (size_t)max_deferred * 4);
   KS_ENSURE(h, h->large_rows, (size_t)max_large * sizeof(LargeRow));
   KS_ENSURE(h, h->chunk_row, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->chunk_idx, (size_t)max_chunks * 4);
   KS_ENSURE(h, h->large_hist, (size_t)max_large * 2 * kLanes * 256 * 4);
   if (!h->attr_tile) {  // per device, so remembered per handle
     KS_CUDA(h, cudaFuncSetAttribute(k_tile_stats, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_stats_smem_bytes()));
-    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big<kBigMax>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes<kBigMax>()));
+    KS_CUDA(h, cudaFuncSetAttribute(k_seg_big<kBigSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)seg_big_smem_bytes<kBigSmall>()));
     h->attr_tile = true;
   }
   KS_CUDA(h, cudaMemsetAsync(h->tile_cnt.p, 0, state_bytes, h->stream));
@@ -534,6 +536,7 @@ int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t ma
   s.max_rows = max_rows;
   s.stats = as<RowStats>(h->stats);
   s.big_rows = as<uint32_t>(h->cta_rows);
+  s.mid_rows = as<uint32_t>(h->big_rows);  // rows of up to kBigSmall samples: the CTA-per-row kernel with the small staging area
   s.large = as<LargeRow>(h->large_rows);
   s.chunk_row = as<uint32_t>(h->chunk_row);
   s.chunk_idx = as<uint32_t>(h->chunk_idx);
@@ -548,8 +551,11 @@ int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t ma
   // the CTA-per-row kernel beside the chain of the largest rows
   KS_CUDA(h, cudaEventRecord(h->fork_ev, h->stream));
   KS_CUDA(h, cudaStreamWaitEvent(h->aux[0], h->fork_ev, 0));
-  k_seg_big<<<h->sm_count * 2, 256, seg_big_smem_bytes(), h->aux[0]>>>(s);
+  k_seg_big<kBigSmall><<<h->sm_count * 6, 256, seg_big_smem_bytes<kBigSmall>(), h->aux[0]>>>(s);
   KS_CUDA(h, cudaEventRecord(h->join_ev[0], h->aux[0]));
+  KS_CUDA(h, cudaStreamWaitEvent(h->aux[1], h->fork_ev, 0));
+  k_seg_big<kBigMax><<<h->sm_count * 2, 256, seg_big_smem_bytes<kBigMax>(), h->aux[1]>>>(s);
+  KS_CUDA(h, cudaEventRecord(h->join_ev[1], h->aux[1]));
   const int lgrid = (int)std::max<uint32_t>(1, std::min<uint32_t>(max_chunks, (uint32_t)h->sm_count * 4));
   k_segL_reduce<<<lgrid, 256, 0, h->stream>>>(s);
   k_segL_init<<<(max_large * 2 * kLanes + 255) / 256, 256, 0, h->stream>>>(s);
@@ -560,7 +566,8 @@ int run_rows_and_stats(ks_handle* h, const uint4* items, uint64_t n, uint32_t ma
   }
   k_segL_final<<<(max_large + 255) / 256, 256, 0, h->stream>>>(s);
   KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[0], 0));
-  h->launches += 6 + 2 * kLargeRounds;
+  KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->join_ev[1], 0));
+  h->launches += 7 + 2 * kLargeRounds;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }

@@ -390,19 +390,26 @@ __global__ void __launch_bounds__(kMidWarps * 32, 3) k_seg_mid(const SegArgs a) 
 // One CTA per row of kMidMax+1 .. kBigMax samples: the same scheme with block-wide reductions and histograms and the
 // row's three value lanes staged in the CTA's shared memory (96 KB).  The selection state (prefix, rank, highest open
 // bit per lane) is computed redundantly by every thread from shared results, so it stays in registers.
-constexpr size_t seg_big_smem_bytes() { return (size_t)kLanes * kBigMax * sizeof(uint32_t); }
+// Two instances: rows up to kBigSmall samples (24 KB of shared memory per CTA, so many CTAs per SM hide each other's
+// barriers and loads) and rows up to kBigMax (96 KB).  CAP = the row capacity of the instance; its rows come from its own list.
+constexpr uint32_t kBigSmall = 2048;
+template <uint32_t CAP>
+constexpr size_t seg_big_smem_bytes() { return (size_t)kLanes * CAP * sizeof(uint32_t); }
 
-__global__ void __launch_bounds__(256, 2) k_seg_big(const SegArgs a) {
-  extern __shared__ __align__(16) uint32_t big_vals[];  // [kLanes][kBigMax]
+template <uint32_t CAP>
+__global__ void __launch_bounds__(256, CAP <= kBigSmall ? 6 : 2) k_seg_big(const SegArgs a) {
+  constexpr uint32_t kBigMax = CAP;  // within this kernel: the capacity of the staging area
+  extern __shared__ __align__(16) uint32_t big_vals[];  // [kLanes][CAP]
   __shared__ uint32_t hist[kLanes][256];
   __shared__ unsigned long long sh_sum[8][kLanes];
   __shared__ uint32_t sh_a[8][kLanes], sh_b[8][kLanes];
   __shared__ uint32_t sh_pick[kLanes][2];
   const uint32_t tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
-  const uint32_t n_big = min(*big_row_counter(a.ctl), a.max_rows);
+  const uint32_t* list = CAP <= kBigSmall ? a.mid_rows : a.big_rows;
+  const uint32_t n_big = min(big_row_counter(a.ctl)[CAP <= kBigSmall ? 1 : 0], a.max_rows);
   const int nl = a.n_lanes;
   for (uint32_t t = blockIdx.x; t < n_big; t += gridDim.x) {
-    const uint32_t row = a.big_rows[t];
+    const uint32_t row = list[t];
     const uint32_t s = a.row_start[row], cnt = min(a.row_start[row + 1] - s, kBigMax);
     unsigned long long sum[kLanes] = {0, 0, 0};
     uint32_t mn[kLanes] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, mx[kLanes] = {0, 0, 0};

@@ -411,7 +411,9 @@ __global__ void __launch_bounds__(256) k_seg_deferred(const DeferredArgs a) {
     const uint32_t row = a.deferred[t];
     if (row >= n_rows) continue;
     const uint32_t st = a.row_start[row], cnt = a.row_start[row + 1] - st;
-    if (cnt <= kBigMax) {
+    if (cnt <= kBigSmall) {
+      s.mid_rows[atomicAdd(big_row_counter(s.ctl) + 1, 1u)] = row;  // the CTA-per-row kernel with the small staging area
+    } else if (cnt <= kBigMax) {
       s.big_rows[atomicAdd(big_row_counter(s.ctl), 1u)] = row;
     } else {
       const uint32_t nch = (cnt + kLargeChunk - 1) / kLargeChunk;
