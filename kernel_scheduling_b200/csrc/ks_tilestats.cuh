@@ -28,9 +28,9 @@ namespace ks {
 constexpr int kTsThreads = 256;
 constexpr int kTsWarps = kTsThreads / 32;
 constexpr int kTsTile = 2048;
-constexpr int kTsOver = 256;
+constexpr int kTsOver = 512;
 constexpr int kTsWin = kTsTile + kTsOver;
-constexpr uint32_t kTsRowMax = 256;  // largest row finished inside a tile
+constexpr uint32_t kTsRowMax = 512;  // largest row finished inside a tile
 constexpr int kTsDigitBits = 6;
 constexpr int kTsBins = 1 << kTsDigitBits;
 
