@@ -147,7 +147,6 @@ int ensure(ks_handle* h, DevBuf& b, size_t bytes) {
 template <typename T>
 T* as(const DevBuf& b) { return reinterpret_cast<T*>(b.p); }
 
-constexpr int kSort16Threads = 512;  // threads per CTA of the sample sort: tiles of 4096 items, runs of 8 items per digit
 
 int bit_length(uint64_t v) {
   int b = 0;
@@ -221,7 +220,7 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 // holds the result.  nk_dev: the key count in device memory -- the passes then split the bits of ITS largest sort key
 // among them (end_bit only fixes the number of passes; kernels read the count when they run).
 int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr, const uint32_t* nk_dev = nullptr) {
-  constexpr int ITEMS = 8;
+  constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   if (n >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "radix sort of 2^30 items or more");
@@ -247,7 +246,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
     h->attr_sort16 = true;
   }
   int cur = 0;
-  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * (1024 / THREADS));
+  const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)h->sm_count * kSort16CtasPerSm);
   for (int p = 0; p < passes; ++p) {
     KS_CUDA(h, cudaMemsetAsync(h->lookback.p, 0, lb_bytes, h->stream));
     if (p == 0 && h->ev_sort[0]) cudaEventRecord(h->ev_sort[0], h->stream);
@@ -885,7 +884,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
 int64_t ks_selftest_bounded_wait(ks_handle* h) {
   if (!h) return -KS_ERR_ARG;
   KS_CUDA(h, cudaSetDevice(h->device));
-  constexpr int ITEMS = 8;
+  constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   const uint64_t n = 2 * (uint64_t)THREADS * ITEMS;
   { int r = reset_run(h); if (r) return r; }
@@ -1458,7 +1457,7 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
   KS_CUDA(h, cudaSetDevice(h->device));
   const uint64_t n = h->mg_n_samples;
   if (n > capacity) return fail(h, KS_ERR_CAPACITY, "ks_mg_partition: send buffer too small");
-  constexpr int ITEMS = 8;
+  constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
@@ -1489,7 +1488,7 @@ int64_t ks_mg_partition(ks_handle* h, const uint32_t* splitters, uint32_t shift,
     KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_dest_hist<<<h->sm_count * 2, 256, 0, h->stream>>>(a, hist);
     k_radix_scan_hist<<<1, 256, 0, h->stream>>>(hist, gbase, 1);
-    k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * (1024 / THREADS)), THREADS, smem, h->stream>>>(a);
+    k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * kSort16CtasPerSm), THREADS, smem, h->stream>>>(a);
     h->launches += 3;
     if (counts) {
       uint32_t hc[16];

@@ -245,7 +245,7 @@ int mg_any_error(ks_handle* h, size_t width, const char* where) {
 int mg_partition_to_peers(ks_handle* h, const uint32_t* splitters, uint32_t shift, uint32_t n_ranks, uint4* const* dest) {
   const uint64_t n = h->mg_n_samples;
   if (!n) return 0;
-  constexpr int ITEMS = 8;
+  constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
@@ -269,7 +269,7 @@ int mg_partition_to_peers(ks_handle* h, const uint32_t* splitters, uint32_t shif
   a.err = &h->d_ctl->err;
   constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
   KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * (1024 / THREADS)), THREADS, smem, h->stream>>>(a);
+  k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * kSort16CtasPerSm), THREADS, smem, h->stream>>>(a);
   ++h->launches;
   KS_CUDA(h, cudaGetLastError());
   return 0;

@@ -258,7 +258,13 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
 // three passes, not four); the look-back reads four earlier tiles per round trip.
 constexpr int kSort16MaxBits = 9;
 constexpr int kSort16Bins = 1 << kSort16MaxBits;  // look-back words per tile, counters per pass
-constexpr int kLbLanes = 8;                       // lanes that look back together for one digit
+#ifndef KS_SORT16_ITEMS
+#define KS_SORT16_ITEMS 8
+#define KS_SORT16_CTAS 2
+#endif
+constexpr int kSort16Threads = 512;               // threads per CTA of the sample sort
+constexpr int kSort16Items = KS_SORT16_ITEMS;     // items per thread: tiles of kSort16Threads x kSort16Items samples
+constexpr int kSort16CtasPerSm = KS_SORT16_CTAS;
 
 // Digits of a sort over end_bit key bits in `passes` passes: as equal as possible, the wider ones first.
 __host__ __device__ __forceinline__ void digit_layout(int end_bit, int passes, int pass, int* shift, int* bits) {
@@ -392,7 +398,7 @@ __global__ void __launch_bounds__(kSort16Bins) k_radix_scan_hist16(const uint32_
 }
 
 template <int ITEMS, int THREADS>
-__global__ void __launch_bounds__(THREADS, 1024 / THREADS) k_onesweep_pass16(const SortPass16Args a) {
+__global__ void __launch_bounds__(THREADS, kSort16CtasPerSm) k_onesweep_pass16(const SortPass16Args a) {
   constexpr int TILE = THREADS * ITEMS;
   constexpr int WARPS = THREADS / 32;
   constexpr int SLOTS = (kSort16Bins + THREADS - 1) / THREADS;  // digits per thread

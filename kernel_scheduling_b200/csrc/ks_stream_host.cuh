@@ -48,7 +48,7 @@ struct StreamParts {
 // n samples at `in` go to their parts' stores
 int stream_partition(ks_handle* h, StreamParts& P, const uint4* in, uint64_t n) {
   if (!n) return 0;
-  constexpr int ITEMS = 8;
+  constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
   const uint32_t ntiles = (uint32_t)((n + TILE - 1) / TILE);
@@ -106,7 +106,7 @@ int stream_partition(ks_handle* h, StreamParts& P, const uint4* in, uint64_t n) 
     KS_CUDA(h, cudaFuncSetAttribute(k_onesweep_pass16<ITEMS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     h->attr_sort16 = true;
   }
-  k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * (1024 / THREADS)), THREADS, smem, h->stream>>>(a);
+  k_onesweep_pass16<ITEMS, THREADS><<<(int)std::min<uint32_t>(ntiles, (uint32_t)h->sm_count * kSort16CtasPerSm), THREADS, smem, h->stream>>>(a);
   h->launches += 2;
   KS_CUDA(h, cudaGetLastError());
   return 0;
