@@ -510,16 +510,19 @@ def main():
 def roofline(per_stage, info, N, S, P, T, ms_per_step, peak, peak_src):
     """The roofline block of the JSON line: the kernel with the largest share of the step, its algorithmic bytes per launch
     over its measured launch time (CUDA events inside the library, on its stream), and the whole path."""
-    # algorithmic bytes per launch and the ncu DRAM traffic per unit (profiles/): decode reads 48 B and writes 16 B per
-    # record; the join reads the 16-byte timeline entry of every record and writes a 16-byte sample per pair; one pass of
-    # the sample sort reads and writes every 16-byte sample once
+    # algorithmic bytes per launch: decode reads 48 B and writes 16 B per record; the join reads the 16-byte timeline entry
+    # of every record and writes a 16-byte sample per pair; one pass of the sample sort reads and writes every 16-byte
+    # sample once.  traffic: dram__bytes_read + dram__bytes_write of one ncu capture of the same kernels at 20 M records of
+    # c3 (41 M samples: larger than L2, small on the device), per unit, scaled to this run's units -- each of these kernels
+    # streams its input once, so its traffic grows in proportion: 63.7 B per record (decode), 16.0 B per record + 14.8 B per
+    # pair (join), 31.9 B per sample (a sort pass).
     passes = max(1, int(info.get("sort_passes", 0)) or 1)
     cand = {
-        "k_decode_hash": (per_stage["ms_decode"], 64.0 * N, 59.3 * N),
-        "k_join": (per_stage["ms_join"], 16.0 * N + 16.0 * P, None),
+        "k_decode_hash": (per_stage["ms_decode"], 64.0 * N, 63.7 * N),
+        "k_join": (per_stage["ms_join"], 16.0 * N + 16.0 * P, 16.0 * N + 14.8 * P),
     }
     if info.get("ms_sort_pass", 0.0) > 0.0:
-        cand["k_onesweep_pass16"] = (info["ms_sort_pass"], 32.0 * (S + P), None)
+        cand["k_onesweep_pass16"] = (info["ms_sort_pass"], 32.0 * (S + P), 31.9 * (S + P))
     dom = max(cand, key=lambda k: cand[k][0] * (passes if k == "k_onesweep_pass16" else 1))
     ms, alg, traffic = cand[dom]
     achieved = alg / (ms * 1e-3) / 1e9 if ms > 0 else 0.0

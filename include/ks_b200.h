@@ -98,7 +98,7 @@ typedef struct ks_table_info {
   uint32_t sort_passes;      /* passes of the sample sort (one launch of the pass kernel each) */
   /* device time of the stages of the last call, CUDA events on the handle's stream */
   float ms_stage_in, ms_decode, ms_order, ms_dict, ms_join, ms_sort, ms_reduce, ms_finalize, ms_total;
-  float ms_sort_pass;        /* device time of the first pass of the sample sort alone */
+  float ms_sort_pass;        /* average device time of one pass of the sample sort (one launch of the pass kernel) */
 } ks_table_info;
 
 typedef struct ks_handle ks_handle;

@@ -102,7 +102,7 @@ struct ks_handle {
   bool hint_valid = false;
   uint64_t hint_samples = 0, hint_nk = 0, hint_rows = 0;
   cudaEvent_t ev[12]{};
-  cudaEvent_t ev_sort[2]{};  // around the first pass of the last sample sort
+  cudaEvent_t ev_sort[2]{};  // around the passes of the last sample sort
   int sort_passes = 0;
   // the three size classes of K4 are independent of one another: they run side by side on two helper streams
   cudaStream_t aux[2]{};
@@ -265,7 +265,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
     a.ticket = as<uint32_t>(h->lookback) + (size_t)ntiles * kSort16Bins;
     a.err = &h->d_ctl->err;
     k_onesweep_pass16<ITEMS, THREADS><<<grid, THREADS, smem, h->stream>>>(a);
-    if (p == 0 && h->ev_sort[1]) cudaEventRecord(h->ev_sort[1], h->stream);
+    if (p == passes - 1 && h->ev_sort[1]) cudaEventRecord(h->ev_sort[1], h->stream);
     cur ^= 1;
   }
   KS_CUDA(h, cudaGetLastError());
@@ -874,7 +874,7 @@ int64_t ks_build_table(ks_handle* h, const void* records, uint64_t n, uint32_t f
     info->ms_finalize = ev_ms(ev[8], ev[9]);
     info->ms_total = ev_ms(ev[0], ev[9]);
     info->sort_passes = (uint32_t)h->sort_passes;
-    info->ms_sort_pass = h->sort_passes > 0 && n_samples ? ev_ms(h->ev_sort[0], h->ev_sort[1]) : 0.f;
+    info->ms_sort_pass = h->sort_passes > 0 && n_samples ? ev_ms(h->ev_sort[0], h->ev_sort[1]) / (float)h->sort_passes : 0.f;
   }
   return (int64_t)h->n_pair_rows;
 }
