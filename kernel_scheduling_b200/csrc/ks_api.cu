@@ -57,6 +57,10 @@ struct ks_handle {
   DevBuf large_rows, chunk_row, chunk_idx, large_hist, small_rows, small8_rows, cta_rows;
   DevBuf tmp[6];
   DevBuf stream_store;  // ks_build_table_streamed: the samples of all windows, one region per key range
+  // ks_mg_build in stages: the copy engines carry the table rows of a stage to the peers on this stream while the next
+  // stage is sorted and reduced on the handle's stream
+  cudaStream_t mg_side[1]{};
+  cudaEvent_t mg_side_ev[2]{};   // [0]: the rows are written; [1]: the copies are done
   DevBuf tsv_text, tsv_lines, tsv_parsed, tsv_valid, tsv_cnt, tsv_vcnt, tsv_dict, tsv_maps;
   DevBuf tsv_kid, tsv_rowsolo, tsv_label, tsv_logtext, tsv_loglines, tsv_logcnt;
   uint64_t tsv_n_lines = 0, tsv_n_valid = 0, tsv_n_bytes = 0, tsv_max_kid = 0;
@@ -78,6 +82,7 @@ struct ks_handle {
   // multi-GPU session state (ks_mg_*)
   const unsigned char* mg_rec = nullptr;
   uint64_t mg_n_owned = 0, mg_n_halo = 0, mg_nk = 0, mg_n_samples = 0;
+  uint64_t mg_rows_hint = 0;  // rows of the last table of ks_mg_build: sizes the table before the last stage's rows are known
   uint32_t mg_flags = 0;
   int mg_cur = 0;
 
@@ -219,7 +224,9 @@ int radix_sort(ks_handle* h, KeyT* keys[2], ValT* vals[2][NV > 0 ? NV : 1], uint
 // K2 driver for the 16-byte sample stream: sorts set 0/1 of h->samples on key bits [0, end_bit); returns the set that
 // holds the result.  nk_dev: the key count in device memory -- the passes then split the bits of ITS largest sort key
 // among them (end_bit only fixes the number of passes; kernels read the count when they run).
-int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr, const uint32_t* nk_dev = nullptr) {
+// key_base: every key is at least key_base and end_bit counts the bits of key - key_base (a key range of a larger sort)
+int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = nullptr, const uint4* first_in = nullptr, const uint32_t* nk_dev = nullptr,
+                 uint32_t key_base = 0) {
   constexpr int ITEMS = kSort16Items;
   constexpr int THREADS = kSort16Threads;
   constexpr int TILE = THREADS * ITEMS;
@@ -237,7 +244,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
   const int hist_grid = (int)std::min<uint64_t>((n + 256 * 16 - 1) / (256 * 16), (uint64_t)h->sm_count * 6);
   // first_in: the unsorted items live outside the two sets (a receive buffer); the first pass reads them from there
   const uint4* src0 = first_in ? first_in : as<uint4>(h->samples[0]);
-  k_radix_hist16<<<hist_grid, 256, 0, h->stream>>>(src0, n_dev, (uint32_t)n, end_bit, passes, nk_dev, hist);
+  k_radix_hist16<<<hist_grid, 256, 0, h->stream>>>(src0, n_dev, (uint32_t)n, end_bit, passes, nk_dev, hist, key_base);
   k_radix_scan_hist16<<<1, kSort16Bins, 0, h->stream>>>(hist, gbase, passes);
   h->launches += 2 + passes;
   constexpr size_t smem = sort16_smem_bytes<ITEMS, THREADS>();
@@ -257,6 +264,7 @@ int radix_sort16(ks_handle* h, uint64_t n, int end_bit, const uint32_t* n_dev = 
     a.n = (uint32_t)n;
     digit_layout(end_bit, passes, p, &a.shift, &a.bits);
     a.nk_dev = nk_dev;
+    a.key_base = key_base;
     a.pass = p;
     a.passes = passes;
     a.unstable = p == 0;
@@ -659,6 +667,8 @@ ks_handle* ks_create(int device, void* stream, const ks_config* cfg) {
   for (auto& e : h->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
   for (auto& e : h->ev_sort) ok = ok && cudaEventCreate(&e) == cudaSuccess;
   for (auto& st : h->aux) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
+  for (auto& st : h->mg_side) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
+  for (auto& e : h->mg_side_ev) ok = ok && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&h->fork_ev, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&h->classify_ev, cudaEventDisableTiming) == cudaSuccess;
   for (auto& e : h->join_ev) ok = ok && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess;
@@ -681,6 +691,7 @@ void ks_destroy(ks_handle* h) {
   if (h->stream) cudaStreamSynchronize(h->stream);
   mg_native_release(h, false);
   auto fr = [](void* p) { if (p) cudaFree(p); };
+  for (auto& st : h->mg_side) if (st) cudaStreamSynchronize(st);
   fr(h->d_ctl); fr(h->dict_keys); fr(h->dict_words); fr(h->dict_launches); fr(h->dict_solo); fr(h->kid_of_slot);
   fr(h->dkeys); fr(h->dslot); fr(h->drank); fr(h->slot_of_kid); fr(h->row_of_kid); fr(h->keys_sorted); fr(h->solo_ns); fr(h->key_rows);
   if (h->h_ctl) cudaFreeHost(h->h_ctl);
@@ -691,6 +702,8 @@ void ks_destroy(ks_handle* h) {
   for (auto& e : h->ev) if (e) cudaEventDestroy(e);
   for (auto& e : h->ev_sort) if (e) cudaEventDestroy(e);
   for (auto& st : h->aux) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+  for (auto& st : h->mg_side) if (st) cudaStreamDestroy(st);
+  for (auto& e : h->mg_side_ev) if (e) cudaEventDestroy(e);
   if (h->fork_ev) cudaEventDestroy(h->fork_ev);
   if (h->classify_ev) cudaEventDestroy(h->classify_ev);
   for (auto& e : h->join_ev) if (e) cudaEventDestroy(e);
@@ -1255,7 +1268,8 @@ int mg_status(ks_handle* h, const char* what) {
 
 // K2 + K4 over the n samples in sample set 0 (this rank's key range), then the solo times of the keys reduced here.
 // Queues only; the caller reads the control words back.
-int mg_reduce_queue(ks_handle* h, uint64_t n, const uint4* first_in = nullptr) {
+// [key_lo, key_hi): the sort keys the samples can have (0, 0: any), so that a key range is sorted over the bits of its width
+int mg_reduce_queue(ks_handle* h, uint64_t n, const uint4* first_in = nullptr, bool solo = true, uint64_t key_lo = 0, uint64_t key_hi = 0) {
   // counters of the row / statistics kernels start from zero
   { int r = mg_zero_u32(h, &h->d_ctl->n_rows, 2); if (r) return r; }
   { int r = mg_zero_u32(h, &h->d_ctl->ticket, 2); if (r) return r; }
@@ -1264,22 +1278,24 @@ int mg_reduce_queue(ks_handle* h, uint64_t n, const uint4* first_in = nullptr) {
   KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad2[1], 0, 8, h->stream));
   KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
   const uint64_t nk = h->mg_nk;
-  const int cur = radix_sort16(h, n, bit_length(nk + nk * nk), nullptr, first_in);
+  const int cur = key_hi > key_lo ? radix_sort16(h, n, std::max(1, bit_length(key_hi - key_lo - 1)), nullptr, first_in, nullptr, (uint32_t)key_lo)
+                                  : radix_sort16(h, n, bit_length(nk + nk * nk), nullptr, first_in);
   if (cur < 0) return cur;
   h->mg_cur = cur;
   h->mg_n_samples = n;
   const uint32_t max_rows = (uint32_t)std::min<uint64_t>(n, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
   { int r = run_rows_and_stats(h, as<uint4>(h->samples[cur]), n, max_rows); if (r) return r; }
-  if (nk) {
+  if (nk && solo) {  // (a range known to hold no solo rows leaves the solo times alone: another stream may be reading them)
     k_solo_ns<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(as<RowStats>(h->stats), h->row_of_kid, (uint32_t)nk, h->solo_ns);
     ++h->launches;
   }
   return 0;
 }
 
-// key rows of every key and the pair rows of this rank's range (written to `out`, room for max_rows)
-int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows, uint32_t n_peers = 0, ks_pair_row* const* peers = nullptr) {
+// key rows of every key (keys = true) and the pair rows of this rank's range (written to `out`, room for max_rows)
+int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows, uint32_t n_peers = 0, ks_pair_row* const* peers = nullptr, bool keys = true) {
   const uint64_t nk = h->mg_nk;
+  cudaStream_t stream = h->stream;
   FinalArgs f{};
   f.stats = as<RowStats>(h->stats);
   f.row_start = as<uint32_t>(h->row_start);
@@ -1298,9 +1314,9 @@ int mg_finalize_queue(ks_handle* h, ks_pair_row* out, uint32_t max_rows, uint32_
   f.ctl = h->d_ctl;
   f.n_peer_tables = n_peers;
   for (uint32_t q = 0; q < n_peers; ++q) f.peer_rows[q] = peers[q];
-  if (nk) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(f);
-  k_finalize_pairs<<<h->sm_count * 4, 256, 0, h->stream>>>(f);
-  h->launches += nk ? 2 : 1;
+  if (nk && keys) k_finalize_keys<<<(unsigned)((nk + 255) / 256), 256, 0, stream>>>(f);
+  k_finalize_pairs<<<h->sm_count * 4, 256, 0, stream>>>(f);
+  h->launches += nk && keys ? 2 : 1;
   KS_CUDA(h, cudaGetLastError());
   return 0;
 }

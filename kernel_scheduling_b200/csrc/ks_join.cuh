@@ -9,10 +9,11 @@
 // arrays; start times are stored relative to the window's first entry in 32 bits whenever the window spans less than
 // 2^31 ns (always, for a busy trace), so the searches and comparisons are 32-bit.  Consecutive lanes take consecutive launches and
 // find where their run of candidates ends by a galloping search (most runs are empty or a few entries long).  An
-// exclusive scan of the run lengths numbers the CANDIDATES of the tile; every thread then takes an equal, contiguous
-// share of the candidates (merge-path style: one binary search for the owner of its first candidate, then a walk),
-// so a 150 us kernel that overlaps forty short ones is spread over many lanes.  Pass 0 counts the valid candidates,
-// one scan and one counter update reserve a contiguous range of the sample stream, pass 1 writes one sample per pair:
+// exclusive scan of the run lengths numbers the CANDIDATES of the tile; they are then examined ONCE, in rounds of
+// kJoinChunk consecutive candidates (merge-path style: one binary search for the owner of a thread's first candidate,
+// then a walk), so a 150 us kernel that overlaps forty short ones is spread over many lanes.  The pairs that pass go to a
+// shared-memory queue in candidate order (one block-wide scan of the threads' counts) and the queue leaves as one
+// contiguous, coalesced run of the sample stream behind a single update of the global sample counter.  One sample per pair:
 //     sort key = n_keys + kid_a * n_keys + kid_b       (a = the launch of the lower tenant)
 //     lane 0 = duration of a, lane 1 = duration of b, lane 2 = max(end) - min(start)
 // Runs that leave the staged window (a launch longer than the look-ahead) are finished by their owner from global

@@ -349,7 +349,18 @@ __global__ void __launch_bounds__(256) k_key_hist_dev(const uint4* __restrict__ 
   const uint32_t shift = key_hist_shift(ctl->n_keys);
   for (uint32_t i = threadIdx.x; i < kKeyHistBins; i += blockDim.x) sh[i] = 0;
   __syncthreads();
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&sh[min(samples[i].x >> shift, kKeyHistBins - 1)], 1u);
+  const uint32_t gstride = gridDim.x * blockDim.x;
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += 4 * gstride) {  // four loads in flight per thread
+    uint32_t k[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t i = i0 + u * gstride;
+      k[u] = i < n ? samples[i].x : 0xFFFFFFFFu;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * gstride < n) atomicAdd(&sh[min(k[u] >> shift, kKeyHistBins - 1)], 1u);
+  }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < kKeyHistBins; i += blockDim.x)
     if (sh[i]) atomicAdd(&hist[i], (unsigned long long)sh[i]);

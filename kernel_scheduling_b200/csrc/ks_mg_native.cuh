@@ -11,9 +11,12 @@
 // Every block starts with a 256-byte header that carries the sender's control words, so after exchanges 2 and 4 every
 // rank knows every rank's error bits and counts: an error on any rank makes ALL ranks return it from the same point, and
 // decisions that change what is exchanged next (a larger key block, a larger sample stream, a larger peer buffer) are
-// taken alike everywhere.  The host waits for the device twice per table (behind exchanges 2 and 4: it needs the
-// histograms for the splitters and the shard sizes for the table); everything else is queued, and what exchange 1 feeds
-// (key merge, halo) reads the other ranks' counts from the gathered headers on the device.
+// taken alike everywhere.  The host waits for the device behind exchanges 2 and 4 (it needs the histograms for the
+// splitters and the shard sizes for the table); everything else is queued, and what exchange 1 feeds (key merge, halo)
+// reads the other ranks' counts from the gathered headers on the device.
+// With peer memory and a large table the build runs in two STAGES behind exchange 3: every rank owns two key ranges, and
+// the table rows of the first are on their way into all GPUs' tables (a stream of their own) while the second range is
+// sorted and reduced; exchange 4 is then made once per stage (see the stage rule in ks_mg_build).
 //
 // NCCL is bound at run time (dlopen of libnccl.so.2, or the library named by KS_NCCL_LIBRARY): the library has no link-time
 // dependency on it, and a process that already loaded NCCL (PyTorch) shares that copy.
@@ -120,8 +123,10 @@ void mg_native_release(ks_handle* h, bool orderly) {
 }
 
 // KS_MG_TRACE=1 in the environment: rank 0 prints the device time between the driver's steps of every call to stderr
+// (KS_MG_TRACE=2: every rank)
 struct MgTrace {
   bool on = false;
+  int rank = 0;
   cudaStream_t stream = nullptr;
   std::vector<std::pair<const char*, cudaEvent_t>> marks;
   void mark(const char* name) {
@@ -134,7 +139,7 @@ struct MgTrace {
   void report() {
     if (!on) return;
     cudaStreamSynchronize(stream);
-    std::string line = "ks_mg_build trace (ms):";
+    std::string line = "ks_mg_build trace, rank " + std::to_string(rank) + " (ms):";
     for (size_t i = 1; i < marks.size(); ++i) {
       char buf[96];
       snprintf(buf, sizeof(buf), " %s=%.3f", marks[i].first, ev_ms(marks[i - 1].second, marks[i].second));
@@ -301,6 +306,7 @@ int ks_mg_comm_init(ks_handle* h, const void* id128, int rank, int world) {
   KS_NCCL(h, api->CommInitRank(&h->mg_comm, world, id, rank));
   h->mg_rank = rank;
   h->mg_world = world;
+  h->mg_rows_hint = 0;
   if (!h->mg_counts) KS_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->mg_counts), 16));
   if (!h->mg_bar) {
     KS_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->mg_bar), 16 * 17));
@@ -375,7 +381,11 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   constexpr size_t H = sizeof(MgHeader);
 
   MgTrace tr;
-  tr.on = rank == 0 && getenv("KS_MG_TRACE") != nullptr;
+  {
+    const char* e = getenv("KS_MG_TRACE");
+    tr.on = e && (rank == 0 || e[0] == '2');
+    tr.rank = rank;
+  }
   tr.stream = h->stream;
   tr.mark("start");
   cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only with KS_TIMING)
@@ -475,7 +485,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
       k_solo_samples<<<h->sm_count * 4, 256, 0, h->stream>>>(s);
       { int r = run_join(h, 0, n_tl, cap_s, nullptr, nullptr, 0, kHaloMax); if (r) return r; }
       tr.mark("samples+join");
-      k_key_hist_dev<<<h->sm_count * 2, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
+      k_key_hist_dev<<<h->sm_count * 6, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, reinterpret_cast<unsigned long long*>(blk + H));
       k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, h->mg_counts, rec, n_owned, cap_s, mg_ipc_of(h->mg_recv_x));
       h->launches += 3;
       KS_CUDA(h, cudaGetLastError());
@@ -533,59 +543,94 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     for (uint32_t b = 0; b < kKeyHistBins; ++b) total[b] += hist_of(q)[b];
   uint64_t all = 0;
   for (uint64_t v : total) all += v;
-  // rank r owns bins [edge[r], edge[r+1]): the first bin with at least r/world of the samples in front of it
-  std::vector<uint32_t> edge(world + 1, kKeyHistBins);
+  const int key_bits = bit_length(nk + nk * nk);
+  const uint32_t shift = key_bits > 12 ? (uint32_t)(key_bits - 12) : 0u;
+  // One or several STAGES.  With peer memory every rank may own up to four key ranges ("parts"): part p belongs to rank
+  // p % world and to stage p / world, and the table is the parts' rows in part order.  The rows of a stage are known (and
+  // written into this GPU's table, from where the copy engines carry them to the peers on a stream of their own) while
+  // the next stage is still being sorted and reduced, so the table's way over NVLink is hidden behind the statistics --
+  // or, where the exchange is the longer of the two, the statistics behind the exchange.  Sorting halves costs about a
+  // tenth more than sorting the whole, so stages are chosen when the last table of this session says that its exchange
+  // takes longer than that (rows x 128 bytes, (world-1)/world of them over NVLink at about 600 GB/s; sort and statistics
+  // about 64 ns per thousand samples) -- from numbers every rank has alike.  KS_MG_STAGES=1|2|4 (the same on every rank)
+  // overrides the rule.
+  int stages = 1;
+  if (p2p) {
+    const double exchange_ms = (double)h->mg_rows_hint * sizeof(ks_pair_row) * (double)(world - 1) / (double)world / 6.0e8;
+    const double reduce_ms = (double)(all / (uint64_t)world) * 6.4e-8;
+    if (exchange_ms > 0.1 * reduce_ms && exchange_ms > 0.2) stages = 2;
+    if (exchange_ms > 0.4 * reduce_ms && exchange_ms > 2.0) stages = 4;
+    if (const char* e = getenv("KS_MG_STAGES")) {
+      if (e[0] == '1') stages = 1;
+      else if (e[0] == '2') stages = 2;
+      else if (e[0] == '4') stages = 4;
+    }
+    while (stages * world > kMaxDest) stages >>= 1;
+  }
+  const int parts = stages * world;
+  // part p owns bins [edge[p], edge[p+1]): the first bin with at least p/parts of the samples in front of it
+  std::vector<uint32_t> edge(parts + 1, kKeyHistBins);
   edge[0] = 0;
   {
     uint64_t before = 0;
     uint32_t b = 0;
-    for (int r = 1; r < world; ++r) {
-      const uint64_t target = (all * (uint64_t)r + (uint64_t)world - 1) / (uint64_t)world;
+    // (equal shares for all stages: a smaller first stage, so that the copies start earlier, was measured slower -- the
+    // copy engines then fall behind and the last stage waits for them)
+    for (int p = 1; p < parts; ++p) {
+      const uint64_t target = (all * (uint64_t)p + (uint64_t)parts - 1) / (uint64_t)parts;
       while (b < kKeyHistBins && before < target) before += total[b++];
-      edge[r] = b;
+      edge[p] = b;
+    }
+    if (stages > 1 && nk) {  // every solo row in stage 0: the table rows of every stage need all solo times
+      const uint32_t solo_end = (uint32_t)std::min<uint64_t>(kKeyHistBins, ((nk - 1) >> shift) + 1);
+      for (int p = world; p < parts; ++p) edge[p] = std::max(edge[p], solo_end);
     }
   }
-  std::vector<uint64_t> send_cnt(world, 0), recv_cnt(world, 0);
-  // cnt[q][r]: samples rank q holds for rank r's key range -- one walk over every rank's histogram
-  uint64_t cnt[16][16] = {{0}};
+  // cnt[q][p]: samples rank q holds for part p -- one walk over every rank's histogram
+  uint64_t cnt[16][kMaxDest] = {{0}};
   for (int q = 0; q < world; ++q) {
     const uint64_t* hq = hist_of(q);
-    for (int r = 0; r < world; ++r) {
+    for (int p = 0; p < parts; ++p) {
       uint64_t sum = 0;
-      for (uint32_t b = edge[r]; b < edge[r + 1]; ++b) sum += hq[b];
-      cnt[q][r] = sum;
+      for (uint32_t b = edge[p]; b < edge[p + 1]; ++b) sum += hq[b];
+      cnt[q][p] = sum;
     }
   }
-  auto range_sum = [&](int q, int r) { return cnt[q][r]; };
-  uint64_t n_recv = 0;
-  for (int q = 0; q < world; ++q) {
-    send_cnt[q] = range_sum(rank, q);
-    recv_cnt[q] = range_sum(q, rank);
-    n_recv += recv_cnt[q];
+  std::vector<uint64_t> part_in(parts, 0);  // samples of part p over all ranks
+  for (int p = 0; p < parts; ++p) {
+    for (int q = 0; q < world; ++q) part_in[p] += cnt[q][p];
+    if (part_in[p] >= kSortMaxItems)  // every rank sees the same counts, so all ranks refuse together
+      return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more in the key range of rank " + std::to_string(p % world));
   }
-  for (int r = 0; r < world; ++r) {  // every rank's inbound total, so that all ranks refuse together
-    uint64_t in = 0;
-    for (int q = 0; q < world; ++q) in += range_sum(q, r);
-    if (in >= kSortMaxItems) return fail(h, KS_ERR_TOO_LARGE, "ks_mg_build: 2^30 samples or more in the key range of rank " + std::to_string(r));
-  }
-  const int key_bits = bit_length(nk + nk * nk);
-  const uint32_t shift = key_bits > 12 ? (uint32_t)(key_bits - 12) : 0u;
-  uint32_t splitters[16] = {0};
-  for (int r = 1; r < world; ++r) splitters[r - 1] = edge[r];
+  auto recv_total = [&](int d) { uint64_t v = 0; for (int s = 0; s < stages; ++s) v += part_in[s * world + d]; return v; };
+  const uint64_t n_recv = recv_total(rank);
+  uint64_t n_stage[4] = {0, 0, 0, 0}, stage_off[5] = {0, 0, 0, 0, 0};  // my parts: their samples, where they begin in my receive buffer
+  for (int s = 0; s < stages; ++s) { n_stage[s] = part_in[s * world + rank]; stage_off[s + 1] = stage_off[s] + n_stage[s]; }
+  std::vector<uint64_t> send_cnt(world, 0), recv_cnt(world, 0);  // one stage: per peer (the send/recv exchange)
+  for (int q = 0; q < world; ++q) { send_cnt[q] = cnt[rank][q]; recv_cnt[q] = cnt[q][rank]; }
+  uint32_t splitters[kMaxDest] = {0};
+  for (int p = 1; p < parts; ++p) splitters[p - 1] = edge[p];
   std::vector<uint64_t> soff(world + 1, 0), roff(world + 1, 0);
   for (int q = 0; q < world; ++q) { soff[q + 1] = soff[q] + send_cnt[q]; roff[q + 1] = roff[q] + recv_cnt[q]; }
-  if (soff[world] != n_samples_local) return fail(h, KS_ERR_COMM, "ks_mg_build: histogram and sample count disagree");
+  {
+    uint64_t mine = 0;
+    for (int p = 0; p < parts; ++p) mine += cnt[rank][p];
+    if (mine != n_samples_local) return fail(h, KS_ERR_COMM, "ks_mg_build: histogram and sample count disagree");
+  }
   const uint4* sort_input = nullptr;  // null: sample set 0
   if (p2p) {
-    // -- peer memory: the partition pass stores every item straight into its place in the destination's receive buffer
-    // where my items start in rank d's buffer: behind those of the ranks in front of me
-    uint64_t my_off_at[16] = {0};
+    // -- peer memory: the partition pass stores every item straight into its place in the destination's receive buffer:
+    // rank d's buffer holds its parts stage after stage; inside a part the senders follow in rank order
+    uint64_t my_off_at[kMaxDest] = {0};  // where my items of part p start in its owner's buffer
     bool grow = false;
     for (int d = 0; d < world; ++d) {
       uint64_t in = 0;
-      for (int q = 0; q < world; ++q) {
-        if (q == rank) my_off_at[d] = in;
-        in += range_sum(q, d);
+      for (int s = 0; s < stages; ++s) {
+        const int p = s * world + d;
+        for (int q = 0; q < world; ++q) {
+          if (q == rank) my_off_at[p] = in;
+          in += cnt[q][p];
+        }
       }
       if (in * 16 > mg_head(h, width2, d).buf_cap) grow = true;  // rank d's buffer is too small: decided alike everywhere
     }
@@ -598,8 +643,9 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
       { int r = mg_fetch_heads(h, H, H); if (r) return r; }
     }
     const size_t wh = grow ? H : width2;  // layout of the pinned header copies
-    uint4* dest[16] = {nullptr};
-    for (int d = 0; d < world; ++d) {
+    uint4* dest[kMaxDest] = {nullptr};
+    for (int p = 0; p < parts; ++p) {
+      const int d = p % world;
       unsigned char* base = nullptr;
       if (d == rank) {
         base = reinterpret_cast<unsigned char*>(h->mg_recv_x.p);
@@ -607,14 +653,15 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
         { int r = mg_import(h, h->mg_peer_recv[d], mg_head(h, wh, d)); if (r) return r; }
         base = reinterpret_cast<unsigned char*>(h->mg_peer_recv[d].p);
       }
-      dest[d] = reinterpret_cast<uint4*>(base + my_off_at[d] * 16);
+      dest[p] = reinterpret_cast<uint4*>(base + my_off_at[p] * 16);
     }
-    { int r = mg_partition_to_peers(h, splitters, shift, (uint32_t)world, dest); if (r) return r; }
+    { int r = mg_partition_to_peers(h, splitters, shift, (uint32_t)parts, dest); if (r) return r; }
     tr.mark("wait1+partition to peers");
     { int r = mg_barrier(h); if (r) return r; }
     tr.mark("barrier");
     sort_input = reinterpret_cast<const uint4*>(h->mg_recv_x.p);
-    if (sample_capacity(h) < n_recv) { int r = ensure_samples(h, n_recv); if (r) return r; }  // the sort's two sets
+    const uint64_t largest = *std::max_element(n_stage, n_stage + 4);
+    if (sample_capacity(h) < largest) { int r = ensure_samples(h, largest); if (r) return r; }  // the sort's two sets
   } else {
     // -- NCCL: partition into sample set 1, one send/recv pair per peer with exact sizes, own part by a local copy
     { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
@@ -641,102 +688,162 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     }
   }
 
-  // ---- phase 4: K2 + K4 over the received key range; solo times                                 (queued, then wait 2)
-  cudaEventRecord(ev[3], h->stream);
-  { int r = mg_reduce_queue(h, n_recv, sort_input); if (r) return r; }
-  tr.mark("sort+stats");
-  if (p2p) { int r = mg_export_ensure(h, h->mg_table_x, std::max<size_t>(h->mg_table_x.cap, (size_t)8 << 20)); if (r) return r; }
-  // block 4: [header | solo times | launches per key | solo launches per key], all by dense key id
+  // ---- phases 4 and 5, once per stage: K2 + K4 over the received part, exchange 4 (then a wait), the table rows
+  // A returning call leaves nothing running on the side stream (the next call may free or overwrite what its copies read).
+  struct SideGuard {
+    ks_handle* h;
+    bool armed = false;
+    void drain() { if (armed) for (auto& st : h->mg_side) cudaStreamSynchronize(st); armed = false; }
+    ~SideGuard() { drain(); }
+  } side{h};
+  std::vector<uint64_t> part_rows(parts, 0);  // table rows of every part, as the stages report them
+  auto row_base = [&](int p) { uint64_t v = 0; for (int i = 0; i < p; ++i) v += part_rows[i]; return v; };
+  uint64_t rows_total = 0;
   const size_t off_launches = H + (size_t)nk * 8, off_solo = off_launches + (size_t)nk * 8;
   const size_t block4 = (off_solo + (size_t)nk * 8 + 15) & ~(size_t)15;
-  {
-    unsigned char* blk = as<unsigned char>(h->mg_block);
-    k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
-    ++h->launches;
-    if (nk) {
-      KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
-      k_counts_export_dev<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, h->d_ctl, (uint32_t)nk,
-                                                                               reinterpret_cast<unsigned long long*>(blk + off_launches),
-                                                                               reinterpret_cast<unsigned long long*>(blk + off_solo));
-      ++h->launches;
-    }
-    KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, block4, kNcclUint8, h->mg_comm, h->stream));
-  }
-  tr.mark("allgather4");
-  { int r = mg_fetch_heads(h, block4, H); if (r) return r; }                                           // ---- wait 2
-  {
-    // A key range with more rows than the row arrays were sized for (and no limit asked for): every rank sees it in the
-    // gathered headers, sizes its arrays for the largest range and the whole build is made again, by all ranks alike.
-    uint64_t most_rows = 0;
-    for (int q = 0; q < world; ++q) {
-      const Control& c = mg_head(h, H, q).ctl;
-      if ((c.err & kErrTooLarge) && !(c.err & ~(kErrTooLarge | kErrUnordered))) most_rows = std::max<uint64_t>(most_rows, c.pad2[0]);
-    }
-    if (most_rows > h->cfg.max_pair_rows && most_rows < (1ull << 31) && h->rows_auto) {
-      h->cfg.max_pair_rows = (uint32_t)std::min<uint64_t>(most_rows + most_rows / 8, 0x7FFFFFFFull);
-      return ks_mg_build(h, records, n_owned, flags, info);
-    }
-  }
-  { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
-  std::vector<uint64_t> row_off(world + 1, 0);
-  for (int q = 0; q < world; ++q) {
-    const Control& c = mg_head(h, H, q).ctl;
-    row_off[q + 1] = row_off[q] + (c.n_rows > c.ticket2 ? c.n_rows - c.ticket2 : 0u);
-  }
-  const uint64_t rows_total = row_off[world], rows_mine = row_off[rank + 1] - row_off[rank];
-  *h->h_ctl = mg_head(h, H, rank).ctl;
-
-  // ---- phase 5: every key's solo time, this rank's rows straight into their place, the other ranks' rows around them
-  cudaEventRecord(ev[4], h->stream);
-  if (nk) {
-    k_solo_merge<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, H, (uint32_t)nk, h->solo_ns);
-    k_counts_sum_import<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, off_launches, off_solo, h->slot_of_kid, (uint32_t)nk,
-                                                                             h->dict_launches, h->dict_solo);
-    h->launches += 2;
-  }
-  if (p2p) {
-    // -- peer memory: the finalize kernel stores this rank's rows into every rank's copy of the table
-    const size_t table_bytes = std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row);
-    bool grow = false;
-    for (int q = 0; q < world; ++q) grow = grow || table_bytes > mg_head(h, H, q).buf_cap;
-    if (grow) {
-      if (table_bytes > h->mg_table_x.cap) { int r = mg_export_ensure(h, h->mg_table_x, table_bytes + table_bytes / 4); if (r) return r; }
+  for (int s = 0; s < stages; ++s) {
+    const bool last = s + 1 == stages;
+    if (s == 0) cudaEventRecord(ev[3], h->stream);
+    const uint4* in_s = sort_input ? sort_input + stage_off[s] : nullptr;
+    // the part's keys lie in [edge << shift, next edge << shift): sorted over the bits of that width only
+    const uint64_t key_end = nk + nk * nk + 1;
+    const uint64_t key_lo = std::min<uint64_t>((uint64_t)edge[s * world + rank] << shift, key_end);
+    const uint64_t key_hi = s * world + rank + 1 == parts ? key_end : std::min<uint64_t>((uint64_t)edge[s * world + rank + 1] << shift, key_end);
+    { int r = mg_reduce_queue(h, p2p ? n_stage[s] : n_recv, in_s, s == 0, key_lo, key_hi); if (r) return r; }
+    tr.mark("sort+stats");
+    if (p2p && s == 0) { int r = mg_export_ensure(h, h->mg_table_x, std::max<size_t>(h->mg_table_x.cap, (size_t)8 << 20)); if (r) return r; }
+    // block 4: [header | solo times | launches per key | solo launches per key], all by dense key id; later stages: the header
+    const size_t width4 = s == 0 ? block4 : H;
+    {
       unsigned char* blk = as<unsigned char>(h->mg_block);
       k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
       ++h->launches;
-      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));  // behind k_solo_merge, which read the old blocks
-      { int r = mg_fetch_heads(h, H, H); if (r) return r; }
+      if (nk && s == 0) {
+        KS_CUDA(h, cudaMemcpyAsync(blk + H, h->solo_ns, nk * 8, cudaMemcpyDeviceToDevice, h->stream));
+        k_counts_export_dev<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(h->slot_of_kid, h->dict_launches, h->dict_solo, h->d_ctl, (uint32_t)nk,
+                                                                                 reinterpret_cast<unsigned long long*>(blk + off_launches),
+                                                                                 reinterpret_cast<unsigned long long*>(blk + off_solo));
+        ++h->launches;
+      }
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, width4, kNcclUint8, h->mg_comm, h->stream));
     }
-    ks_pair_row* peers[15];
-    uint32_t n_peers = 0;
+    tr.mark("allgather4");
+    { int r = mg_fetch_heads(h, width4, H); if (r) return r; }                                         // ---- wait 2 (per stage)
+    {
+      // A key range with more rows than the row arrays were sized for (and no limit asked for): every rank sees it in the
+      // gathered headers, sizes its arrays for the largest range and the whole build is made again, by all ranks alike.
+      uint64_t most_rows = 0;
+      for (int q = 0; q < world; ++q) {
+        const Control& c = mg_head(h, H, q).ctl;
+        if ((c.err & kErrTooLarge) && !(c.err & ~(kErrTooLarge | kErrUnordered))) most_rows = std::max<uint64_t>(most_rows, c.pad2[0]);
+      }
+      if (most_rows > h->cfg.max_pair_rows && most_rows < (1ull << 31) && h->rows_auto) {
+        h->cfg.max_pair_rows = (uint32_t)std::min<uint64_t>(most_rows + most_rows / 8, 0x7FFFFFFFull);
+        side.drain();
+        return ks_mg_build(h, records, n_owned, flags, info);
+      }
+    }
+    { int r = mg_any_error(h, H, "reduce"); if (r) return r; }
     for (int q = 0; q < world; ++q) {
-      if (q == rank) continue;
-      { int r = mg_import(h, h->mg_peer_table[q], mg_head(h, H, q)); if (r) return r; }
-      peers[n_peers++] = reinterpret_cast<ks_pair_row*>(h->mg_peer_table[q].p) + row_off[rank];
+      const Control& c = mg_head(h, H, q).ctl;
+      part_rows[s * world + q] = c.n_rows > c.ticket2 ? c.n_rows - c.ticket2 : 0u;
     }
-    ks_pair_row* table = reinterpret_cast<ks_pair_row*>(h->mg_table_x.p);
-    { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine, n_peers, peers); if (r) return r; }
-    tr.mark("wait2+finalize to peers");
-    { int r = mg_barrier(h); if (r) return r; }
-    tr.mark("barrier");
-    h->pair_rows_src = table;
-  } else {
-    KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
-    ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
-    { int r = mg_finalize_queue(h, table + row_off[rank], (uint32_t)rows_mine); if (r) return r; }
-    tr.mark("wait2+finalize");
-    if (world > 1) {
-      KS_NCCL(h, api->GroupStart());
+    const int p_mine = s * world + rank;
+    const uint64_t rows_mine = part_rows[p_mine];
+    const uint64_t rows_before = row_base(s * world);  // the rows of the stages before this one
+    rows_total = row_base(parts);                      // the rows known so far; behind the last stage: the table
+    if (s == 0) *h->h_ctl = mg_head(h, H, rank).ctl;
+
+    // ---- phase 5: every key's solo time, this rank's rows straight into their place, the other ranks' rows around them
+    if (last) cudaEventRecord(ev[4], h->stream);
+    if (nk && s == 0) {
+      k_solo_merge<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, H, (uint32_t)nk, h->solo_ns);
+      k_counts_sum_import<<<(unsigned)((nk + 255) / 256), 256, 0, h->stream>>>(gathered, block4, (uint32_t)world, off_launches, off_solo, h->slot_of_kid, (uint32_t)nk,
+                                                                               h->dict_launches, h->dict_solo);
+      h->launches += 2;
+    }
+    if (p2p) {
+      // -- peer memory.  Behind the last stage the table's size is known; before, it is the last table's, or the rows seen
+      // so far scaled to all stages and a quarter
+      const uint64_t want_rows = last ? rows_total : std::max<uint64_t>(h->mg_rows_hint, rows_total * (uint64_t)stages / (uint64_t)(s + 1) * 5 / 4);
+      const size_t table_bytes = std::max<uint64_t>(want_rows, 1) * sizeof(ks_pair_row);
+      bool grow = false;
+      for (int q = 0; q < world; ++q) grow = grow || table_bytes > mg_head(h, H, q).buf_cap;
+      ks_pair_row* old_table = reinterpret_cast<ks_pair_row*>(h->mg_table_x.p);
+      if (grow) {
+        side.drain();  // the copies of the earlier stages went into the old tables: made again below
+        if (table_bytes > h->mg_table_x.cap) { int r = mg_export_ensure(h, h->mg_table_x, table_bytes + table_bytes / 4); if (r) return r; }
+        unsigned char* blk = as<unsigned char>(h->mg_block);
+        k_mg_header<<<1, 32, 0, h->stream>>>(reinterpret_cast<MgHeader*>(blk), h->d_ctl, nullptr, rec, n_owned, 0, mg_ipc_of(h->mg_table_x));
+        ++h->launches;
+        KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, H, kNcclUint8, h->mg_comm, h->stream));  // behind k_solo_merge, which read the old blocks
+        { int r = mg_fetch_heads(h, H, H); if (r) return r; }
+      }
+      ks_pair_row* peer_tab[16] = {nullptr};
       for (int q = 0; q < world; ++q) {
         if (q == rank) continue;
-        const uint64_t rows_q = row_off[q + 1] - row_off[q];
-        if (rows_mine) KS_NCCL(h, api->Send(table + row_off[rank], rows_mine * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
-        if (rows_q) KS_NCCL(h, api->Recv(table + row_off[q], rows_q * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+        { int r = mg_import(h, h->mg_peer_table[q], mg_head(h, H, q)); if (r) return r; }
+        peer_tab[q] = reinterpret_cast<ks_pair_row*>(h->mg_peer_table[q].p);
       }
-      KS_NCCL(h, api->GroupEnd());
+      ks_pair_row* table = reinterpret_cast<ks_pair_row*>(h->mg_table_x.p);
+      const uint64_t base = row_base(p_mine);
+      if (stages == 1) {
+        // one stage: the table kernel stores its rows into every table itself (one pass, nothing to overlap with)
+        ks_pair_row* peers[15];
+        uint32_t n_peers = 0;
+        for (int q = 0; q < world; ++q)
+          if (q != rank) peers[n_peers++] = peer_tab[q] + base;
+        { int r = mg_finalize_queue(h, table + base, (uint32_t)rows_mine, n_peers, peers); if (r) return r; }
+      } else {
+        // Stages: the kernel writes this GPU's table only and the copy engines carry the rows to the peers on the side
+        // stream, one peer after the other -- they take no SM, register or shared memory from the sort and statistics
+        // kernels of the next stage, which a storing kernel running beside them does (measured: the next stage a third
+        // slower).  The peers are visited in a rotated order so that no GPU is everybody's target at the same time; two or
+        // four streams side by side were measured no faster or slower than one.
+        if (grow && s > 0 && table != old_table && rows_before)  // the earlier stages' rows (all ranks') move to the new table
+          KS_CUDA(h, cudaMemcpyAsync(table, old_table, rows_before * sizeof(ks_pair_row), cudaMemcpyDeviceToDevice, h->stream));
+        { int r = mg_finalize_queue(h, table + base, (uint32_t)rows_mine, 0, nullptr, s == 0); if (r) return r; }
+        KS_CUDA(h, cudaEventRecord(h->mg_side_ev[0], h->stream));
+        KS_CUDA(h, cudaStreamWaitEvent(h->mg_side[0], h->mg_side_ev[0], 0));
+        side.armed = true;
+        for (int k = 1; k < world; ++k) {
+          const int q = (rank + k) % world;
+          if (rows_mine)
+            KS_CUDA(h, cudaMemcpyAsync(peer_tab[q] + base, table + base, rows_mine * sizeof(ks_pair_row), cudaMemcpyDeviceToDevice, h->mg_side[0]));
+        }
+        KS_CUDA(h, cudaEventRecord(h->mg_side_ev[1], h->mg_side[0]));
+        if (last) {
+          KS_CUDA(h, cudaStreamWaitEvent(h->stream, h->mg_side_ev[1], 0));
+          side.armed = false;
+        }
+      }
+      if (!last) {
+        tr.mark("wait2+rows on their way");
+      } else {
+        tr.mark("wait2+finalize to peers");
+        { int r = mg_barrier(h); if (r) return r; }
+        tr.mark("barrier");
+        h->pair_rows_src = table;
+        h->mg_rows_hint = rows_total;
+      }
+    } else {
+      KS_ENSURE(h, h->pair_rows, std::max<size_t>(rows_total, 1) * sizeof(ks_pair_row));
+      ks_pair_row* table = as<ks_pair_row>(h->pair_rows);
+      { int r = mg_finalize_queue(h, table + row_base(rank), (uint32_t)rows_mine); if (r) return r; }
+      tr.mark("wait2+finalize");
+      if (world > 1) {
+        KS_NCCL(h, api->GroupStart());
+        for (int q = 0; q < world; ++q) {
+          if (q == rank) continue;
+          const uint64_t rows_q = part_rows[q];
+          if (rows_mine) KS_NCCL(h, api->Send(table + row_base(rank), rows_mine * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+          if (rows_q) KS_NCCL(h, api->Recv(table + row_base(q), rows_q * sizeof(ks_pair_row), kNcclUint8, q, h->mg_comm, h->stream));
+        }
+        KS_NCCL(h, api->GroupEnd());
+      }
+      tr.mark("shard exchange");
+      h->pair_rows_src = table;
     }
-    tr.mark("shard exchange");
-    h->pair_rows_src = table;
   }
   tr.report();
   h->n_key_rows = nk;

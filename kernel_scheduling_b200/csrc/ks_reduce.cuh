@@ -1,7 +1,9 @@
-// ks_reduce.cuh -- K4: segmented reductions over the sorted sample stream, and the final tables.
+// ks_reduce.cuh -- K4: the rows of the sorted sample stream, and the final tables.
 //
-//  k_rows_count / k_rows_scan / k_rows_fill   find where the sort key changes: one row per run (ordered compaction)
-//  (ks_segstats.cuh)                           the integer statistics of every row
+//  k_rows_count / k_rows_scan / k_rows_fill   find where the sort key changes: one row per run (ordered compaction); the
+//                                              resident-table update uses these, the table builds find their rows inside
+//                                              the statistics kernel (ks_tilestats.cuh)
+//  (ks_tilestats.cuh, ks_segstats.cuh)         the integer statistics of every row
 //  k_finalize_keys / k_finalize_pairs          integer statistics -> the float tables (one IEEE division per value)
 //
 // Everything a row needs from its samples is an integer (durations in ns), so count, min, max and the median are

@@ -279,6 +279,8 @@ __host__ __device__ __forceinline__ int sort_key_bits(uint64_t nk) {  // bits of
   return b;
 }
 
+constexpr int kMaxDest = 32;  // destinations of a partition pass (by_dest)
+
 struct SortPass16Args {
   // by_dest != 0: the "digit" is the destination rank of the item = number of splitters <= (key >> split_shift)
   // by_dest == 2: the items of destination d go to dest[d] (this rank's place in rank d's receive buffer, peer memory for
@@ -286,7 +288,7 @@ struct SortPass16Args {
   uint32_t by_dest;
   uint32_t n_split;
   uint32_t split_shift;
-  uint32_t split[15];
+  uint32_t split[kMaxDest - 1];
   const uint4* in;
   uint4* out;
   const uint32_t* n_dev;
@@ -297,13 +299,14 @@ struct SortPass16Args {
   int bits;
   const uint32_t* nk_dev;
   int pass, passes;
+  uint32_t key_base;       // the digits are those of key - key_base (a key range that starts at key_base sorts over fewer bits)
   int unstable;            // 1: equal digits may change their order inside a tile (the first pass of a sort)
   uint32_t spin_limit;     // polls before a look-back gives up; 0 = kSpinLimit
   const uint32_t* gbase;   // [kSort16Bins]
   uint32_t* lookback;      // [tiles][kSort16Bins], zeroed before the pass
   uint32_t* ticket;
   uint32_t* err;
-  uint4* dest[16];
+  uint4* dest[kMaxDest];
 };
 
 __device__ __forceinline__ void pass_digit(const SortPass16Args& a, int* shift, int* bits) {
@@ -316,7 +319,7 @@ __device__ __forceinline__ void pass_digit(const SortPass16Args& a, int* shift, 
 }
 
 __device__ __forceinline__ uint32_t digit16(const SortPass16Args& a, uint32_t key, int shift, uint32_t dmask) {
-  if (!a.by_dest) return (key >> shift) & dmask;
+  if (!a.by_dest) return ((key - a.key_base) >> shift) & dmask;
   const uint32_t b = key >> a.split_shift;
   uint32_t d = 0;
   for (uint32_t i = 0; i < a.n_split; ++i) d += a.split[i] <= b;
@@ -337,20 +340,20 @@ __device__ __forceinline__ uint32_t match_digit_n(uint32_t d, uint32_t valid_lan
   return same;
 }
 
-// histogram of the destination digit (multi-GPU partition): hist[16]
+// histogram of the destination digit (multi-GPU partition): hist[kMaxDest]
 __global__ void __launch_bounds__(256) k_dest_hist(const SortPass16Args a, uint32_t* __restrict__ hist) {
-  __shared__ uint32_t sh[16];
-  if (threadIdx.x < 16) sh[threadIdx.x] = 0;
+  __shared__ uint32_t sh[kMaxDest];
+  if (threadIdx.x < kMaxDest) sh[threadIdx.x] = 0;
   __syncthreads();
   const uint32_t n = a.n_dev ? *a.n_dev : a.n;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&sh[digit16(a, a.in[i].x, 0, 0xFFu)], 1u);
   __syncthreads();
-  if (threadIdx.x < 16 && sh[threadIdx.x]) atomicAdd(&hist[threadIdx.x], sh[threadIdx.x]);
+  if (threadIdx.x < kMaxDest && sh[threadIdx.x]) atomicAdd(&hist[threadIdx.x], sh[threadIdx.x]);
 }
 
 // the digit counts of every pass in one read of the sort keys: hist[passes][kSort16Bins]
 __global__ void __launch_bounds__(256) k_radix_hist16(const uint4* __restrict__ items, const uint32_t* n_dev, uint32_t n, int end_bit, int passes,
-                                                      const uint32_t* nk_dev, uint32_t* __restrict__ hist) {
+                                                      const uint32_t* nk_dev, uint32_t* __restrict__ hist, uint32_t key_base) {
   __shared__ uint32_t sh[4 * kSort16Bins];
   if (n_dev) n = min(*n_dev, n);
   if (nk_dev) end_bit = min(sort_key_bits(*nk_dev), passes * kSort16MaxBits);
@@ -367,7 +370,7 @@ __global__ void __launch_bounds__(256) k_radix_hist16(const uint4* __restrict__ 
     for (int u = 0; u < 4; ++u) {
       const uint32_t i = i0 + u * gstride;
       valid[u] = i < n;
-      k[u] = valid[u] ? items[i].x : 0u;
+      k[u] = valid[u] ? items[i].x - key_base : 0u;
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -415,7 +418,7 @@ __global__ void __launch_bounds__(THREADS, kSort16CtasPerSm) k_onesweep_pass16(c
   int shift, bits;
   pass_digit(a, &shift, &bits);
   const uint32_t dmask = (1u << bits) - 1u;
-  const uint32_t nd = a.by_dest ? 16u : (1u << bits);  // digits in use
+  const uint32_t nd = a.by_dest ? (uint32_t)kMaxDest : (1u << bits);  // digits in use
 
   while (true) {
     // A ticket is drawn only when its tile is started: a tile that is reserved ahead of time keeps every later tile waiting

@@ -261,7 +261,12 @@ extern "C" int64_t ks_build_table_streamed(ks_handle* h, const void* records, ui
       KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad[0], 0, 4 * 8 + 8, h->stream));
       KS_CUDA(h, cudaMemsetAsync(&h->d_ctl->pad2[0], 0, 16, h->stream));
       KS_CUDA(h, cudaMemsetAsync(h->row_of_kid, 0xFF, (size_t)(kMaxKeys + 1) * 4, h->stream));
-      const int cur = radix_sort16(h, np, key_bits, nullptr, as<uint4>(h->stream_store) + P.off[part]);
+      // the range's keys lie in [splitter << shift, next splitter << shift): sorted over the bits of that width only
+      const uint64_t key_end = nk + nk * nk + 1;
+      const uint64_t key_lo = part ? std::min<uint64_t>((uint64_t)P.splitters[part - 1] << P.shift, key_end) : 0;
+      const uint64_t key_hi = part + 1 < P.n_parts ? std::min<uint64_t>((uint64_t)P.splitters[part] << P.shift, key_end) : key_end;
+      const int cur = key_hi > key_lo ? radix_sort16(h, np, std::max(1, bit_length(key_hi - key_lo - 1)), nullptr, as<uint4>(h->stream_store) + P.off[part], nullptr, (uint32_t)key_lo)
+                                      : radix_sort16(h, np, key_bits, nullptr, as<uint4>(h->stream_store) + P.off[part]);
       if (cur < 0) return cur;
       const uint32_t max_rows = (uint32_t)std::min<uint64_t>(np, (uint64_t)h->cfg.max_pair_rows + nk) + 1;
       { int r = run_rows_and_stats(h, np ? as<uint4>(h->samples[cur]) : as<uint4>(h->samples[0]), np, max_rows); if (r) return r; }

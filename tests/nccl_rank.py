@@ -39,12 +39,22 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     torch.cuda.synchronize()
     skeys, spairs = session.build(window2, key_type=True)
     # ragged windows: three launches over two ranks, then one launch (the second rank's window is empty)
-    tiny_tables = []
+    tiny_tables, tiny_windows = [], []
     for m in (3, 1):
         lo3, hi3 = parallel.split_windows(m, world)[rank]
         w3 = torch.from_numpy(rec[:m][lo3:hi3].view(np.uint8).reshape(-1).copy()).cuda()
         torch.cuda.synchronize()
+        tiny_windows.append(w3)
         tiny_tables.append(session.build(w3))
+    # the same builds in stages (every rank owns two or four key ranges; the rows of one are carried to the other GPUs
+    # while the next is reduced): forced here, large tables choose it by themselves
+    two_stage_ok = True
+    for stages in ("2", "4"):
+        os.environ["KS_MG_STAGES"] = stages
+        staged = [session.build(window), session.build(window), session.build(window2, key_type=True)] + [session.build(w) for w in tiny_windows]
+        two_stage_ok = two_stage_ok and all(a[0].tobytes() == b_[0].tobytes() and a[1].tobytes() == b_[1].tobytes()
+                                            for a, b_ in zip(staged, [(nkeys, npairs), (nkeys, npairs), (skeys, spairs)] + tiny_tables))
+    os.environ["KS_MG_STAGES"] = "1"
     peer_memory = session.peer_memory
     # a bad record in the LAST rank's window: every rank gets the same status from the same call, nobody is left waiting,
     # and the session works afterwards
@@ -68,5 +78,5 @@ with torch.cuda.stream(stream), PairTableBuilder(device=rank, stream=stream.cuda
     ckeys, cpairs = session.build(window)
     session.close()
 np.savez(os.path.join(out, f"rank{rank}.npz"), keys=keys, pairs=pairs, nkeys=nkeys, npairs=npairs, skeys=skeys, spairs=spairs, ckeys=ckeys, cpairs=cpairs,
-         peer_memory=peer_memory, bad_status=status, t3keys=tiny_tables[0][0], t3pairs=tiny_tables[0][1], t1keys=tiny_tables[1][0], t1pairs=tiny_tables[1][1])
+         peer_memory=peer_memory, bad_status=status, two_stage_ok=two_stage_ok, t3keys=tiny_tables[0][0], t3pairs=tiny_tables[0][1], t1keys=tiny_tables[1][0], t1pairs=tiny_tables[1][1])
 dist.destroy_process_group()

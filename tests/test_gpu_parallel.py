@@ -106,6 +106,7 @@ def test_two_nccl_ranks(tmp_path):
         # ... and the one with the bulk exchanges on NCCL instead of peer memory
         assert d["ckeys"].tobytes() == d["keys"].tobytes() and d["cpairs"].tobytes() == d["pairs"].tobytes()
         print("peer memory:", bool(d["peer_memory"]))
+        assert bool(d["two_stage_ok"])  # two key ranges per rank, the first stored while the second is reduced: the same bytes
         assert int(d["bad_status"]) == 3  # KS_ERR_RECORD on BOTH ranks, although only the last rank's window held the bad record
         assert_tables_match(d["t3keys"], d["t3pairs"], *O.build_pair_table(rec[:3]))  # ragged windows
         assert_tables_match(d["t1keys"], d["t1pairs"], *O.build_pair_table(rec[:1]))  # an empty window on the second rank
