@@ -281,7 +281,7 @@ int64_t ks_tsv_extract(ks_handle* h, const char* text, uint64_t n_bytes, uint32_
 int64_t ks_segment_hist(ks_handle* h, const uint32_t* values, const uint64_t* offsets, uint64_t n_segments, uint32_t n_bins, uint32_t log2_bins,
                         uint32_t flags, uint32_t* out);
 
-/* ---- the resident table: windows of new launches merged into statistics that stay in HBM (BASELINE config 5: "online
+/* ---- the resident table: windows of new launches merged into statistics that stay in HBM (benchmark configuration 5: "online
  * incremental mode"; the reference has no such path, its tables are rebuilt offline).  At any time the table read out is
  * exactly the one ks_build_table gives for all launches so far: counts, sums, minima and maxima are accumulators, and
  * for the medians every row keeps the 64 values around its median in sorted order plus how many lie below (ks_update.cuh).

@@ -1,4 +1,4 @@
-"""Online incremental mode (BASELINE config c5): a resident pair table updated window by window.
+"""Online incremental mode (benchmark configuration c5): a resident pair table updated window by window.
 
     python -m kernel_scheduling_b200.online [--windows 10000] [--window-records 65536] [--verify] [--publish-every K]
 

@@ -14,7 +14,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REFERENCE = Path(os.environ.get("KS_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: KS_REFERENCE_DIR, or the directory "reference" beside this repository
+REFERENCE = Path(os.environ.get("KS_REFERENCE_DIR") or HERE.parent.parent / "reference")
 
 
 def build() -> bool:

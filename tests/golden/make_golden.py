@@ -19,7 +19,7 @@ import pandas as pd
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("KS_REFERENCE_DIR", "/root/reference"))
+REF = Path(os.environ.get("KS_REFERENCE_DIR") or ROOT.parent / "reference")  # the reference checkout beside this repository
 TIMING_COLS = ["kernel_id", "kernel_us", "prefetch_us", "prefetch_to_kernel_gap_us", "hook_tag", "prefetch_bytes", "prefetched_tensors", "args_check",
                "kernel_name", "start_ns", "end_ns", "batch_id", "batch_size", "batch_pos", "block", "model", "grid"]
 
