@@ -389,7 +389,12 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   tr.stream = h->stream;
   tr.mark("start");
   cudaEvent_t* ev = h->ev;  // phase boundaries on the handle's stream (read only with KS_TIMING)
-  const bool p2p = h->mg_p2p && world > 1;
+  // one rank with KS_MG_STAGES=2|4 in the environment: the staged build on the rank's own buffers (no peers to copy to),
+  // so that the stage logic can be exercised on one GPU
+  bool self_staged = false;
+  if (world == 1)
+    if (const char* e = getenv("KS_MG_STAGES")) self_staged = e[0] == '2' || e[0] == '4';
+  const bool p2p = (h->mg_p2p && world > 1) || self_staged;
   const uint64_t n_tl = n_owned + kHaloMax;  // the join always sees all halo slots (unused ones are inert)
   const size_t width2 = H + kMgHistBytes, block2 = width2;
   // blocks 2 and 4 at their largest, so that the exchange buffers are sized once per key capacity

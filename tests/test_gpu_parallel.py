@@ -127,6 +127,28 @@ def test_native_driver_single_rank(cfg, n, key_type):
         session.close()
 
 
+@pytest.mark.parametrize("stages", ["2", "4"])
+def test_native_driver_in_stages_single_rank(stages, monkeypatch):
+    """The staged build (every rank owns several key ranges, reduced one after the other, each sorted over the bits of its
+    own width, their rows placed in key-range order) with one rank: no peers to copy to, everything else as on eight GPUs."""
+    monkeypatch.setenv("KS_MG_STAGES", stages)
+    with PairTableBuilder(device=0) as b:
+        session = parallel.NativeSession(b)
+        for cfg, n, key_type in (("c3", 400_000, False), ("c4", 500_000, False), ("c2", 300_000, True), ("c1", 3, False), ("c1", 0, False)):
+            rec = trace.generate(trace.config(cfg, max(n, 4096)))[:n]
+            okeys, opairs = O.build_pair_table(rec, key_mode=O.KEY_TYPE if key_type else O.KEY_SHAPE)
+            window = _window(rec)
+            for _ in range(2):  # the second call knows the last table's size
+                keys, pairs = session.build(window, key_type=key_type)
+                assert_tables_match(keys, pairs, okeys, opairs)
+        # ... and the same handle without stages afterwards
+        monkeypatch.delenv("KS_MG_STAGES")
+        rec = trace.generate(trace.config("c3", 200_000))
+        keys, pairs = session.build(_window(rec))
+        assert_tables_match(keys, pairs, *O.build_pair_table(rec))
+        session.close()
+
+
 def _window(rec):
     t = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).cuda()
     torch.cuda.synchronize()
