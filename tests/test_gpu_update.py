@@ -109,3 +109,42 @@ def test_a_jump_of_a_rows_distribution_is_reported_not_hidden():
             b.update(rec[n1:])
         assert e.value.status == _lib.ERR_REBUILD
         b.update_end()
+
+
+def test_online_driver_verifies_publishes_and_takes_host_windows():
+    """The online configuration's driver at a small size: stretches generated beside the GPU, the table at the end equal to
+    a batch build over every launch (verify), the last windows arriving in pinned host memory, and the table republished in
+    the shared-memory segment every few windows."""
+    import os
+
+    from kernel_scheduling_b200 import online, pair_table_shm
+
+    name = f"/ks_test_online_{os.getpid()}"
+    try:
+        res = online.run(windows=24, per=4096, verify=True, publish_every=8, host_windows=4, shm_name=name)
+        assert res["verified_against_batch_build"] is True
+        assert res["records"] == 24 * 4096 and res["windows"] == 24
+        assert res["host_windows"]["windows"] == 4 and res["publish"]["times"] == 3
+        assert res["p50"] > 0 and res["device_ms_p50"] > 0 and res["pair_rows"] > 0
+        with pair_table_shm.Attached(name) as seg:
+            assert seg.generation == 24  # the last publication: after window 24
+    finally:
+        pair_table_shm.unlink(name)
+
+
+def test_online_stretches_are_ordered_and_reproducible():
+    from kernel_scheduling_b200 import online
+
+    got = list(online.stretches(7, 512))
+    old = online.STRETCH_WINDOWS
+    try:
+        online.STRETCH_WINDOWS = 3  # three stretches of 3, 3 and 1 windows
+        parts = list(online.stretches(7, 512))
+    finally:
+        online.STRETCH_WINDOWS = old
+    assert [f for f, _ in got] == [0] and [f for f, _ in parts] == [0, 3, 6]
+    assert sum(len(r) for _, r in parts) == 7 * 512 == len(got[0][1])
+    allrec = np.concatenate([r for _, r in parts])
+    assert np.all(np.diff(allrec["start_ns"].astype(np.int64)) >= 0)  # stretches follow one another in time
+    again = np.concatenate([r for _, r in online.stretches(7, 512)])
+    assert again.tobytes() == got[0][1].tobytes()
