@@ -366,6 +366,46 @@ __global__ void __launch_bounds__(256) k_key_hist_dev(const uint4* __restrict__ 
     if (sh[i]) atomicAdd(&hist[i], (unsigned long long)sh[i]);
 }
 
+// The histogram bins that hold a cut between two key ranges, counted again in 1 << sub_bits sub-bins each:
+// out[cut index << sub_bits | sub-bin] += 1 for every sample whose bin is bin[cut index].
+struct KeySubHistArgs {
+  uint32_t n_cut;
+  uint32_t sub_bits;
+  uint32_t bin[31];  // ascending
+};
+__global__ void __launch_bounds__(256) k_key_subhist_dev(const uint4* __restrict__ samples, const Control* __restrict__ ctl, uint64_t capacity, const KeySubHistArgs a,
+                                                         unsigned long long* __restrict__ out) {
+  __shared__ uint32_t sh[31 * 256];
+  __shared__ unsigned char cut_of_bin[kKeyHistBins];
+  const uint32_t n = (uint32_t)min((unsigned long long)capacity, ctl->n_pairs);
+  const uint32_t shift = key_hist_shift(ctl->n_keys);
+  const uint32_t words = a.n_cut << a.sub_bits;
+  for (uint32_t i = threadIdx.x; i < words; i += blockDim.x) sh[i] = 0;
+  for (uint32_t i = threadIdx.x; i < kKeyHistBins; i += blockDim.x) cut_of_bin[i] = 0xFF;
+  __syncthreads();
+  if (threadIdx.x < a.n_cut) cut_of_bin[a.bin[threadIdx.x]] = (unsigned char)threadIdx.x;
+  __syncthreads();
+  const uint32_t sub_shift = shift - a.sub_bits, sub_mask = (1u << a.sub_bits) - 1u;  // sub_bits <= shift
+  const uint32_t gstride = gridDim.x * blockDim.x;
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += 4 * gstride) {  // four loads in flight per thread
+    uint32_t k[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t i = i0 + u * gstride;
+      k[u] = i < n ? samples[i].x : 0xFFFFFFFFu;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u * gstride >= n) continue;
+      const uint32_t c = cut_of_bin[min(k[u] >> shift, kKeyHistBins - 1)];
+      if (c != 0xFF) atomicAdd(&sh[(c << a.sub_bits) | ((k[u] >> sub_shift) & sub_mask)], 1u);
+    }
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < words; i += blockDim.x)
+    if (sh[i]) atomicAdd(&out[i], (unsigned long long)sh[i]);
+}
+
 // every key's solo time: the rank that reduced the key's solo row has a number, the others NaN
 __global__ void __launch_bounds__(256) k_solo_merge(const unsigned char* __restrict__ gathered, size_t stride, uint32_t world, size_t off_solo, uint32_t nk,
                                                     double* __restrict__ solo_ns) {

@@ -129,6 +129,7 @@ struct MgTrace {
   int rank = 0;
   cudaStream_t stream = nullptr;
   std::vector<std::pair<const char*, cudaEvent_t>> marks;
+  std::string note;  // appended to the line (the rows of this rank's parts)
   void mark(const char* name) {
     if (!on) return;
     cudaEvent_t e;
@@ -145,7 +146,8 @@ struct MgTrace {
       snprintf(buf, sizeof(buf), " %s=%.3f", marks[i].first, ev_ms(marks[i - 1].second, marks[i].second));
       line += buf;
     }
-    fprintf(stderr, "%s\n", line.c_str());
+    fprintf(stderr, "%s%s\n", line.c_str(), note.c_str());
+    note.clear();
     for (auto& m : marks) cudaEventDestroy(m.second);
     marks.clear();
   }
@@ -573,10 +575,30 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     while (stages * world > kMaxDest) stages >>= 1;
   }
   const int parts = stages * world;
-  // part p owns bins [edge[p], edge[p+1]): the first bin with at least p/parts of the samples in front of it
-  std::vector<uint32_t> edge(parts + 1, kKeyHistBins);
+  // Part p owns the keys [edge[p], edge[p+1]) in units of FINE bins (key >> fshift).  First cut: the histogram bin in
+  // which the share p/parts of the samples is reached.  A bin is 1/4,096 of the key space, and a hot kernel's pairs can put
+  // a percent of all samples into one or two of them -- a third of a part when there are 32 parts.  With KS_MG_REFINE=1
+  // (the same on every rank) the bins that hold a cut are counted once more in 256 sub-bins each (one more pass over the
+  // sample keys, one more exchange and host wait) and the cut is placed inside them, so that all parts hold the same
+  // number of samples; every count stays exact (whole bins from the first histogram, split bins from the second).
+  // Off by default: on the 1 B-record trace it gained 1 ms of 57.5 on four GPUs and LOST 3.6 ms of 66.2 on eight -- the
+  // ranks no longer wait for one another behind sort + statistics, but a part's ROWS (what the copy engines carry) then
+  // differ more, and at eight GPUs the copies are what the build waits for.
+  const uint32_t sub_bits = std::min<uint32_t>(8, shift);
+  bool refine = false;
+  if (const char* e = getenv("KS_MG_REFINE")) refine = e[0] == '1' && parts > 1 && sub_bits > 0 && all > 0;
+  const uint32_t fshift = refine ? shift - sub_bits : shift;        // fine bin = key >> fshift
+  const uint32_t fbits = refine ? sub_bits : 0;                     // fine bins per histogram bin = 1 << fbits
+  std::vector<uint64_t> edge(parts + 1, (uint64_t)kKeyHistBins << fbits);
   edge[0] = 0;
+  std::vector<uint64_t> coarse((size_t)world * kKeyHistBins);       // the pinned copies are overwritten by the next exchange
+  for (int q = 0; q < world; ++q) memcpy(&coarse[(size_t)q * kKeyHistBins], hist_of(q), kMgHistBytes);
+  KeySubHistArgs cut{};                                             // the bins that hold a cut, ascending
+  std::vector<uint64_t> sub;                                        // [rank][cut bin][sub-bin]
   {
+    // first cut, and for every part the samples of its cut bin that belong in front of the cut
+    std::vector<uint32_t> cut_bin(parts, 0);
+    std::vector<uint64_t> need(parts, 0);
     uint64_t before = 0;
     uint32_t b = 0;
     // (equal shares for all stages: a smaller first stage, so that the copies start earlier, was measured slower -- the
@@ -584,23 +606,69 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     for (int p = 1; p < parts; ++p) {
       const uint64_t target = (all * (uint64_t)p + (uint64_t)parts - 1) / (uint64_t)parts;
       while (b < kKeyHistBins && before < target) before += total[b++];
-      edge[p] = b;
+      edge[p] = (uint64_t)b << fbits;
+      if (refine && b > 0 && before > target) {  // the cut lies inside bin b - 1
+        cut_bin[p] = b;                          // + 1, 0 = none
+        need[p] = target - (before - total[b - 1]);
+        if (!cut.n_cut || cut.bin[cut.n_cut - 1] != b - 1) cut.bin[cut.n_cut++] = b - 1;
+      }
     }
-    if (stages > 1 && nk) {  // every solo row in stage 0: the table rows of every stage need all solo times
-      const uint32_t solo_end = (uint32_t)std::min<uint64_t>(kKeyHistBins, ((nk - 1) >> shift) + 1);
+    if (cut.n_cut) {
+      const size_t sub_words = (size_t)cut.n_cut << fbits, sub_bytes = sub_words * 8;
+      unsigned char* blk = as<unsigned char>(h->mg_block);
+      KS_CUDA(h, cudaMemsetAsync(blk, 0, sub_bytes, h->stream));
+      cut.sub_bits = fbits;
+      k_key_subhist_dev<<<h->sm_count * 6, 256, 0, h->stream>>>(as<uint4>(h->samples[0]), h->d_ctl, cap_s, cut, reinterpret_cast<unsigned long long*>(blk));
+      ++h->launches;
+      KS_CUDA(h, cudaGetLastError());
+      KS_NCCL(h, api->AllGather(blk, h->mg_gathered.p, sub_bytes, kNcclUint8, h->mg_comm, h->stream));
+      sub.resize(sub_words * (size_t)world);
+      KS_CUDA(h, cudaMemcpyAsync(sub.data(), h->mg_gathered.p, sub_bytes * (size_t)world, cudaMemcpyDeviceToHost, h->stream));
+      KS_CUDA(h, cudaStreamSynchronize(h->stream));                                                    // ---- wait 1b
+      tr.mark("cut bins counted again");
+      for (int p = 1; p < parts; ++p) {
+        if (!cut_bin[p]) continue;
+        const uint32_t cb = cut_bin[p] - 1;
+        uint32_t ci = 0;
+        while (cut.bin[ci] != cb) ++ci;
+        uint64_t acc = 0;
+        uint32_t j = 0;
+        while (j < (1u << fbits) && acc < need[p]) {  // the first sub-bin boundary with at least `need` samples in front
+          for (int q = 0; q < world; ++q) acc += sub[((size_t)q * cut.n_cut + ci) << fbits | j];
+          ++j;
+        }
+        edge[p] = ((uint64_t)cb << fbits) + j;
+      }
+    }
+    if (stages > 1 && nk) {  // every solo row in stage 0 (a bin boundary: no split bin needed): the table rows of every stage need all solo times
+      const uint64_t solo_end = std::min<uint64_t>(kKeyHistBins, ((nk - 1) >> shift) + 1) << fbits;
       for (int p = world; p < parts; ++p) edge[p] = std::max(edge[p], solo_end);
     }
+    for (int p = 1; p <= parts; ++p) edge[p] = std::max(edge[p], edge[p - 1]);
   }
-  // cnt[q][p]: samples rank q holds for part p -- one walk over every rank's histogram
+  // cnt[q][p]: samples rank q holds for part p -- whole bins from its histogram, split bins from its sub-bin counts
   uint64_t cnt[16][kMaxDest] = {{0}};
-  for (int q = 0; q < world; ++q) {
-    const uint64_t* hq = hist_of(q);
-    for (int p = 0; p < parts; ++p) {
-      uint64_t sum = 0;
-      for (uint32_t b = edge[p]; b < edge[p + 1]; ++b) sum += hq[b];
-      cnt[q][p] = sum;
+  auto count_range = [&](int q, uint64_t lo, uint64_t hi) -> uint64_t {  // fine bins [lo, hi)
+    const uint64_t* hq = &coarse[(size_t)q * kKeyHistBins];
+    const uint64_t fmask = (1ull << fbits) - 1;
+    uint64_t sum = 0;
+    while (lo < hi) {
+      const uint64_t bin = lo >> fbits, bin_end = (bin + 1) << fbits;
+      if (!(lo & fmask) && hi >= bin_end) { sum += hq[bin]; lo = bin_end; continue; }
+      uint32_t ci = 0;
+      while (ci < cut.n_cut && cut.bin[ci] != bin) ++ci;
+      if (ci == cut.n_cut) return ~0ull;  // a split bin that was not counted: cannot happen (checked below)
+      const uint64_t stop = std::min(hi, bin_end);
+      for (uint64_t f = lo; f < stop; ++f) sum += sub[(((size_t)q * cut.n_cut + ci) << fbits) | (f & fmask)];
+      lo = stop;
     }
-  }
+    return sum;
+  };
+  for (int q = 0; q < world; ++q)
+    for (int p = 0; p < parts; ++p) {
+      cnt[q][p] = count_range(q, edge[p], edge[p + 1]);
+      if (cnt[q][p] == ~0ull) return fail(h, KS_ERR_COMM, "ks_mg_build: a key range ends inside a histogram bin that was not split");
+    }
   std::vector<uint64_t> part_in(parts, 0);  // samples of part p over all ranks
   for (int p = 0; p < parts; ++p) {
     for (int q = 0; q < world; ++q) part_in[p] += cnt[q][p];
@@ -614,7 +682,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
   std::vector<uint64_t> send_cnt(world, 0), recv_cnt(world, 0);  // one stage: per peer (the send/recv exchange)
   for (int q = 0; q < world; ++q) { send_cnt[q] = cnt[rank][q]; recv_cnt[q] = cnt[q][rank]; }
   uint32_t splitters[kMaxDest] = {0};
-  for (int p = 1; p < parts; ++p) splitters[p - 1] = edge[p];
+  for (int p = 1; p < parts; ++p) splitters[p - 1] = (uint32_t)edge[p];
   std::vector<uint64_t> soff(world + 1, 0), roff(world + 1, 0);
   for (int q = 0; q < world; ++q) { soff[q + 1] = soff[q] + send_cnt[q]; roff[q + 1] = roff[q] + recv_cnt[q]; }
   {
@@ -660,7 +728,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
       }
       dest[p] = reinterpret_cast<uint4*>(base + my_off_at[p] * 16);
     }
-    { int r = mg_partition_to_peers(h, splitters, shift, (uint32_t)parts, dest); if (r) return r; }
+    { int r = mg_partition_to_peers(h, splitters, fshift, (uint32_t)parts, dest); if (r) return r; }
     tr.mark("wait1+partition to peers");
     { int r = mg_barrier(h); if (r) return r; }
     tr.mark("barrier");
@@ -669,7 +737,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     if (sample_capacity(h) < largest) { int r = ensure_samples(h, largest); if (r) return r; }  // the sort's two sets
   } else {
     // -- NCCL: partition into sample set 1, one send/recv pair per peer with exact sizes, own part by a local copy
-    { int64_t r = ks_mg_partition(h, splitters, shift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
+    { int64_t r = ks_mg_partition(h, splitters, fshift, (uint32_t)world, h->samples[1].p, sample_capacity(h), nullptr); if (r < 0) return r; }
     tr.mark("wait1+partition");
     const bool in_place = n_recv <= sample_capacity(h);
     if (!in_place) KS_ENSURE(h, h->mg_recv, n_recv * 16);
@@ -712,8 +780,8 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     const uint4* in_s = sort_input ? sort_input + stage_off[s] : nullptr;
     // the part's keys lie in [edge << shift, next edge << shift): sorted over the bits of that width only
     const uint64_t key_end = nk + nk * nk + 1;
-    const uint64_t key_lo = std::min<uint64_t>((uint64_t)edge[s * world + rank] << shift, key_end);
-    const uint64_t key_hi = s * world + rank + 1 == parts ? key_end : std::min<uint64_t>((uint64_t)edge[s * world + rank + 1] << shift, key_end);
+    const uint64_t key_lo = std::min<uint64_t>(edge[s * world + rank] << fshift, key_end);
+    const uint64_t key_hi = s * world + rank + 1 == parts ? key_end : std::min<uint64_t>(edge[s * world + rank + 1] << fshift, key_end);
     { int r = mg_reduce_queue(h, p2p ? n_stage[s] : n_recv, in_s, s == 0, key_lo, key_hi); if (r) return r; }
     tr.mark("sort+stats");
     if (p2p && s == 0) { int r = mg_export_ensure(h, h->mg_table_x, std::max<size_t>(h->mg_table_x.cap, (size_t)8 << 20)); if (r) return r; }
@@ -755,6 +823,7 @@ int64_t ks_mg_build(ks_handle* h, const void* records, uint64_t n_owned, uint32_
     }
     const int p_mine = s * world + rank;
     const uint64_t rows_mine = part_rows[p_mine];
+    if (tr.on) tr.note += " [stage " + std::to_string(s) + ": " + std::to_string(n_stage[s]) + " samples, " + std::to_string(rows_mine) + " rows]";
     const uint64_t rows_before = row_base(s * world);  // the rows of the stages before this one
     rows_total = row_base(parts);                      // the rows known so far; behind the last stage: the table
     if (s == 0) *h->h_ctl = mg_head(h, H, rank).ctl;

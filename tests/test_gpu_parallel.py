@@ -127,11 +127,12 @@ def test_native_driver_single_rank(cfg, n, key_type):
         session.close()
 
 
-@pytest.mark.parametrize("stages", ["2", "4"])
-def test_native_driver_in_stages_single_rank(stages, monkeypatch):
+@pytest.mark.parametrize("stages,refine", [("2", "0"), ("4", "0"), ("4", "1")])
+def test_native_driver_in_stages_single_rank(stages, refine, monkeypatch):
     """The staged build (every rank owns several key ranges, reduced one after the other, each sorted over the bits of its
     own width, their rows placed in key-range order) with one rank: no peers to copy to, everything else as on eight GPUs."""
     monkeypatch.setenv("KS_MG_STAGES", stages)
+    monkeypatch.setenv("KS_MG_REFINE", refine)  # 1: the cuts between key ranges placed inside histogram bins (equal sample counts)
     with PairTableBuilder(device=0) as b:
         session = parallel.NativeSession(b)
         for cfg, n, key_type in (("c3", 400_000, False), ("c4", 500_000, False), ("c2", 300_000, True), ("c1", 3, False), ("c1", 0, False)):
