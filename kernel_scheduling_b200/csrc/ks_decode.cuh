@@ -155,11 +155,7 @@ __global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm) k_decode_has
       }
       start[u] = (unsigned long long)w2.x | ((unsigned long long)w2.y << 32);
       end[u] = (unsigned long long)w2.z | ((unsigned long long)w2.w << 32);
-#ifdef KS_EXP_NOHASH
-      key[u] = ((unsigned long long)w0[u].x << 32 | w1[u].w) * 0x9E3779B97F4A7C15ull | 1ull;
-#else
       key[u] = kernel_key(w0[u].x, w0[u].y, w0[u].z, w0[u].w, w1[u].x, w1[u].y, w1[u].z, w1[u].w, a.type_mode != 0);
-#endif
       seen[u] = valid[u] ? ld_volatile_u64(reinterpret_cast<const uint64_t*>(a.dict_keys + dict_home(key[u]))) : 0ull;
     }
 
@@ -182,7 +178,6 @@ __global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm) k_decode_has
           a.dict_words[2 * (size_t)slot] = k0;
           a.dict_words[2 * (size_t)slot + 1] = k1;
         }
-#ifndef KS_EXP_NOCOUNT
         if (!a.halo) {
           // launch counts: CTA-local cache first (a plain load finds the key's entry once it exists), global atomics
           // when the cache is crowded
@@ -204,7 +199,6 @@ __global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm) k_decode_has
             if (solo) atomicAdd(&a.dict_solo[slot], 1u);
           }
         }
-#endif
         if (end[u] < start[u] || end[u] - start[u] >= 0x80000000ull) err |= kErrRecord;
         if (start[u] < prev[u] && !(a.halo && r[u] == 0)) err |= kErrUnordered;
         const uint32_t dur = (uint32_t)(end[u] - start[u]);

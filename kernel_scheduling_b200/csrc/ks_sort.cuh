@@ -258,13 +258,9 @@ __global__ void __launch_bounds__(kSortThreads) k_onesweep_pass(const SortPassAr
 // three passes, not four); the look-back reads four earlier tiles per round trip.
 constexpr int kSort16MaxBits = 9;
 constexpr int kSort16Bins = 1 << kSort16MaxBits;  // look-back words per tile, counters per pass
-#ifndef KS_SORT16_ITEMS
-#define KS_SORT16_ITEMS 8
-#define KS_SORT16_CTAS 2
-#endif
 constexpr int kSort16Threads = 512;               // threads per CTA of the sample sort
-constexpr int kSort16Items = KS_SORT16_ITEMS;     // items per thread: tiles of kSort16Threads x kSort16Items samples
-constexpr int kSort16CtasPerSm = KS_SORT16_CTAS;
+constexpr int kSort16Items = 8;                   // items per thread: tiles of kSort16Threads x kSort16Items samples
+constexpr int kSort16CtasPerSm = 2;
 
 // Digits of a sort over end_bit key bits in `passes` passes: as equal as possible, the wider ones first.
 __host__ __device__ __forceinline__ void digit_layout(int end_bit, int passes, int pass, int* shift, int* bits) {
@@ -441,16 +437,8 @@ __global__ void __launch_bounds__(THREADS, kSort16CtasPerSm) k_onesweep_pass16(c
     }
     // The first pass of a sort has no earlier order to keep, so it may rank the items of a tile in any order: one
     // shared-memory atomic per item on the CTA's counters (row 0) instead of a ballot per digit bit and per-warp counters.
-    #ifdef KS_EXP_ALLUNSTABLE
-    uint32_t* wh = warp_hist;
-#else
     uint32_t* wh = warp_hist + (a.unstable ? 0u : warp * kSort16Bins);
-#endif
-#ifdef KS_EXP_ALLUNSTABLE
-    if (true) {
-#else
     if (a.unstable) {
-#endif
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
         const uint32_t li = wbase + i * 32 + lane;
@@ -532,9 +520,6 @@ __global__ void __launch_bounds__(THREADS, kSort16CtasPerSm) k_onesweep_pass16(c
         left[q] = (tid + q * THREADS < nd) ? tile : 0u;
         open = open || left[q] != 0;
       }
-#ifdef KS_EXP_NO_LOOKBACK
-      open = false;
-#endif
       uint32_t spins = 0;
       const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
       while (open) {
