@@ -5,6 +5,8 @@
   postprocess_cases.json   inputs (two start_ns columns) and the exact stdout of scheduler/postprocess.py
   combine_in_*.csv / combine_out_*.csv   inputs and outputs of postprocess/profile_postprocess.py's CLI
   function_base.tsv        symbol -> ncu_function_base(symbol), from oracle/_ref/ref_function_base
+  pair_table_small.npz     the main path (no reference implementation exists for it): seeded traces of a few thousand launches
+                           and their tables from the O(n^2) restatement that uses numpy.median (SHAPE and TYPE keys)
 The vectors are committed; the tests never read the reference tree.
 """
 import json
@@ -155,7 +157,32 @@ def ncu_pool_case():
     print(f"ncu_pool_case: {len(frame)} launches, labels {labels}")
 
 
+def pair_table_case():
+    """The interval join + slowdown statistics have no reference implementation to run.  Their fixture is the table the
+    quadratic pure-Python restatement gives (the slowest and plainest statement of the definitions), stored with its input."""
+    sys.path.insert(0, str(ROOT))
+    from kernel_scheduling_b200 import trace
+    from oracle import pair_table_oracle as O
+
+    out = {}
+    for tag, cfg, n, mode in (("c1", "c1", 2500, O.KEY_SHAPE), ("c3", "c3", 2000, O.KEY_SHAPE), ("c2type", "c2", 2000, O.KEY_TYPE)):
+        spec = trace.config(cfg, n)
+        for t in spec.tenants:
+            t.n_keys = min(t.n_keys, 40)  # few keys: rows with many samples, even and odd counts
+        rec = trace.generate(spec, interleave_solo=(tag == "c3"))
+        keys, pairs = O.build_pair_table_bruteforce(rec, key_mode=mode)  # dicts of columns
+        out[f"{tag}.records"], out[f"{tag}.mode"] = rec, np.int64(mode)
+        for c, v in keys.items():
+            out[f"{tag}.keys.{c}"] = v
+        for c, v in pairs.items():
+            out[f"{tag}.pairs.{c}"] = v
+        print(f"pair_table_case {tag}: {len(rec)} records, {len(keys['key'])} keys, {len(pairs['count'])} rows, {int(pairs['count'].sum())} pairs, "
+              f"largest row {int(pairs['count'].max())}")
+    np.savez_compressed(HERE / "pair_table_small.npz", **out)
+
+
 if __name__ == "__main__":
+    pair_table_case()
     postprocess_cases()
     combine_cases()
     function_base_cases()

@@ -247,3 +247,17 @@ def test_streamed_build_edge_cases(builder):
     assert e.value.status == _lib.ERR_NOT_ORDERED
     keys, pairs = builder.build(rec, time_ordered=True)  # the handle stays usable
     assert_tables_match(keys, pairs, *O.build_pair_table(rec))
+
+
+def test_committed_pair_tables(builder):
+    """The CUDA path against the committed fixture of the main path (records in, table out), SHAPE and TYPE keys."""
+    import os
+
+    from tests.helpers import load_golden_pair_tables
+
+    cases = load_golden_pair_tables(os.path.join(os.path.dirname(__file__), "golden", "pair_table_small.npz"))
+    for tag, (rec, mode, gkeys, gpairs) in cases.items():
+        keys, pairs = builder.build(rec, key_type=(mode == O.KEY_TYPE))
+        assert_tables_match(keys, pairs, gkeys, gpairs)
+        keys, pairs = builder.build(rec, key_type=(mode == O.KEY_TYPE), time_ordered=True)
+        assert_tables_match(keys, pairs, gkeys, gpairs)

@@ -207,3 +207,19 @@ def test_fast_generator_is_ordered_deterministic_and_shaped_like_the_numpy_one()
     for t in range(4):
         m = (rec["smem_word"] >> 24) == t
         assert (rec["start_ns"][m][1:] >= rec["end_ns"][m][:-1]).all()
+
+
+def test_oracles_equal_the_committed_pair_tables():
+    """The main path's fixture (tests/golden/pair_table_small.npz: seeded traces and the tables the quadratic restatement
+    gave when the fixture was made): the vectorised oracle and the C oracle still give exactly those tables."""
+    from oracle import c_oracle as CO
+    from tests.helpers import assert_columns_match, load_golden_pair_tables
+
+    cases = load_golden_pair_tables(os.path.join(GOLDEN, "pair_table_small.npz"))
+    assert set(cases) == {"c1", "c3", "c2type"}
+    for tag, (rec, mode, gkeys, gpairs) in cases.items():
+        assert rec.dtype == RECORD_DTYPE and len(gpairs["count"]) > 200
+        keys, pairs = O.build_pair_table(rec, key_mode=mode)
+        assert_columns_match(keys, pairs, gkeys, gpairs)
+        ckeys, cpairs = CO.build_pair_table(rec, key_mode=mode)
+        assert_columns_match(ckeys, cpairs, gkeys, gpairs)
