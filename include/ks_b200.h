@@ -236,7 +236,13 @@ int ks_mg_comm_destroy(ks_handle* h);
  * the environment of any rank turns it off): the partition kernel and the finalize kernel store straight into the other
  * GPUs' buffers over NVLink, and a 16-byte all-gather orders the stores before the readers.  Otherwise they are NCCL
  * send/recv pairs.  Returns 1 for peer memory, 0 for NCCL.  ks_mg_comm_destroy is collective in peer-memory mode (every
- * rank unmaps before any rank frees). */
+ * rank unmaps before any rank frees).
+ * In peer-memory mode a large table (its size is known from the session's previous build) is built in two or four
+ * STAGES: every rank owns several key ranges, and while one range is sorted and reduced the copy engines carry the rows
+ * of the range before it into the other GPUs' tables.  Environment (the same on every rank): KS_MG_STAGES=1|2|4 forces the
+ * stage count (with one rank: the staged build on the rank's own buffers), KS_MG_REFINE=1 places the cuts between key
+ * ranges inside histogram bins so that the ranges hold equal sample counts, KS_MG_TRACE=1|2 prints the device time
+ * between the driver's steps (rank 0 | every rank). */
 int ks_mg_peer_memory(ks_handle* h);
 
 /* ---- the agent's timing log (text) -> launch records, on the device.  Replaces the pandas read of the 17-column TSV the
