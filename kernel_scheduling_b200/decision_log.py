@@ -7,7 +7,7 @@ The scheduler daemon writes one row per finished kernel (scheduler/scheduler_dae
 ``kernel_id``, ``kernel_base``, ``grid``, ``block``, ``model``) and how long it waited (``request_ns``, ``post_ns``,
 ``queue_wait_us``).  The agents' logs (scheduler/agent.cpp:692-705) hold what the kernel then did (``start_ns``,
 ``end_ns``); the two are joined on (pid, kernel_id), as the daemon's comment says (:587).  The reference ships no analysis of
-these logs; this module is the one the survey lists as the next consumer of the device-side text parser:
+these logs; this module analyses them with the device-side text parser and the segmented kernels of the pair-table path:
 
   * both logs are parsed on the device (``ks_tsv_extract``: line splitting, tab walking, integer / decimal / dimension
     fields, 64-bit string hashes),
