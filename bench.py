@@ -333,15 +333,17 @@ def main():
         sampler.wait_first(5.0)
     barrier()
     warm = max(args.warmup, 3)
-    t0 = time.perf_counter()
-    for _ in range(warm):
+    for _ in range(warm - 1):
         step_device()
     torch.cuda.synchronize()
-    est_ms = 1e3 * (time.perf_counter() - t0) / warm
+    t0 = time.perf_counter()  # the last warm-up step alone sizes the timed region (the first ones grow buffers)
+    step_device()
+    torch.cuda.synchronize()
+    est_ms = 1e3 * (time.perf_counter() - t0)
     if args.clock_load_steps > 0 and est_ms * warm < 300.0:  # short steps: more load in front so that the sampler sees steady clocks
         for _ in range(int(min(args.clock_load_steps, 300.0 / max(est_ms, 1e-3)))):
             step_device()
-    n_blocks = int(min(50, max(3, -(-MIN_TIMED_S * 1e3 // max(est_ms * args.steps, 1e-3))))) if args.clock_load_steps > 0 else 1
+    n_blocks = int(min(50, max(3, -(-1.2 * MIN_TIMED_S * 1e3 // max(est_ms * args.steps, 1e-3))))) if args.clock_load_steps > 0 else 1
     nb = torch.tensor([n_blocks], device="cuda")
     if world > 1:
         dist.all_reduce(nb, op=dist.ReduceOp.MAX)
